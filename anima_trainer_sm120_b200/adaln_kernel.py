@@ -1,0 +1,83 @@
+"""Fused AdaLN and gated-residual autograd ops with the call surface of
+anima-trainer's ``adaln_kernel.py`` (``FusedAdaLN`` :157, ``fused_adaln`` :258,
+``FusedGatedAdd`` :332, ``fused_gated_add`` :422), backed by the sm_100a kernels
+in ``csrc/adaln.cu``.
+
+Shapes follow the reference: ``x``/``y`` are ``(B, T, H, W, D)``, modulation
+tensors are ``(B, T, 1, 1, D)`` and broadcast over ``(H, W)``. Statistics and all
+elementwise math are fp32; results are stored in bf16. Unlike the reference the
+``(H, W)`` reductions (dscale, dshift, dgate) are deterministic.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+BF16 = torch.bfloat16
+
+
+def _flat(t: torch.Tensor, d: int) -> torch.Tensor:
+    t = t.contiguous().view(-1, d)
+    return t if t.dtype == BF16 else t.to(BF16)
+
+
+class FusedAdaLN(torch.autograd.Function):
+    """``LayerNorm(x, no affine, eps) * (1 + scale) + shift``."""
+
+    @staticmethod
+    def forward(ctx, x, scale, shift, eps):
+        assert x.is_cuda, "FusedAdaLN requires CUDA tensors"
+        B, T, H, W, D = x.shape
+        x_flat, scale_flat, shift_flat = _flat(x, D), _flat(scale, D), _flat(shift, D)
+        N, M, HW = x_flat.shape[0], scale_flat.shape[0], H * W
+        assert N == M * HW, f"shape mismatch: N={N}, M={M}, HW={HW}"
+        y, mean, rstd = ops.adaln_fwd(x_flat, scale_flat, shift_flat, eps, HW)
+        ctx.save_for_backward(x_flat, scale_flat, mean, rstd)
+        ctx.x_shape, ctx.scale_shape, ctx.HW = (B, T, H, W, D), scale.shape, HW
+        ctx.dtypes = (x.dtype, scale.dtype, shift.dtype)
+        return y.view(B, T, H, W, D).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_flat, scale_flat, mean, rstd = ctx.saved_tensors
+        B, T, H, W, D = ctx.x_shape
+        dx, dscale, dshift = ops.adaln_bwd(_flat(dy, D), x_flat, scale_flat, mean, rstd, ctx.HW)
+        xd, sd, bd = ctx.dtypes
+        return (dx.view(B, T, H, W, D).to(xd), dscale.view(ctx.scale_shape).to(sd),
+                dshift.view(ctx.scale_shape).to(bd), None)
+
+
+def fused_adaln(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, eps: float) -> torch.Tensor:
+    return FusedAdaLN.apply(x, scale, shift, eps)
+
+
+class FusedGatedAdd(torch.autograd.Function):
+    """``out = x + gate * y``; backward ``dx = dout``, ``dy = gate * dout``,
+    ``dgate = sum_{h,w}(dout * y)``."""
+
+    @staticmethod
+    def forward(ctx, x, gate, y):
+        assert x.is_cuda, "FusedGatedAdd requires CUDA tensors"
+        assert x.shape == y.shape, f"x {x.shape} != y {y.shape}"
+        B, T, H, W, D = x.shape
+        x_flat, y_flat, gate_flat = _flat(x, D), _flat(y, D), _flat(gate, D)
+        N, M, HW = x_flat.shape[0], gate_flat.shape[0], H * W
+        assert N == M * HW, f"shape mismatch: N={N}, M={M}, HW={HW}"
+        out = ops.gated_add_fwd(x_flat, gate_flat, y_flat, HW)
+        ctx.save_for_backward(y_flat, gate_flat)
+        ctx.shape, ctx.gate_shape, ctx.HW = (B, T, H, W, D), gate.shape, HW
+        ctx.dtypes = (gate.dtype, y.dtype)
+        return out.view(B, T, H, W, D).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dout):
+        y_flat, gate_flat = ctx.saved_tensors
+        B, T, H, W, D = ctx.shape
+        dy, dgate = ops.gated_add_bwd(_flat(dout, D), y_flat, gate_flat, ctx.HW)
+        gd, yd = ctx.dtypes
+        return dout, dgate.view(ctx.gate_shape).to(gd), dy.view(B, T, H, W, D).to(yd)
+
+
+def fused_gated_add(x: torch.Tensor, gate: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    return FusedGatedAdd.apply(x, gate, y)

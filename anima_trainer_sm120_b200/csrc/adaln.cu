@@ -1,0 +1,480 @@
+// Fused AdaLN (LayerNorm without affine, then *(1+scale)+shift) and the gated
+// residual x + gate*y, forward and backward, for bf16 activations.
+//
+// Replaces anima-trainer's five Triton kernels in adaln_kernel.py:
+//   _fwd_kernel (:34-68), _bwd_dx_kernel (:71-103), _bwd_dsdb_kernel (:106-154),
+//   _gated_add_fwd_kernel (:272-295), _gated_add_bwd_dgate_kernel (:298-329).
+// All four kernels here are HBM-bound; each tensor is read or written once with
+// 16-byte streaming accesses:
+//   adaln_fwd      4 B/elem (+ 8 B/row of saved statistics)
+//   adaln_bwd      6 B/elem: dx AND the dscale/dshift partial sums come from one
+//                  pass over dy and x (the reference makes two passes)
+//   gated_add_fwd  6 B/elem
+//   gated_add_bwd  6 B/elem: dy and the dgate partial sums from one pass
+// The reductions over the hw rows of a sample are two-stage (per-block partials in
+// caller-provided scratch, then a fixed-order sum), so results are bit-reproducible;
+// the reference uses fp32 atomics.
+#include "common.cuh"
+
+namespace anima {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kRowsPerIter = 4;
+
+// ------------------------------------------------------------------ forward
+// One warp per row; lane l owns the 16-byte chunks l, l+32, ... of the row.
+template <int NCH>
+__global__ void __launch_bounds__(kThreads)
+adaln_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ scale,
+                 const __nv_bfloat16* __restrict__ shift, float eps, int64_t rows, int64_t hw,
+                 int d, __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out,
+                 float* __restrict__ rstd_out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int64_t bt = row / hw;
+  const __nv_bfloat16* xr = x + row * d;
+
+  float v[NCH][8];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) {
+    const int col = (i * 32 + lane) * 8;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (col < d) raw = ldg_stream16(xr + col);
+    unpack8(raw, v[i]);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) sum += v[i][k];
+  }
+  const float mean = warp_sum(sum) / static_cast<float>(d);
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) {
+    const bool ok = (i * 32 + lane) * 8 < d;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      v[i][k] = ok ? v[i][k] - mean : 0.f;  // padded tail must not add mean^2 (adaln_kernel.py:55-57)
+      sq += v[i][k] * v[i][k];
+    }
+  }
+  const float var = warp_sum(sq) / static_cast<float>(d);
+  const float rstd = 1.0f / sqrtf(var + eps);
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) {
+    const int col = (i * 32 + lane) * 8;
+    if (col < d) {
+      float s[8], b[8], o[8];
+      unpack8(*reinterpret_cast<const uint4*>(scale + bt * d + col), s);
+      unpack8(*reinterpret_cast<const uint4*>(shift + bt * d + col), b);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) o[k] = v[i][k] * rstd * (1.0f + s[k]) + b[k];
+      stg_stream16(y + row * d + col, pack8(o));
+    }
+  }
+  if (lane == 0) {
+    mean_out[row] = mean;
+    rstd_out[row] = rstd;
+  }
+}
+
+// ------------------------------------------------------------------ backward
+// Work split shared by adaln_bwd and gated_add_bwd: the hw rows of every sample
+// are cut into `chunks` contiguous pieces, one CTA each; thread t owns the
+// 16-byte column chunks t, t+256, ... and carries their partial sums in registers.
+struct RowSplit {
+  int chunks;          // CTAs per sample
+  int rows_per_chunk;  // multiple of kRowsPerIter
+};
+
+RowSplit make_split(int64_t bt, int64_t hw) {
+  const int64_t target = 2LL * sm_count();  // two resident CTAs per SM
+  int64_t chunks = std::max<int64_t>(1, ceil_div(target, std::max<int64_t>(bt, 1)));
+  int64_t rpc = ceil_div(ceil_div(hw, chunks), kRowsPerIter) * kRowsPerIter;
+  chunks = ceil_div(hw, rpc);
+  return {static_cast<int>(chunks), static_cast<int>(rpc)};
+}
+
+template <int NCH>
+__global__ void __launch_bounds__(kThreads)
+adaln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                 const __nv_bfloat16* __restrict__ scale, const float* __restrict__ mean,
+                 const float* __restrict__ rstd, int64_t hw, int d, int rows_per_chunk,
+                 __nv_bfloat16* __restrict__ dx, float* __restrict__ partial) {
+  constexpr int R = kRowsPerIter;
+  __shared__ float red[2][kThreads / 32][2 * R];
+
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const int64_t bt = blockIdx.y;
+  const int64_t row_begin = bt * hw + static_cast<int64_t>(blockIdx.x) * rows_per_chunk;
+  const int64_t row_end = min(bt * hw + hw, row_begin + rows_per_chunk);
+  const float inv_d = 1.0f / static_cast<float>(d);
+
+  float one_plus_s[NCH][8], ds[NCH][8], db[NCH][8];
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int col = (j * kThreads + t) * 8;
+    float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (col < d) unpack8(*reinterpret_cast<const uint4*>(scale + bt * d + col), s);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      one_plus_s[j][k] = 1.0f + s[k];
+      ds[j][k] = 0.f;
+      db[j][k] = 0.f;
+    }
+  }
+
+  int buf = 0;
+  for (int64_t r0 = row_begin; r0 < row_end; r0 += R) {
+    float g[R][NCH][8], xh[R][NCH][8];  // dy then dxhat; x then xhat
+    float mu[R], rs[R];
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      const int64_t row = r0 + k;
+      const bool row_ok = row < row_end;
+      mu[k] = row_ok ? mean[row] : 0.f;
+      rs[k] = row_ok ? rstd[row] : 0.f;
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const int col = (j * kThreads + t) * 8;
+        uint4 a = make_uint4(0u, 0u, 0u, 0u), b = a;
+        if (row_ok && col < d) {
+          a = ldg_stream16(dy + row * d + col);
+          b = ldg_stream16(x + row * d + col);
+        }
+        unpack8(a, g[k][j]);
+        unpack8(b, xh[k][j]);
+      }
+    }
+    float part[2 * R];
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      float p1 = 0.f, p2 = 0.f;
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const bool ok = (j * kThreads + t) * 8 < d;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float xhat = ok ? (xh[k][j][e] - mu[k]) * rs[k] : 0.f;
+          const float dyv = g[k][j][e];
+          ds[j][e] += dyv * xhat;
+          db[j][e] += dyv;
+          const float dxhat = dyv * one_plus_s[j][e];
+          xh[k][j][e] = xhat;
+          g[k][j][e] = dxhat;
+          p1 += dxhat;
+          p2 += dxhat * xhat;
+        }
+      }
+      part[2 * k] = warp_sum(p1);
+      part[2 * k + 1] = warp_sum(p2);
+    }
+    if (lane == 0) {
+#pragma unroll
+      for (int q = 0; q < 2 * R; ++q) red[buf][warp][q] = part[q];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+      for (int w = 0; w < kThreads / 32; ++w) {
+        c1 += red[buf][w][2 * k];
+        c2 += red[buf][w][2 * k + 1];
+      }
+      c1 *= inv_d;
+      c2 *= inv_d;
+      const int64_t row = r0 + k;
+      if (row < row_end) {
+#pragma unroll
+        for (int j = 0; j < NCH; ++j) {
+          const int col = (j * kThreads + t) * 8;
+          if (col < d) {
+            float o[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = rs[k] * (g[k][j][e] - c1 - xh[k][j][e] * c2);
+            stg_stream16(dx + row * d + col, pack8(o));
+          }
+        }
+      }
+    }
+    buf ^= 1;
+  }
+
+  // partial[bt][chunk][0] = dscale sums, [1] = dshift sums; fp32 [d] each.
+  float* out = partial + ((bt * gridDim.x + blockIdx.x) * 2) * static_cast<int64_t>(d);
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int col = (j * kThreads + t) * 8;
+    if (col < d) {
+      *reinterpret_cast<float4*>(out + col) = make_float4(ds[j][0], ds[j][1], ds[j][2], ds[j][3]);
+      *reinterpret_cast<float4*>(out + col + 4) = make_float4(ds[j][4], ds[j][5], ds[j][6], ds[j][7]);
+      *reinterpret_cast<float4*>(out + d + col) = make_float4(db[j][0], db[j][1], db[j][2], db[j][3]);
+      *reinterpret_cast<float4*>(out + d + col + 4) = make_float4(db[j][4], db[j][5], db[j][6], db[j][7]);
+    }
+  }
+}
+
+// out_k[bt][c] = bf16( sum over chunks (ascending) of partial[bt][chunk][k][c] ), k < nout.
+__global__ void finalize_partials_kernel(const float* __restrict__ partial, int64_t bt_count, int chunks,
+                                         int nout, int d, __nv_bfloat16* __restrict__ out0,
+                                         __nv_bfloat16* __restrict__ out1) {
+  const int64_t total = bt_count * nout * d;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % d);
+    const int k = static_cast<int>((i / d) % nout);
+    const int64_t bt = i / (static_cast<int64_t>(d) * nout);
+    float acc = 0.f;
+    for (int ch = 0; ch < chunks; ++ch)
+      acc += partial[((bt * chunks + ch) * nout + k) * static_cast<int64_t>(d) + c];
+    (k == 0 ? out0 : out1)[bt * d + c] = __float2bfloat16_rn(acc);
+  }
+}
+
+// ------------------------------------------------------------------ gated residual
+__global__ void __launch_bounds__(kThreads)
+gated_add_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate,
+                     const __nv_bfloat16* __restrict__ y, int64_t rows, int64_t hw, int d8,
+                     __nv_bfloat16* __restrict__ out) {
+  constexpr int U = 4;
+  const int64_t total = rows * d8;  // 16-byte chunks
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+  for (int64_t base = blockIdx.x * static_cast<int64_t>(kThreads) + threadIdx.x; base < total;
+       base += stride * U) {
+    uint4 xa[U], ya[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = base + u * stride;
+      if (i < total) {
+        xa[u] = ldg_stream16(x + i * 8);
+        ya[u] = ldg_stream16(y + i * 8);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = base + u * stride;
+      if (i < total) {
+        const int64_t row = i / d8;
+        const int c8 = static_cast<int>(i - row * d8);
+        float xf[8], yf[8], gf[8], o[8];
+        unpack8(xa[u], xf);
+        unpack8(ya[u], yf);
+        unpack8(*reinterpret_cast<const uint4*>(gate + (row / hw) * (d8 * 8LL) + c8 * 8), gf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = xf[e] + gf[e] * yf[e];
+        stg_stream16(out + i * 8, pack8(o));
+      }
+    }
+  }
+}
+
+template <int NCH>
+__global__ void __launch_bounds__(kThreads)
+gated_add_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ y,
+                     const __nv_bfloat16* __restrict__ gate, int64_t hw, int d, int rows_per_chunk,
+                     __nv_bfloat16* __restrict__ dy, float* __restrict__ partial) {
+  constexpr int R = kRowsPerIter;
+  const int t = threadIdx.x;
+  const int64_t bt = blockIdx.y;
+  const int64_t row_begin = bt * hw + static_cast<int64_t>(blockIdx.x) * rows_per_chunk;
+  const int64_t row_end = min(bt * hw + hw, row_begin + rows_per_chunk);
+
+  float gt[NCH][8], dg[NCH][8];
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int col = (j * kThreads + t) * 8;
+    float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (col < d) unpack8(*reinterpret_cast<const uint4*>(gate + bt * d + col), s);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      gt[j][k] = s[k];
+      dg[j][k] = 0.f;
+    }
+  }
+  for (int64_t r0 = row_begin; r0 < row_end; r0 += R) {
+    uint4 a[R][NCH], b[R][NCH];
+#pragma unroll
+    for (int k = 0; k < R; ++k)
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const int col = (j * kThreads + t) * 8;
+        a[k][j] = make_uint4(0u, 0u, 0u, 0u);
+        b[k][j] = a[k][j];
+        if (r0 + k < row_end && col < d) {
+          a[k][j] = ldg_stream16(dout + (r0 + k) * d + col);
+          b[k][j] = ldg_stream16(y + (r0 + k) * d + col);
+        }
+      }
+#pragma unroll
+    for (int k = 0; k < R; ++k)
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const int col = (j * kThreads + t) * 8;
+        float df[8], yf[8], o[8];
+        unpack8(a[k][j], df);
+        unpack8(b[k][j], yf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          dg[j][e] += df[e] * yf[e];
+          o[e] = gt[j][e] * df[e];
+        }
+        if (r0 + k < row_end && col < d) stg_stream16(dy + (r0 + k) * d + col, pack8(o));
+      }
+  }
+  float* out = partial + (bt * gridDim.x + blockIdx.x) * static_cast<int64_t>(d);
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int col = (j * kThreads + t) * 8;
+    if (col < d) {
+      *reinterpret_cast<float4*>(out + col) = make_float4(dg[j][0], dg[j][1], dg[j][2], dg[j][3]);
+      *reinterpret_cast<float4*>(out + col + 4) = make_float4(dg[j][4], dg[j][5], dg[j][6], dg[j][7]);
+    }
+  }
+}
+
+int check_rows(const char* who, int64_t rows, int64_t hw, int64_t d, int64_t max_d) {
+  ANIMA_REQUIRE(rows >= 0 && hw > 0 && d > 0, ANIMA_E_ARG, "%s: bad sizes rows=%lld hw=%lld d=%lld", who,
+                (long long)rows, (long long)hw, (long long)d);
+  ANIMA_REQUIRE(rows % hw == 0, ANIMA_E_SHAPE, "%s: rows=%lld is not a multiple of hw=%lld", who,
+                (long long)rows, (long long)hw);
+  ANIMA_REQUIRE(d % 8 == 0, ANIMA_E_SHAPE, "%s: d=%lld must be a multiple of 8", who, (long long)d);
+  ANIMA_REQUIRE(d <= max_d, ANIMA_E_TOO_LARGE, "%s: d=%lld exceeds the supported maximum %lld", who,
+                (long long)d, (long long)max_d);
+  return ANIMA_OK;
+}
+
+}  // namespace
+}  // namespace anima
+
+using namespace anima;
+
+extern "C" int anima_adaln_fwd(const void* x, const void* scale, const void* shift, float eps,
+                               int64_t rows, int64_t hw, int64_t d, void* y, float* mean, float* rstd,
+                               void* stream) {
+  ANIMA_REQUIRE(x && scale && shift && y && mean && rstd, ANIMA_E_ARG, "adaln_fwd: null pointer");
+  if (int rc = check_rows("adaln_fwd", rows, hw, d, 4096)) return rc;
+  ANIMA_REQUIRE(aligned16(x) && aligned16(scale) && aligned16(shift) && aligned16(y), ANIMA_E_ALIGN,
+                "adaln_fwd: tensors must be 16-byte aligned");
+  if (rows == 0) return ANIMA_OK;
+  const auto* xp = static_cast<const __nv_bfloat16*>(x);
+  const auto* sp = static_cast<const __nv_bfloat16*>(scale);
+  const auto* bp = static_cast<const __nv_bfloat16*>(shift);
+  auto* yp = static_cast<__nv_bfloat16*>(y);
+  const unsigned grid = static_cast<unsigned>(ceil_div(rows, kThreads / 32));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int di = static_cast<int>(d);
+#define ANIMA_LAUNCH_FWD(N) \
+  adaln_fwd_kernel<N><<<grid, kThreads, 0, s>>>(xp, sp, bp, eps, rows, hw, di, yp, mean, rstd)
+  if (d <= 256) ANIMA_LAUNCH_FWD(1);
+  else if (d <= 512) ANIMA_LAUNCH_FWD(2);
+  else if (d <= 1024) ANIMA_LAUNCH_FWD(4);
+  else if (d <= 2048) ANIMA_LAUNCH_FWD(8);
+  else ANIMA_LAUNCH_FWD(16);
+#undef ANIMA_LAUNCH_FWD
+  ANIMA_CHECK_LAUNCH("adaln_fwd");
+  return ANIMA_OK;
+}
+
+extern "C" int64_t anima_adaln_bwd_workspace_bytes(int64_t rows, int64_t hw, int64_t d) {
+  if (rows < 0 || hw <= 0 || d <= 0 || rows % hw) return ANIMA_E_SHAPE;
+  const RowSplit sp = make_split(rows / hw, hw);
+  return (rows / hw) * sp.chunks * 2 * d * static_cast<int64_t>(sizeof(float));
+}
+
+extern "C" int anima_adaln_bwd(const void* dy, const void* x, const void* scale, const float* mean,
+                               const float* rstd, int64_t rows, int64_t hw, int64_t d, void* dx,
+                               void* dscale, void* dshift, void* workspace, int64_t workspace_bytes,
+                               void* stream) {
+  ANIMA_REQUIRE(dy && x && scale && mean && rstd && dx && dscale && dshift, ANIMA_E_ARG,
+                "adaln_bwd: null pointer");
+  if (int rc = check_rows("adaln_bwd", rows, hw, d, 4096)) return rc;
+  ANIMA_REQUIRE(aligned16(dy) && aligned16(x) && aligned16(scale) && aligned16(dx), ANIMA_E_ALIGN,
+                "adaln_bwd: tensors must be 16-byte aligned");
+  if (rows == 0) return ANIMA_OK;
+  const int64_t need = anima_adaln_bwd_workspace_bytes(rows, hw, d);
+  ANIMA_REQUIRE(workspace && aligned16(workspace) && workspace_bytes >= need, ANIMA_E_WORKSPACE,
+                "adaln_bwd: workspace of %lld bytes (16-byte aligned) required, got %lld", (long long)need,
+                (long long)workspace_bytes);
+  const int64_t bt = rows / hw;
+  ANIMA_REQUIRE(bt <= 65535, ANIMA_E_TOO_LARGE, "adaln_bwd: rows/hw=%lld exceeds 65535", (long long)bt);
+  const RowSplit sp = make_split(bt, hw);
+  const dim3 grid(sp.chunks, static_cast<unsigned>(bt));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* ws = static_cast<float*>(workspace);
+  const auto* dyp = static_cast<const __nv_bfloat16*>(dy);
+  const auto* xp = static_cast<const __nv_bfloat16*>(x);
+  const auto* scp = static_cast<const __nv_bfloat16*>(scale);
+  auto* dxp = static_cast<__nv_bfloat16*>(dx);
+  if (d <= 2048)
+    adaln_bwd_kernel<1><<<grid, kThreads, 0, s>>>(dyp, xp, scp, mean, rstd, hw, (int)d,
+                                                  sp.rows_per_chunk, dxp, ws);
+  else
+    adaln_bwd_kernel<2><<<grid, kThreads, 0, s>>>(dyp, xp, scp, mean, rstd, hw, (int)d,
+                                                  sp.rows_per_chunk, dxp, ws);
+  ANIMA_CHECK_LAUNCH("adaln_bwd");
+  const int64_t total = bt * 2 * d;
+  finalize_partials_kernel<<<static_cast<unsigned>(std::min<int64_t>(ceil_div(total, 256), 1024)), 256, 0, s>>>(
+      ws, bt, sp.chunks, 2, (int)d, static_cast<__nv_bfloat16*>(dscale),
+      static_cast<__nv_bfloat16*>(dshift));
+  ANIMA_CHECK_LAUNCH("adaln_bwd finalize");
+  return ANIMA_OK;
+}
+
+extern "C" int anima_gated_add_fwd(const void* x, const void* gate, const void* y, int64_t rows,
+                                   int64_t hw, int64_t d, void* out, void* stream) {
+  ANIMA_REQUIRE(x && gate && y && out, ANIMA_E_ARG, "gated_add_fwd: null pointer");
+  if (int rc = check_rows("gated_add_fwd", rows, hw, d, INT32_MAX / 2)) return rc;
+  ANIMA_REQUIRE(aligned16(x) && aligned16(gate) && aligned16(y) && aligned16(out), ANIMA_E_ALIGN,
+                "gated_add_fwd: tensors must be 16-byte aligned");
+  if (rows == 0) return ANIMA_OK;
+  const int64_t total = rows * (d / 8);
+  const unsigned grid =
+      static_cast<unsigned>(std::min<int64_t>(ceil_div(total, kThreads * 4), 8LL * sm_count()));
+  gated_add_fwd_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gate),
+      static_cast<const __nv_bfloat16*>(y), rows, hw, static_cast<int>(d / 8),
+      static_cast<__nv_bfloat16*>(out));
+  ANIMA_CHECK_LAUNCH("gated_add_fwd");
+  return ANIMA_OK;
+}
+
+extern "C" int64_t anima_gated_add_bwd_workspace_bytes(int64_t rows, int64_t hw, int64_t d) {
+  if (rows < 0 || hw <= 0 || d <= 0 || rows % hw) return ANIMA_E_SHAPE;
+  const RowSplit sp = make_split(rows / hw, hw);
+  return (rows / hw) * sp.chunks * d * static_cast<int64_t>(sizeof(float));
+}
+
+extern "C" int anima_gated_add_bwd(const void* dout, const void* y, const void* gate, int64_t rows,
+                                   int64_t hw, int64_t d, void* dy, void* dgate, void* workspace,
+                                   int64_t workspace_bytes, void* stream) {
+  ANIMA_REQUIRE(dout && y && gate && dy && dgate, ANIMA_E_ARG, "gated_add_bwd: null pointer");
+  if (int rc = check_rows("gated_add_bwd", rows, hw, d, 4096)) return rc;
+  ANIMA_REQUIRE(aligned16(dout) && aligned16(y) && aligned16(gate) && aligned16(dy), ANIMA_E_ALIGN,
+                "gated_add_bwd: tensors must be 16-byte aligned");
+  if (rows == 0) return ANIMA_OK;
+  const int64_t need = anima_gated_add_bwd_workspace_bytes(rows, hw, d);
+  ANIMA_REQUIRE(workspace && aligned16(workspace) && workspace_bytes >= need, ANIMA_E_WORKSPACE,
+                "gated_add_bwd: workspace of %lld bytes (16-byte aligned) required, got %lld",
+                (long long)need, (long long)workspace_bytes);
+  const int64_t bt = rows / hw;
+  ANIMA_REQUIRE(bt <= 65535, ANIMA_E_TOO_LARGE, "gated_add_bwd: rows/hw=%lld exceeds 65535", (long long)bt);
+  const RowSplit sp = make_split(bt, hw);
+  const dim3 grid(sp.chunks, static_cast<unsigned>(bt));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* ws = static_cast<float*>(workspace);
+  const auto* dop = static_cast<const __nv_bfloat16*>(dout);
+  const auto* yp = static_cast<const __nv_bfloat16*>(y);
+  const auto* gp = static_cast<const __nv_bfloat16*>(gate);
+  auto* dyp = static_cast<__nv_bfloat16*>(dy);
+  if (d <= 2048)
+    gated_add_bwd_kernel<1><<<grid, kThreads, 0, s>>>(dop, yp, gp, hw, (int)d, sp.rows_per_chunk, dyp, ws);
+  else
+    gated_add_bwd_kernel<2><<<grid, kThreads, 0, s>>>(dop, yp, gp, hw, (int)d, sp.rows_per_chunk, dyp, ws);
+  ANIMA_CHECK_LAUNCH("gated_add_bwd");
+  const int64_t total = bt * d;
+  finalize_partials_kernel<<<static_cast<unsigned>(std::min<int64_t>(ceil_div(total, 256), 1024)), 256, 0, s>>>(
+      ws, bt, sp.chunks, 1, (int)d, static_cast<__nv_bfloat16*>(dgate), nullptr);
+  ANIMA_CHECK_LAUNCH("gated_add_bwd finalize");
+  return ANIMA_OK;
+}

@@ -1,0 +1,196 @@
+// Tile kernel shared by the MXFP8 quantiser and the fused LoKr merge + quantise:
+// one CTA owns a 128 x 128 tile whose bf16 values come from a Loader functor
+// (plain global loads, or W + alpha * kron(w1, w2) built on the fly).
+#pragma once
+
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace anima {
+namespace mxq {
+
+constexpr int kTile = 128;      // tile edge in elements
+constexpr int kThreads = 256;
+constexpr float kAmaxFloor = 1e-30f;  // mxfp8_gemm.py:114
+
+struct QuantParams {
+  int64_t rows, cols;
+  uint8_t* codes_row;
+  uint8_t* scales_row;
+  uint8_t* codes_colT;
+  uint8_t* scales_col;
+  int tiled;  // scale layout
+};
+
+// e = ceil(log2(amax / 448)) clamped to [-127, 127], for amax >= 1e-30 (normal fp32).
+__device__ __forceinline__ int mx_exponent(float amax) {
+  const uint32_t u = __float_as_uint(amax);
+  const int E = static_cast<int>(u >> 23) - 127;
+  const uint32_t mant = u & 0x7fffffu;
+  if (E == 128) return 127;  // inf / nan: log2 -> inf, clamped
+  int e = E - 8 + (mant > 0x600000u ? 1 : 0);
+  return max(-127, min(127, e));
+}
+
+// 2^-e as fp32 for e in [-127, 127]; 2^-127 is the subnormal 0x00400000.
+__device__ __forceinline__ float mx_inv_scale(int e) {
+  return e >= 127 ? __uint_as_float(0x00400000u) : __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+}
+
+__device__ __forceinline__ uint32_t e4m3x2(float lo, float hi) {
+  return static_cast<uint32_t>(
+      __nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
+}
+
+__device__ __forceinline__ int tiled_offset(int r, int j) {
+  return (r & 31) * 16 + (r >> 5) * 4 + j;
+}
+
+// Loader: __device__ uint4 operator()(int64_t row, int64_t col) const — the 8 bf16
+// values at (row, col .. col+7), both in range.
+template <bool ROW, bool COL, class Loader>
+__global__ void __launch_bounds__(kThreads) mx_quantize_kernel(const QuantParams p, const Loader load) {
+  __shared__ uint4 tile[COL ? kTile * 16 : 1];  // 128 rows x 256 B
+  __shared__ __align__(16) uint8_t sc_row[ROW ? 512 : 16];
+  __shared__ __align__(16) uint8_t sc_col[COL ? 512 : 16];
+
+  const int t = threadIdx.x;
+  const int64_t tile_r = static_cast<int64_t>(blockIdx.y) * kTile;
+  const int64_t tile_c = static_cast<int64_t>(blockIdx.x) * kTile;
+  const int c16 = t & 15;  // 16-byte chunk (8 elements) within the tile row
+  const int r0 = t >> 4;   // 0..15
+  const int64_t col = tile_c + c16 * 8;
+  const bool col_ok = col < p.cols;  // cols % 32 == 0 or % 8 == 0: a chunk is all in or all out
+
+  if (ROW) {
+    // Padding entries of a partial tile must be 0 in the tiled layout.
+    reinterpret_cast<uint16_t*>(sc_row)[t] = 0;
+  }
+  if (COL) reinterpret_cast<uint16_t*>(sc_col)[t] = 0;
+
+  uint4 raw[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int64_t r = tile_r + r0 + 16 * i;
+    raw[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (col_ok && r < p.rows) raw[i] = load(r, col);
+  }
+  if (ROW || COL) __syncthreads();  // zero fill of sc_* visible before the byte stores
+
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r_in = r0 + 16 * i;
+    if (COL) tile[r_in * 16 + c16] = raw[i];
+    if (ROW) {
+      float f[8];
+      unpack8(raw[i], f);
+      float amax = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(f[k]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      amax = fmaxf(amax, kAmaxFloor);
+      const int e = mx_exponent(amax);
+      const float inv = mx_inv_scale(e);
+      uint2 codes;
+      codes.x = e4m3x2(f[0] * inv, f[1] * inv) | (e4m3x2(f[2] * inv, f[3] * inv) << 16);
+      codes.y = e4m3x2(f[4] * inv, f[5] * inv) | (e4m3x2(f[6] * inv, f[7] * inv) << 16);
+      const int64_t r = tile_r + r_in;
+      if (col_ok && r < p.rows) {
+        *reinterpret_cast<uint2*>(p.codes_row + r * p.cols + col) = codes;
+        if ((c16 & 3) == 0) {
+          const int j = c16 >> 2;
+          sc_row[p.tiled ? tiled_offset(r_in, j) : r_in * 4 + j] = static_cast<uint8_t>(e + 127);
+        }
+      }
+    }
+  }
+
+  if (COL) {
+    __syncthreads();
+    const int cp = t & 63;  // column pair
+    const int g = t >> 6;   // 32-row group within the tile
+    const uint32_t* tile32 = reinterpret_cast<const uint32_t*>(tile);
+    float amax0 = 0.f, amax1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const uint32_t w = tile32[(32 * g + i) * 64 + cp];
+      const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+      amax0 = fmaxf(amax0, fabsf(v.x));
+      amax1 = fmaxf(amax1, fabsf(v.y));
+    }
+    const int e0 = mx_exponent(fmaxf(amax0, kAmaxFloor));
+    const int e1 = mx_exponent(fmaxf(amax1, kAmaxFloor));
+    const float inv0 = mx_inv_scale(e0), inv1 = mx_inv_scale(e1);
+    uint32_t w0[8], w1[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      float a[4], b[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t w = tile32[(32 * g + 4 * q + k) * 64 + cp];
+        const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+        a[k] = v.x * inv0;
+        b[k] = v.y * inv1;
+      }
+      w0[q] = e4m3x2(a[0], a[1]) | (e4m3x2(a[2], a[3]) << 16);
+      w1[q] = e4m3x2(b[0], b[1]) | (e4m3x2(b[2], b[3]) << 16);
+    }
+    const int64_t c0 = tile_c + 2 * cp;
+    const int64_t rg = tile_r + 32 * g;
+    if (c0 < p.cols && rg < p.rows) {  // rows % 32 == 0: the group is all in or all out
+      uint8_t* d0 = p.codes_colT + c0 * p.rows + rg;
+      stg_stream16(d0, make_uint4(w0[0], w0[1], w0[2], w0[3]));
+      stg_stream16(d0 + 16, make_uint4(w0[4], w0[5], w0[6], w0[7]));
+      sc_col[p.tiled ? tiled_offset(2 * cp, g) : (2 * cp) * 4 + g] = static_cast<uint8_t>(e0 + 127);
+      if (c0 + 1 < p.cols) {
+        uint8_t* d1 = d0 + p.rows;
+        stg_stream16(d1, make_uint4(w1[0], w1[1], w1[2], w1[3]));
+        stg_stream16(d1 + 16, make_uint4(w1[4], w1[5], w1[6], w1[7]));
+        sc_col[p.tiled ? tiled_offset(2 * cp + 1, g) : (2 * cp + 1) * 4 + g] =
+            static_cast<uint8_t>(e1 + 127);
+      }
+    }
+  }
+
+  __syncthreads();
+  // Scale bytes of the tile: 128 "rows" x 4 k-blocks, staged in shared memory.
+  if (ROW) {
+    const int64_t kb = p.cols / 32;
+    if (p.tiled) {
+      if (t < 128) {
+        const int64_t chunk = blockIdx.y * ceil_div(kb, 4) + blockIdx.x;
+        reinterpret_cast<uint32_t*>(p.scales_row + chunk * 512)[t] =
+            reinterpret_cast<const uint32_t*>(sc_row)[t];
+      }
+    } else {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int idx = t + h * kThreads;
+        const int64_t r = tile_r + (idx >> 2), k = tile_c / 32 + (idx & 3);
+        if (r < p.rows && k < kb) p.scales_row[r * kb + k] = sc_row[idx];
+      }
+    }
+  }
+  if (COL) {
+    const int64_t kb = p.rows / 32;
+    if (p.tiled) {
+      if (t < 128) {
+        const int64_t chunk = blockIdx.x * ceil_div(kb, 4) + blockIdx.y;
+        reinterpret_cast<uint32_t*>(p.scales_col + chunk * 512)[t] =
+            reinterpret_cast<const uint32_t*>(sc_col)[t];
+      }
+    } else {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int idx = t + h * kThreads;
+        const int64_t c = tile_c + (idx >> 2), k = tile_r / 32 + (idx & 3);
+        if (c < p.cols && k < kb) p.scales_col[c * kb + k] = sc_col[idx];
+      }
+    }
+  }
+}
+
+}  // namespace mxq
+}  // namespace anima

@@ -1,0 +1,261 @@
+"""Quantised linears with the call surface of anima-trainer's ``fp8_quant.py``, on the
+sm_100a MXFP8 kernels (no Transformer Engine, no cuBLASLt).
+
+Mirrored interface (anima-trainer ``src/anima_trainer/fp8_quant.py``):
+``MXFP8FrozenLinear`` (:118) / ``mxfp8_frozen_linear`` (:180), ``MXFP8LoKrLinear`` (:190) /
+``mxfp8_lokr_linear`` (:267), ``FP8LoKrLinear`` (:460) / ``fp8_lokr_linear`` (:514),
+``FP8FrozenLinear`` (:519) / ``fp8_frozen_linear`` (:573), ``is_quantized`` (:276),
+``quantize_frozen_linears`` (:313), ``collect_lokr_wrapped_linears`` (:408),
+``quantize_tlokr_base_weights`` (:583).
+
+What differs from the reference, by design of the B200 path:
+* every GEMM — forward, dgrad AND wgrad — runs in MXFP8 on tcgen05. The reference keeps the
+  MXFP8 backward in bf16 because cuBLAS lacks those layouts on sm_120 (:196-205) and uses TE
+  block-FP8 for its production ``fp8`` mode; here ``FP8LoKrLinear`` is the same three-GEMM
+  contract in MXFP8.
+* a pre-quantised weight is a :class:`QuantWeight` (row-wise operand for forward, column-wise
+  operand for dgrad, both made from one read of W) instead of a TE tensor object.
+* :class:`LoKrLinearFused` goes further than the reference API: it takes W, w1, w2 directly,
+  never materialises kron(w1, w2) in HBM, and returns the adapter gradients from the wgrad.
+"""
+from __future__ import annotations
+
+import types
+from typing import Iterable, NamedTuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import ops
+from ._lib import SCALES_TILED
+
+BF16 = torch.bfloat16
+MXFP8_BLOCK = 32
+
+
+class QuantWeight(NamedTuple):
+    """MXFP8 forms of a weight ``W [N, K]``: ``row`` quantised along K (forward operand),
+    ``col`` quantised along N and stored ``[K, N]`` (dgrad operand)."""
+
+    row: ops.MXOperand
+    col: ops.MXOperand | None
+
+
+def quantize_weight(W: torch.Tensor, *, with_dgrad: bool = True) -> QuantWeight:
+    W = W.detach()
+    if W.dtype != BF16:
+        W = W.to(BF16)
+    row, col = ops.mx_quantize(W.contiguous(), rowwise=True, colwise=with_dgrad, layout=SCALES_TILED)
+    return QuantWeight(row, col)
+
+
+def _flat2d(x: torch.Tensor) -> torch.Tensor:
+    x2 = x.reshape(-1, x.shape[-1])
+    return x2 if x2.dtype == BF16 else x2.to(BF16)
+
+
+def _bias_bf16(bias):
+    return None if bias is None else bias.detach().to(BF16).contiguous()
+
+
+class MXFP8FrozenLinear(torch.autograd.Function):
+    """``y = x @ W.T (+ bias)`` for a frozen, pre-quantised W (reference signature
+    ``apply(x, W_mx, W_bf16, bias)``). Forward: quantise x, MXFP8 GEMM. Backward: MXFP8 dgrad
+    against the column-wise operand when ``W_mx`` carries one, else the reference's bf16
+    ``grad_y @ W_bf16`` (:171)."""
+
+    @staticmethod
+    def forward(ctx, x, W_mx: QuantWeight, W_bf16, bias=None):
+        x2 = _flat2d(x)
+        x_row, _ = ops.mx_quantize(x2, rowwise=True)
+        y = ops.mx_gemm(x_row, W_mx.row, bias=_bias_bf16(bias))
+        ctx.W_mx, ctx.W_bf16, ctx.has_bias = W_mx, W_bf16, bias is not None
+        return y.reshape(*x.shape[:-1], W_bf16.shape[0]).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        gy2 = _flat2d(grad_y)
+        if ctx.W_mx.col is not None:
+            g_row, _ = ops.mx_quantize(gy2, rowwise=True)
+            gx2 = ops.mx_gemm(g_row, ctx.W_mx.col)
+        else:
+            gx2 = gy2 @ ctx.W_bf16.to(BF16)
+        grad_x = gx2.reshape(*grad_y.shape[:-1], ctx.W_bf16.shape[1]).to(grad_y.dtype)
+        grad_bias = grad_y.reshape(-1, grad_y.shape[-1]).sum(dim=0) if ctx.has_bias else None
+        return grad_x, None, None, grad_bias
+
+
+def mxfp8_frozen_linear(x, W_mx, W_bf16, bias=None):
+    return MXFP8FrozenLinear.apply(x, W_mx, W_bf16, bias)
+
+
+# T-LoKr's frozen base projection has the same contract (reference :519-580).
+FP8FrozenLinear = MXFP8FrozenLinear
+
+
+def fp8_frozen_linear(x, weight_q, weight_bf16, bias):
+    return MXFP8FrozenLinear.apply(x, weight_q, weight_bf16, bias)
+
+
+class MXFP8LoKrLinear(torch.autograd.Function):
+    """``y = x @ merged_W.T (+ bias)`` with merged_W quantised just in time (reference
+    signature ``apply(x, merged_W, bias)``, :224-264 / :480-511): forward, dgrad and wgrad are
+    MXFP8 GEMMs; x and merged_W are each read once to produce both of their operand forms."""
+
+    @staticmethod
+    def forward(ctx, x, merged_W, bias=None):
+        x2 = _flat2d(x)
+        need_w = ctx.needs_input_grad[1]
+        x_row, x_col = ops.mx_quantize(x2, rowwise=True, colwise=need_w)
+        w_row, w_col = ops.mx_quantize(merged_W.detach().to(BF16).contiguous(), rowwise=True, colwise=True)
+        y = ops.mx_gemm(x_row, w_row, bias=_bias_bf16(bias))
+        ctx.x_col, ctx.w_col = x_col, w_col
+        ctx.has_bias, ctx.w_dtype, ctx.in_features = bias is not None, merged_W.dtype, merged_W.shape[1]
+        return y.reshape(*x.shape[:-1], merged_W.shape[0]).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        gy2 = _flat2d(grad_y)
+        g_row, g_col = ops.mx_quantize(gy2, rowwise=True, colwise=ctx.x_col is not None)
+        grad_x = ops.mx_gemm(g_row, ctx.w_col).reshape(*grad_y.shape[:-1], ctx.in_features).to(grad_y.dtype)
+        grad_w = None
+        if ctx.x_col is not None:
+            grad_w = ops.mx_gemm(g_col, ctx.x_col).to(ctx.w_dtype)          # gy^T @ x
+        grad_bias = grad_y.reshape(-1, grad_y.shape[-1]).sum(dim=0) if ctx.has_bias else None
+        return grad_x, grad_w, grad_bias
+
+
+def mxfp8_lokr_linear(x, merged_W, bias=None):
+    return MXFP8LoKrLinear.apply(x, merged_W, bias)
+
+
+FP8LoKrLinear = MXFP8LoKrLinear
+
+
+def fp8_lokr_linear(x, merged_W, bias):
+    return MXFP8LoKrLinear.apply(x, merged_W, bias)
+
+
+class LoKrLinearFused(torch.autograd.Function):
+    """``y = x @ (W + alpha * kron(w1, w2)).T (+ bias)`` without ever writing the merged weight
+    or its gradient's Kronecker expansion to HBM as bf16 tensors of their own:
+
+    forward   one kernel builds merged = W + alpha*kron(w1, w2) and emits its row- and
+              column-wise MXFP8 operands; x is quantised (both forms) from one read; MXFP8 GEMM.
+    backward  grad_y quantised (both forms) from one read; MXFP8 dgrad; MXFP8 wgrad with fp32
+              output; one pass over dW gives dw1 and dw2 (the adjoint of torch.kron that the
+              reference obtains through autograd, lokr_patch.py:19-21).
+    """
+
+    @staticmethod
+    def forward(ctx, x, W, bias, w1, w2, alpha: float):
+        x2 = _flat2d(x)
+        train = ctx.needs_input_grad[3] or ctx.needs_input_grad[4]
+        x_row, x_col = ops.mx_quantize(x2, rowwise=True, colwise=train)
+        _, w_row, w_col = ops.lokr_merge_quantize(W.detach(), w1.detach(), w2.detach(), alpha, want_merged=False,
+                                                  rowwise=True, colwise=True)
+        y = ops.mx_gemm(x_row, w_row, bias=_bias_bf16(bias))
+        ctx.save_for_backward(w1, w2)
+        ctx.x_col, ctx.w_col, ctx.alpha = x_col, w_col, float(alpha)
+        ctx.has_bias, ctx.in_features = bias is not None, W.shape[1]
+        return y.reshape(*x.shape[:-1], W.shape[0]).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        w1, w2 = ctx.saved_tensors
+        gy2 = _flat2d(grad_y)
+        g_row, g_col = ops.mx_quantize(gy2, rowwise=True, colwise=ctx.x_col is not None)
+        grad_x = ops.mx_gemm(g_row, ctx.w_col).reshape(*grad_y.shape[:-1], ctx.in_features).to(grad_y.dtype)
+        g_w1 = g_w2 = None
+        if ctx.x_col is not None:
+            dw = ops.mx_gemm(g_col, ctx.x_col, out_dtype=torch.float32)
+            d1, d2 = ops.lokr_kron_backward(dw, w1.detach(), w2.detach(), ctx.alpha)
+            g_w1, g_w2 = d1.to(w1.dtype), d2.to(w2.dtype)
+        grad_bias = grad_y.reshape(-1, grad_y.shape[-1]).sum(dim=0) if ctx.has_bias else None
+        return grad_x, None, grad_bias, g_w1, g_w2, None
+
+
+def lokr_linear_fused(x, W, bias, w1, w2, alpha: float = 1.0):
+    return LoKrLinearFused.apply(x, W, bias, w1, w2, alpha)
+
+
+# ------------------------------------------------------------------------------ module walkers
+def is_quantized(mod: nn.Module) -> bool:
+    return getattr(mod, "_mxfp8_W", None) is not None
+
+
+def _mxfp8_linear_forward(self: nn.Linear, x: torch.Tensor) -> torch.Tensor:
+    """Forward bound onto a pre-quantised frozen ``nn.Linear`` (reference :284-310). A leading
+    size that is not a multiple of 32 takes the bf16 ``F.linear`` path, as in the reference."""
+    W_mx = getattr(self, "_mxfp8_W", None)
+    W_bf16 = getattr(self, "_mxfp8_W_bf16", None)
+    if W_mx is None or W_bf16 is None:
+        return F.linear(x, self.weight, self.bias)
+    if (x.numel() // x.shape[-1]) % MXFP8_BLOCK != 0:
+        return F.linear(x, W_bf16, self.bias)
+    return MXFP8FrozenLinear.apply(x, W_mx, W_bf16, self.bias)
+
+
+def quantize_frozen_linears(
+    dit: nn.Module,
+    skip: Iterable[nn.Module] = (),
+    min_size: int = 256 * 256,
+    skip_name_substrings: tuple[str, ...] = ("adaln_modulation", "t_embedder", "FinalLayer"),
+) -> int:
+    """Pre-quantise every frozen ``nn.Linear`` of ``dit`` and rebind its forward (reference
+    :313-405, same skip rules: explicit ``skip`` set, name substrings, trainable weights, fewer
+    than ``min_size`` elements, a dimension not divisible by 32). The MXFP8 copies are plain
+    attributes, never buffers, so they stay out of ``state_dict``. Idempotent; returns the count."""
+    skip_ids = {id(m) for m in skip}
+    for name, mod in dit.named_modules():
+        if isinstance(mod, nn.Linear) and any(s in name for s in skip_name_substrings):
+            skip_ids.add(id(mod))
+    count = 0
+    for mod in dit.modules():
+        if not isinstance(mod, nn.Linear) or id(mod) in skip_ids:
+            continue
+        if mod.weight.requires_grad or is_quantized(mod):
+            continue
+        out_dim, in_dim = mod.weight.shape
+        if out_dim * in_dim < min_size or out_dim % MXFP8_BLOCK or in_dim % MXFP8_BLOCK:
+            continue
+        W = mod.weight.detach().contiguous()
+        mod._mxfp8_W = quantize_weight(W)
+        mod._mxfp8_W_bf16 = W
+        mod.forward = types.MethodType(_mxfp8_linear_forward, mod)
+        count += 1
+    return count
+
+
+def collect_lokr_wrapped_linears(network: nn.Module) -> list[nn.Linear]:
+    """The ``nn.Linear`` instances wrapped by LoKr modules of ``network`` (reference :408-421):
+    any module exposing ``org_module[0]`` and ``lokr_w1``."""
+    wrapped = []
+    for mod in network.modules():
+        org = getattr(mod, "org_module", None)
+        if org is not None and hasattr(mod, "lokr_w1") and isinstance(org[0], nn.Linear):
+            wrapped.append(org[0])
+    return wrapped
+
+
+def quantize_tlokr_base_weights(network: nn.Module) -> int:
+    """Pre-quantise the frozen base Linear of every T-LoKr module once (reference :583-613).
+    MXFP8 needs both dimensions divisible by 32; a mismatch raises, as the reference does for
+    its 128-alignment."""
+    count = 0
+    for module in network.modules():
+        if not getattr(module, "_tlokr_enabled", False) or not hasattr(module, "org_module"):
+            continue
+        if getattr(module, "_tlokr_fp8_base_weight", None) is not None:
+            continue
+        inner = module.org_module[0]
+        if not isinstance(inner, nn.Linear):
+            raise TypeError(f"{getattr(module, 'lora_name', module)}: T-LoKr base must be nn.Linear")
+        out_dim, in_dim = inner.weight.shape
+        if out_dim % MXFP8_BLOCK or in_dim % MXFP8_BLOCK:
+            raise ValueError(f"{getattr(module, 'lora_name', module)}: base shape "
+                             f"{tuple(inner.weight.shape)} is not 32-aligned")
+        module._tlokr_fp8_base_weight = quantize_weight(inner.weight)
+        count += 1
+    return count

@@ -1,0 +1,268 @@
+"""Thin tensor-level wrappers, one per entry point of ``libanima_b200.so``.
+
+Each wrapper validates dtypes, allocates the outputs with ``torch.empty`` (the
+library itself never allocates), passes raw pointers plus the current CUDA
+stream, and raises on a negative status. Nothing here computes on the host.
+"""
+from __future__ import annotations
+
+from typing import NamedTuple
+
+import torch
+
+from . import _lib
+from ._lib import SCALES_PLAIN, SCALES_TILED, check, ptr
+
+BF16 = torch.bfloat16
+
+
+def _bf16_2d(x: torch.Tensor, name: str) -> torch.Tensor:
+    if x.dtype != BF16:
+        raise TypeError(f"{name} must be bfloat16, got {x.dtype}")
+    if x.dim() != 2:
+        raise ValueError(f"{name} must be 2-D, got shape {tuple(x.shape)}")
+    return x
+
+
+class MXOperand(NamedTuple):
+    """One K-major MXFP8 GEMM operand: e4m3 codes ``[rows, k]`` and its e8m0 scales."""
+
+    codes: torch.Tensor   # uint8 [rows, k]
+    scales: torch.Tensor  # uint8, PLAIN [rows, k/32] or TILED (flat, see anima_b200.h)
+    layout: int           # SCALES_PLAIN | SCALES_TILED
+
+    @property
+    def rows(self) -> int:
+        return self.codes.shape[0]
+
+    @property
+    def k(self) -> int:
+        return self.codes.shape[1]
+
+
+def scales_bytes(rows: int, k: int, layout: int) -> int:
+    return check(_lib.load().anima_mx_scales_bytes(rows, k, layout))
+
+
+def _alloc_scales(rows: int, k: int, layout: int, device) -> torch.Tensor:
+    if layout == SCALES_PLAIN:
+        return torch.empty((rows, k // 32), dtype=torch.uint8, device=device)
+    return torch.empty(scales_bytes(rows, k, layout), dtype=torch.uint8, device=device)
+
+
+def mx_quantize(
+    x: torch.Tensor, *, rowwise: bool = True, colwise: bool = False, layout: int = SCALES_TILED
+) -> tuple[MXOperand | None, MXOperand | None]:
+    """Quantise bf16 ``x [rows, cols]`` (last-dim stride 1) from one read.
+
+    Returns ``(row_op, col_op)``: ``row_op`` is x quantised along its columns
+    (``[rows, cols]``), ``col_op`` is x quantised along its rows and stored
+    transposed (``[cols, rows]``) — i.e. ``quantize_rowwise(x.t().contiguous())``.
+    """
+    _bf16_2d(x, "x")
+    dev = _lib.require_cuda(x)
+    if x.stride(1) != 1 and x.shape[1] > 1:
+        x = x.contiguous()
+    rows, cols = x.shape
+    if rowwise and cols % 32:
+        raise ValueError(f"rowwise quantisation needs cols % 32 == 0, got {cols}")
+    if colwise and rows % 32:
+        raise ValueError(f"columnwise quantisation needs rows % 32 == 0, got {rows}")
+    row_op = col_op = None
+    if rowwise:
+        row_op = MXOperand(torch.empty((rows, cols), dtype=torch.uint8, device=dev),
+                           _alloc_scales(rows, cols, layout, dev), layout)
+    if colwise:
+        col_op = MXOperand(torch.empty((cols, rows), dtype=torch.uint8, device=dev),
+                           _alloc_scales(cols, rows, layout, dev), layout)
+    with torch.cuda.device(dev):
+        check(_lib.load().anima_mx_quantize(
+            ptr(x), rows, cols, x.stride(0) if rows > 1 else cols,
+            ptr(row_op.codes) if row_op else None, ptr(row_op.scales) if row_op else None,
+            ptr(col_op.codes) if col_op else None, ptr(col_op.scales) if col_op else None,
+            layout, _lib.stream_ptr(dev)))
+    return row_op, col_op
+
+
+def mx_dequantize(op: MXOperand) -> torch.Tensor:
+    dev = _lib.require_cuda(op.codes, op.scales)
+    out = torch.empty(op.codes.shape, dtype=BF16, device=dev)
+    with torch.cuda.device(dev):
+        check(_lib.load().anima_mx_dequantize(ptr(op.codes), ptr(op.scales), op.rows, op.k, op.layout,
+                                              ptr(out), _lib.stream_ptr(dev)))
+    return out
+
+
+def mx_retile(op: MXOperand) -> MXOperand:
+    """PLAIN-scaled operand -> TILED-scaled operand (codes are shared, not copied)."""
+    if op.layout == SCALES_TILED:
+        return op
+    dev = _lib.require_cuda(op.codes, op.scales)
+    tiled = _alloc_scales(op.rows, op.k, SCALES_TILED, dev)
+    with torch.cuda.device(dev):
+        check(_lib.load().anima_mx_scales_retile(ptr(op.scales.contiguous()), op.rows, op.k, ptr(tiled),
+                                                 _lib.stream_ptr(dev)))
+    return MXOperand(op.codes, tiled, SCALES_TILED)
+
+
+def mx_gemm(a: MXOperand, b: MXOperand, *, bias: torch.Tensor | None = None,
+            out_dtype: torch.dtype = BF16, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``C[M,N] = A[M,K] . B[N,K]^T (+ bias)`` on the tcgen05 block-scaled tensor path."""
+    dev = _lib.require_cuda(a.codes, a.scales, b.codes, b.scales, bias)
+    if a.layout != SCALES_TILED or b.layout != SCALES_TILED:
+        raise ValueError("mx_gemm needs TILED scales; convert with mx_retile()")
+    if a.k != b.k:
+        raise ValueError(f"contraction sizes differ: A has K={a.k}, B has K={b.k}")
+    if not (a.codes.is_contiguous() and b.codes.is_contiguous()):
+        raise ValueError("mx_gemm operands must be contiguous (K-major)")
+    if out_dtype not in (BF16, torch.float32):
+        raise TypeError("out_dtype must be bfloat16 or float32")
+    if bias is not None and (bias.dtype != BF16 or bias.numel() != b.rows or not bias.is_contiguous()):
+        raise ValueError("bias must be contiguous bfloat16 of length N")
+    M, N, K = a.rows, b.rows, a.k
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=dev)
+    elif out.shape != (M, N) or out.dtype != out_dtype or out.stride(1) != 1:
+        raise ValueError("out has the wrong shape, dtype or layout")
+    with torch.cuda.device(dev):
+        check(_lib.load().anima_mx_gemm(
+            ptr(a.codes), ptr(a.scales), ptr(b.codes), ptr(b.scales), ptr(out), M, N, K, out.stride(0),
+            ptr(bias), 1 if out_dtype == torch.float32 else 0, ptr(_lib.status_word(dev)),
+            _lib.stream_ptr(dev)))
+    return out
+
+
+def _factor_flag(w1: torch.Tensor, w2: torch.Tensor) -> int:
+    if w1.dtype != w2.dtype or w1.dtype not in (BF16, torch.float32):
+        raise TypeError("LoKr factors must both be bfloat16 or both float32")
+    return 1 if w1.dtype == torch.float32 else 0
+
+
+def lokr_merge_quantize(
+    w: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, alpha: float, *, want_merged: bool = True,
+    rowwise: bool = False, colwise: bool = False, layout: int = SCALES_TILED,
+) -> tuple[torch.Tensor | None, MXOperand | None, MXOperand | None]:
+    """``merged = W + alpha * kron(w1, w2)`` and/or its MXFP8 forms, from one read of W."""
+    _bf16_2d(w, "W")
+    dev = _lib.require_cuda(w, w1, w2)
+    w, w1, w2 = w.contiguous(), w1.contiguous(), w2.contiguous()
+    N, K = w.shape
+    up, uq = w1.shape
+    if w2.shape != (N // up, K // uq) or N % up or K % uq:
+        raise ValueError(f"kron({tuple(w1.shape)}, {tuple(w2.shape)}) does not match W {tuple(w.shape)}")
+    merged = torch.empty_like(w) if want_merged else None
+    row_op = col_op = None
+    if rowwise:
+        row_op = MXOperand(torch.empty((N, K), dtype=torch.uint8, device=dev),
+                           _alloc_scales(N, K, layout, dev), layout)
+    if colwise:
+        col_op = MXOperand(torch.empty((K, N), dtype=torch.uint8, device=dev),
+                           _alloc_scales(K, N, layout, dev), layout)
+    with torch.cuda.device(dev):
+        check(_lib.load().anima_lokr_merge_quantize(
+            ptr(w), ptr(w1), ptr(w2), _factor_flag(w1, w2), float(alpha), N, K, up, uq, ptr(merged),
+            ptr(row_op.codes) if row_op else None, ptr(row_op.scales) if row_op else None,
+            ptr(col_op.codes) if col_op else None, ptr(col_op.scales) if col_op else None,
+            layout, _lib.stream_ptr(dev)))
+    return merged, row_op, col_op
+
+
+def lokr_kron_backward(dw: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, alpha: float
+                       ) -> tuple[torch.Tensor, torch.Tensor]:
+    """fp32 ``(dw1, dw2)`` from ``dW`` (bf16 or fp32) of the merged weight."""
+    dev = _lib.require_cuda(dw, w1, w2)
+    if dw.dtype not in (BF16, torch.float32) or dw.dim() != 2:
+        raise TypeError("dW must be a 2-D bfloat16 or float32 tensor")
+    dw, w1, w2 = dw.contiguous(), w1.contiguous(), w2.contiguous()
+    N, K = dw.shape
+    up, uq = w1.shape
+    lib = _lib.load()
+    nbytes = check(lib.anima_lokr_kron_backward_workspace_bytes(N, K, up, uq))
+    ws = _lib.workspace(nbytes, dev, "kron")
+    dw1 = torch.empty((up, uq), dtype=torch.float32, device=dev)
+    dw2 = torch.empty((N // up, K // uq), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.anima_lokr_kron_backward(
+            ptr(dw), 1 if dw.dtype == torch.float32 else 0, ptr(w1), ptr(w2), _factor_flag(w1, w2),
+            float(alpha), N, K, up, uq, ptr(dw1), ptr(dw2), ptr(ws), ws.numel(), _lib.stream_ptr(dev)))
+    return dw1, dw2
+
+
+def adaln_fwd(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, eps: float, hw: int
+              ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """x ``[rows, d]``, scale/shift ``[rows/hw, d]`` (bf16, contiguous) -> (y, mean, rstd)."""
+    dev = _lib.require_cuda(x, scale, shift)
+    rows, d = x.shape
+    y = torch.empty_like(x)
+    mean = torch.empty(rows, dtype=torch.float32, device=dev)
+    rstd = torch.empty(rows, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(_lib.load().anima_adaln_fwd(ptr(x), ptr(scale), ptr(shift), float(eps), rows, hw, d, ptr(y),
+                                          ptr(mean), ptr(rstd), _lib.stream_ptr(dev)))
+    return y, mean, rstd
+
+
+def adaln_bwd(dy: torch.Tensor, x: torch.Tensor, scale: torch.Tensor, mean: torch.Tensor,
+              rstd: torch.Tensor, hw: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    dev = _lib.require_cuda(dy, x, scale, mean, rstd)
+    rows, d = x.shape
+    lib = _lib.load()
+    nbytes = check(lib.anima_adaln_bwd_workspace_bytes(rows, hw, d))
+    ws = _lib.workspace(nbytes, dev, "adaln")
+    dx = torch.empty_like(x)
+    dscale = torch.empty_like(scale)
+    dshift = torch.empty_like(scale)
+    with torch.cuda.device(dev):
+        check(lib.anima_adaln_bwd(ptr(dy), ptr(x), ptr(scale), ptr(mean), ptr(rstd), rows, hw, d, ptr(dx),
+                                  ptr(dscale), ptr(dshift), ptr(ws), ws.numel(), _lib.stream_ptr(dev)))
+    return dx, dscale, dshift
+
+
+def gated_add_fwd(x: torch.Tensor, gate: torch.Tensor, y: torch.Tensor, hw: int) -> torch.Tensor:
+    dev = _lib.require_cuda(x, gate, y)
+    rows, d = x.shape
+    out = torch.empty_like(x)
+    with torch.cuda.device(dev):
+        check(_lib.load().anima_gated_add_fwd(ptr(x), ptr(gate), ptr(y), rows, hw, d, ptr(out),
+                                              _lib.stream_ptr(dev)))
+    return out
+
+
+def gated_add_bwd(dout: torch.Tensor, y: torch.Tensor, gate: torch.Tensor, hw: int
+                  ) -> tuple[torch.Tensor, torch.Tensor]:
+    dev = _lib.require_cuda(dout, y, gate)
+    rows, d = y.shape
+    lib = _lib.load()
+    nbytes = check(lib.anima_gated_add_bwd_workspace_bytes(rows, hw, d))
+    ws = _lib.workspace(nbytes, dev, "gated")
+    dy = torch.empty_like(y)
+    dgate = torch.empty_like(gate)
+    with torch.cuda.device(dev):
+        check(lib.anima_gated_add_bwd(ptr(dout), ptr(y), ptr(gate), rows, hw, d, ptr(dy), ptr(dgate),
+                                      ptr(ws), ws.numel(), _lib.stream_ptr(dev)))
+    return dy, dgate
+
+
+def tlokr_rank_mix(hidden: torch.Tensor, c: torch.Tensor, mask: torch.Tensor | None, transpose: bool
+                   ) -> torch.Tensor:
+    dev = _lib.require_cuda(hidden, c, mask)
+    batch, n, _, rank = hidden.shape
+    out = torch.empty_like(hidden)
+    with torch.cuda.device(dev):
+        check(_lib.load().anima_tlokr_rank_mix(ptr(hidden), ptr(c), ptr(mask), batch, n, rank,
+                                               1 if transpose else 0, ptr(out), _lib.stream_ptr(dev)))
+    return out
+
+
+def tlokr_rank_mix_wgrad(grad_mixed: torch.Tensor, hidden: torch.Tensor, mask: torch.Tensor | None
+                         ) -> torch.Tensor:
+    dev = _lib.require_cuda(grad_mixed, hidden, mask)
+    batch, n, _, rank = hidden.shape
+    lib = _lib.load()
+    nbytes = check(lib.anima_tlokr_rank_mix_wgrad_workspace_bytes(batch, n, rank))
+    ws = _lib.workspace(nbytes, dev, "mixwgrad")
+    dc = torch.empty((8, 8), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.anima_tlokr_rank_mix_wgrad(ptr(grad_mixed), ptr(hidden), ptr(mask), batch, n, rank, ptr(dc),
+                                             ptr(ws), ws.numel(), _lib.stream_ptr(dev)))
+    return dc

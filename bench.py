@@ -1,0 +1,329 @@
+"""Benchmark of the quantised LoKr-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (BASELINE.json config 2): batch 8 x 4096 image tokens (M = 32768 rows) through the DiT
+linear shapes (N, K) in {(2048,2048), (6144,2048), (8192,2048), (2048,8192)}. One step is, for
+every shape, the whole LoKr-linear training pass through the package's autograd operator:
+  forward   quantise x (row+column forms, one read), build W + alpha*kron(w1,w2) and quantise it
+            (one read of W), MXFP8 GEMM  y = x . W'^T
+  backward  quantise dy (both forms), MXFP8 dgrad  dx = dy . W', MXFP8 wgrad  dW = dy^T . x (fp32),
+            Kronecker backward to dw1 / dw2
+and, with more than one GPU, one NCCL all-reduce of the flat adapter-gradient buffer (the only
+exchange of the data-parallel step; every rank works on its own batch shard: weak scaling).
+
+`value`  = GEMM flops (2*M*N*K for each of the 3 GEMMs of each shape, all ranks) / step time, inputs
+           resident in HBM; the quantise / merge / Kronecker kernels are inside the timed region.
+`e2e`    = the same metric with every step's x and dy copied from pinned host memory and the adapter
+           gradients plus a checksum of y copied back (weights stay resident, as in training).
+`roofline` is for the dominant kernel (the tcgen05 GEMM), timed with CUDA events inside the step.
+`cpu_baseline` / `--impl reference`: the reference's bf16 eager PyTorch LoKr linear (config 1:
+x [2048,2048], W [8192,2048], factor 8) forward + backward on the host cores.
+Inputs are synthetic (seeded), larger than L2 (x alone is 128 MiB), so no L2 flush is needed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+M_ROWS = 32768
+SHAPES = [(2048, 2048), (6144, 2048), (8192, 2048), (2048, 8192)]  # (N, K)
+FACTOR = 8
+METRIC = "mxfp8_lokr_linear_gemm_tflops"
+UNIT = "TFLOP/s"
+
+
+def gemm_flops_per_step() -> float:
+    return sum(3 * 2.0 * M_ROWS * n * k for n, k in SHAPES)
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons every 200 ms while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.samples: list[list[str]] = []
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def stop(self) -> dict:
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
+        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_lokr_linear(seconds_budget: float, max_iters: int) -> dict:
+    """The reference's bf16 eager path for one LoKr linear (lokr_patch.py:76-94) on the host:
+    config 1, forward + backward to x, w1, w2. Returns TFLOP/s over the three GEMMs."""
+    from oracle import lokr as OL
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(42)
+    rows, K, N = 2048, 2048, 8192
+    x = torch.randn(rows, K, generator=g).to(torch.bfloat16)
+    W = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+    w1 = torch.randn(FACTOR, FACTOR, generator=g) * 0.1
+    w2 = torch.randn(N // FACTOR, K // FACTOR, generator=g) * 0.02
+    gy = torch.randn(rows, N, generator=g).to(torch.bfloat16)
+    flops = 3 * 2.0 * rows * N * K
+    OL.lokr_linear_bf16(x, W, None, w1, w2, 1.0, gy)  # warm-up
+    times = []
+    t_start = time.perf_counter()
+    while len(times) < max_iters and (time.perf_counter() - t_start < seconds_budget or len(times) < 2):
+        t0 = time.perf_counter()
+        OL.lokr_linear_bf16(x, W, None, w1, w2, 1.0, gy)
+        times.append(time.perf_counter() - t0)
+    times.sort()
+    med = times[len(times) // 2]
+    return {"value": flops / med / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"config 1: LoKr linear x[2048,2048] W[8192,2048] factor 8, bf16 eager torch fwd+bwd, "
+                      f"median of {len(times)} iterations ({med * 1e3:.1f} ms each)",
+            "ms_per_iter": med * 1e3, "iters": len(times)}
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    # each "step" is one bounded sample (one fwd+bwd of config 1); W warm-ups then K steps
+    res = cpu_lokr_linear(seconds_budget=120.0, max_iters=max(2, args.steps + args.warmup))
+    line = {"impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_iter"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": workload_config(args.gpus),
+            "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int) -> dict:
+    return {"workload": "config 2: MXFP8 LoKr-linear fwd+dgrad+wgrad at M=32768 over (N,K) in "
+                        "{(2048,2048),(6144,2048),(8192,2048),(2048,8192)}, factor-8 LoKr delta",
+            "rows_per_gpu": M_ROWS, "shapes_NK": SHAPES, "parallelism": f"dp{n_gpus}",
+            "l2": "inputs larger than L2 (x is 128 MiB per shape); no flush"}
+
+
+# ----------------------------------------------------------------------------- GPU arm
+class Shape:
+    """Device-resident operands of one linear shape plus pinned host copies for the e2e leg."""
+
+    def __init__(self, n: int, k: int, dev, seed: int, host: bool):
+        g = torch.Generator().manual_seed(seed)
+        x = torch.randn(M_ROWS, k, generator=g)
+        idx = torch.randperm(k, generator=g)[: max(1, -(-k // 1000))]
+        x[:, idx] *= 50.0                                             # 0.1 % outlier channels
+        self.n, self.k = n, k
+        self.x_host = x.to(torch.bfloat16).pin_memory() if host else x.to(torch.bfloat16)
+        dy = (torch.randn(M_ROWS, n, generator=g) * 0.01).to(torch.bfloat16)
+        self.dy_host = dy.pin_memory() if host else dy
+        self.x = self.x_host.to(dev)
+        self.dy = self.dy_host.to(dev)
+        self.W = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+        self.w1 = (torch.randn(FACTOR, FACTOR, generator=g) * 0.1).to(dev).requires_grad_(True)
+        self.w2 = (torch.randn(n // FACTOR, k // FACTOR, generator=g) * 0.02).to(dev).requires_grad_(True)
+
+
+def run_gpu_arm(args) -> None:
+    import torch.distributed as dist
+
+    from anima_trainer_sm120_b200 import _lib, ops
+    from anima_trainer_sm120_b200.fp8_quant import lokr_linear_fused
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (there is no CPU path for the product arm)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+
+    shapes = [Shape(n, k, dev, seed=1000 * rank + i, host=True) for i, (n, k) in enumerate(SHAPES)]
+    n_grad = sum(s.w1.numel() + s.w2.numel() for s in shapes)
+    flat_grad = torch.zeros(n_grad, dtype=torch.float32, device=dev)
+    grad_host = torch.empty(n_grad, dtype=torch.float32).pin_memory()
+    chk_host = torch.empty(len(shapes), dtype=torch.float32).pin_memory()
+    chk_dev = torch.zeros(len(shapes), dtype=torch.float32, device=dev)
+    gemm_events: list[tuple[torch.cuda.Event, torch.cuda.Event, float]] = []
+    launches = [0]
+
+    # time every tcgen05 GEMM launch with events on the launching stream
+    real_gemm = ops.mx_gemm
+
+    def timed_gemm(a, b, **kw):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = real_gemm(a, b, **kw)
+        e1.record()
+        gemm_events.append((e0, e1, 2.0 * a.rows * b.rows * a.k))
+        return out
+
+    def count(fn, n):
+        def wrapped(*a, **kw):
+            launches[0] += n
+            return fn(*a, **kw)
+        return wrapped
+
+    ops.mx_gemm = count(timed_gemm, 1)
+    ops.mx_quantize = count(ops.mx_quantize, 1)
+    ops.lokr_merge_quantize = count(ops.lokr_merge_quantize, 1)
+    ops.lokr_kron_backward = count(ops.lokr_kron_backward, 2)
+
+    def step(e2e: bool):
+        off = 0
+        for i, s in enumerate(shapes):
+            if e2e:
+                s.x.copy_(s.x_host, non_blocking=True)
+                s.dy.copy_(s.dy_host, non_blocking=True)
+            s.w1.grad = s.w2.grad = None
+            y = lokr_linear_fused(s.x, s.W, None, s.w1, s.w2, 1.0)
+            y.backward(s.dy)
+            for p in (s.w1, s.w2):
+                flat_grad[off:off + p.numel()].copy_(p.grad.reshape(-1))
+                off += p.numel()
+            if e2e:
+                chk_dev[i] = y[::4096, ::512].float().sum()
+        if world > 1:
+            dist.all_reduce(flat_grad)
+            flat_grad.mul_(1.0 / world)
+        if e2e:
+            grad_host.copy_(flat_grad, non_blocking=True)
+            chk_host.copy_(chk_dev, non_blocking=True)
+            torch.cuda.current_stream().synchronize()   # the host reads the step's result
+
+    def timed(e2e: bool, steps: int, warmup: int):
+        for _ in range(warmup):
+            step(e2e)
+        gemm_events.clear()
+        launches[0] = 0
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step(e2e)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.barrier()
+            ms = float(t.item())
+        torch.cuda.synchronize()
+        return ms
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms_total = timed(False, args.steps, max(args.warmup, 3))
+    clocks = sampler.stop() if rank == 0 else {}
+    _lib.check_status_word(dev)
+    n_launch = launches[0]
+    gemm_ms = sum(a.elapsed_time(b) for a, b, _ in gemm_events)
+    gemm_fl = sum(f for _, _, f in gemm_events)
+    n_gemm = len(gemm_events)
+    ms_e2e = timed(True, args.steps, 1)
+    _lib.check_status_word(dev)
+
+    if rank == 0:
+        peaks = {}
+        pk = ROOT / "MEASURED_PEAKS.json"
+        if pk.exists():
+            peaks = json.loads(pk.read_text())
+        bf16_peak = peaks.get("bf16_tflops_sustained")
+        peak = 2.0 * bf16_peak if bf16_peak else 2.0 * 1400.0
+        achieved = gemm_fl / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+        ms_step = ms_total / args.steps
+        fl = gemm_flops_per_step() * world
+        h2d = sum(s.x_host.numel() * 2 + s.dy_host.numel() * 2 for s in shapes)
+        d2h = n_grad * 4 + len(shapes) * 4
+        cpu = cpu_lokr_linear(seconds_budget=15.0, max_iters=20) if world == 1 else None
+        line = {
+            "metric": METRIC, "value": fl / (ms_step * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "mxfp8 (e4m3 codes, e8m0 scales, fp32 accumulate)",
+            "data": "synthetic", "config": workload_config(world),
+            "e2e": {"value": fl / (ms_e2e / args.steps * 1e-3) / 1e12, "unit": UNIT,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": n_launch,
+            "roofline": {"bound": "tensor", "kernel": "mx_gemm_kernel", "achieved": achieved, "peak": peak,
+                         "unit": UNIT, "frac": achieved / peak, "traffic": None,
+                         "peak_source": ("2 x measured sustained bf16 cuBLAS TFLOP/s (MEASURED_PEAKS.json); "
+                                         "no measured fp8 figure exists" if bf16_peak else
+                                         "2 x 1400 TFLOP/s fallback"),
+                         "frac_of_nominal_4500": achieved / 4500.0,
+                         "launches": n_gemm, "avg_launch_ms": gemm_ms / max(n_gemm, 1),
+                         "gemm_share_of_step": gemm_ms / ms_total},
+            "clocks": clocks,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,186 @@
+/*
+ * anima_b200.h — C ABI of libanima_b200.so: hand-written sm_100a CUDA for the
+ * quantised-linear hot path of anima-trainer (MXFP8 quantise, block-scaled
+ * GEMM fwd/dgrad/wgrad with the LoKr delta, fused AdaLN + gated residual,
+ * T-LoKr rank mix and its weight gradient).
+ *
+ * Citations "ref: <file>:<lines>" name the anima-trainer interface (paths
+ * relative to that project's root) that an entry point replaces.
+ *
+ * Conventions for every function below
+ *   - all pointers are DEVICE pointers unless the name says otherwise;
+ *   - tensors are dense row-major; "bf16" means 16-bit bfloat words;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *   - nothing allocates, frees or synchronises; scratch memory is passed in by
+ *     the caller and its size is given by the matching *_workspace_bytes();
+ *   - the return value is ANIMA_OK or a negative ANIMA_E_* code; the text for
+ *     the last failure on the calling thread is anima_last_error();
+ *   - there is no CPU fallback: with no usable GPU the call fails.
+ */
+#ifndef ANIMA_B200_H_
+#define ANIMA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ANIMA_ABI_VERSION 1
+
+enum {
+  ANIMA_OK = 0,
+  ANIMA_E_ARG = -1,         /* null pointer, negative size, bad enum             */
+  ANIMA_E_ALIGN = -2,       /* pointer or leading dimension not 16-byte aligned  */
+  ANIMA_E_SHAPE = -3,       /* size not divisible as the kernel requires         */
+  ANIMA_E_CUDA = -4,        /* a CUDA runtime/driver call failed                 */
+  ANIMA_E_UNSUPPORTED = -5, /* valid request this build has no kernel for        */
+  ANIMA_E_WORKSPACE = -6,   /* workspace pointer null or too small               */
+  ANIMA_E_TOO_LARGE = -7    /* exceeds a fixed capacity of the entry point       */
+};
+
+/* Layout of an e8m0 scale tensor that belongs to a code matrix [rows, k]
+ * quantised along k in blocks of 32 (kb = k/32 scale bytes per row).
+ *   PLAIN  : [rows, kb] row-major — the layout of ref: mxfp8_gemm.py:51-65.
+ *   TILED  : the tensor-core operand layout. Rows are padded to 128 and kb to 4;
+ *            tile (rt, kt) = 128 rows x 4 scale bytes is a contiguous 512-byte
+ *            chunk at ((rt * ceil(kb/4)) + kt) * 512, and inside a chunk the
+ *            byte of (r, j) sits at (r % 32) * 16 + (r / 32) * 4 + j.
+ *            Padding bytes are written as 0. */
+enum { ANIMA_SCALES_PLAIN = 0, ANIMA_SCALES_TILED = 1 };
+
+int anima_abi_version(void);
+const char* anima_last_error(void);
+
+/* ---------------------------------------------------------------- MXFP8 quantise
+ * ref: mxfp8_gemm.py:68-183 (quantize_rowwise + _quantize_rowwise_kernel),
+ *      mxfp8_gemm.py:186-222 (quantize_weight_for_lhs / quantize_weight_for_dgrad).
+ *
+ * x is bf16 [rows, cols] with row pitch ld_x elements. Per group of 32 elements:
+ *   amax = max(max|x|, 1e-30); e = ceil(log2(amax / 448)) clamped to [-127, 127];
+ *   code = e4m3(x * 2^-e) round-to-nearest-even, saturating at +-448; scale byte = e + 127.
+ * Two optional outputs, produced from ONE read of x:
+ *   rowwise   : groups run along cols. codes_row u8 [rows, cols], scales_row for
+ *               matrix [rows, k=cols].                      needs cols % 32 == 0
+ *   columnwise: groups run along rows; written TRANSPOSED so it is again K-major:
+ *               codes_colT u8 [cols, rows], scales_col for matrix [cols, k=rows].
+ *               This is quantize_rowwise(x.t().contiguous()).  needs rows % 32 == 0
+ * Pass NULL for the pair that is not wanted. */
+int anima_mx_quantize(const void* x_bf16, int64_t rows, int64_t cols, int64_t ld_x,
+                      uint8_t* codes_row, uint8_t* scales_row,
+                      uint8_t* codes_colT, uint8_t* scales_col,
+                      int scale_layout, void* stream);
+
+/* Bytes of the scale tensor of a code matrix [rows, k] in the given layout. */
+int64_t anima_mx_scales_bytes(int64_t rows, int64_t k, int scale_layout);
+
+/* ref: mxfp8_gemm.py:225-232 (dequantize_rowwise). out bf16 [rows, k]. */
+int anima_mx_dequantize(const uint8_t* codes, const uint8_t* scales, int64_t rows, int64_t k,
+                        int scale_layout, void* out_bf16, void* stream);
+
+/* PLAIN -> TILED re-layout of a scale tensor (for callers holding reference-layout blocks). */
+int anima_mx_scales_retile(const uint8_t* plain, int64_t rows, int64_t k, uint8_t* tiled,
+                           void* stream);
+
+/* ---------------------------------------------------------------- MXFP8 GEMM
+ * ref: mxfp8_gemm.py:254-336 (_mxfp8_gemm_kernel, mxfp8_matmul);
+ *      fp8_quant.py:146-150 (general_gemm 'TN'), :503-507 ('NN' dgrad, 'NT' wgrad).
+ *
+ * C[M,N] = A[M,K] . B[N,K]^T  (+ bias[N]) with A, B e4m3 codes, both K-major, and
+ * TILED e8m0 scales of [M,K] and [N,K]; fp32 accumulation in tensor memory.
+ * The three training GEMMs map onto this one form through the quantiser outputs:
+ *   fwd   y  = x . W^T        : A = rowwise(x),     B = rowwise(W)
+ *   dgrad dx = dy . W         : A = rowwise(dy),    B = columnwise(W)   (codes_colT [K_in, N_out])
+ *   wgrad dW = dy^T . x       : A = columnwise(dy), B = columnwise(x)   (contraction over rows)
+ * out_dtype 0: C bf16; 1: C fp32. ldc in elements. M, N, K > 0, K % 32 == 0.
+ * status (device int32, may be NULL): set non-zero if a bounded wait inside the
+ * kernel gave up; the kernel then returns early and C is undefined. */
+int anima_mx_gemm(const uint8_t* a_codes, const uint8_t* a_scales,
+                  const uint8_t* b_codes, const uint8_t* b_scales,
+                  void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
+                  const void* bias_bf16, int out_dtype, int32_t* status, void* stream);
+
+/* ---------------------------------------------------------------- LoKr merged weight
+ * ref: lokr_patch.py:76-84 (merged = W + alpha * kron(w1, w2)) followed by the two
+ *      weight quantisations of fp8_quant.py:234-235 / :501.
+ *
+ * W bf16 [N,K]; w1 [up,uq], w2 [vp,vq] = [N/up, K/uq], both fp32 (factors_are_fp32 != 0)
+ * or both bf16. With n = i*vp + p and k = j*vq + q:
+ *   diff   = bf16(w1[i,j] * w2[p,q])                  (torch.kron in the weight dtype)
+ *   merged = bf16(W[n,k] + alpha * diff)              (fp32 sum, rounded once)
+ * Emits (each optional) the bf16 merged weight and its rowwise / columnwise MXFP8
+ * forms exactly as anima_mx_quantize(merged) would. vq % 8 == 0. */
+int anima_lokr_merge_quantize(const void* w_bf16, const void* w1, const void* w2,
+                              int factors_are_fp32, float alpha, int64_t N, int64_t K,
+                              int64_t up, int64_t uq,
+                              void* merged_bf16,
+                              uint8_t* codes_row, uint8_t* scales_row,
+                              uint8_t* codes_colT, uint8_t* scales_col,
+                              int scale_layout, void* stream);
+
+/* ref: autograd of lokr_patch.py:76-84 through torch.kron (docstring :19-21).
+ * dW [N,K] (bf16 if dw_is_fp32 == 0 else fp32):
+ *   dw1[i,j] = alpha * sum_{p,q} dW[i*vp+p, j*vq+q] * w2[p,q]
+ *   dw2[p,q] = alpha * sum_{i,j} dW[i*vp+p, j*vq+q] * w1[i,j]
+ * dw1 fp32 [up,uq], dw2 fp32 [vp,vq]; up, uq <= 8; deterministic two-stage reduction. */
+int64_t anima_lokr_kron_backward_workspace_bytes(int64_t N, int64_t K, int64_t up, int64_t uq);
+int anima_lokr_kron_backward(const void* dw, int dw_is_fp32, const void* w1, const void* w2,
+                             int factors_are_fp32, float alpha, int64_t N, int64_t K, int64_t up,
+                             int64_t uq, float* dw1, float* dw2, void* workspace,
+                             int64_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------- fused AdaLN
+ * ref: adaln_kernel.py:34-68 (_fwd_kernel), :157-207 (FusedAdaLN.forward).
+ * x, y bf16 [rows, d]; scale, shift bf16 [rows / hw, d]; row r uses modulation row r / hw.
+ *   mean = sum(x)/d; var = sum((x-mean)^2)/d; rstd = 1/sqrt(var+eps);
+ *   y = (x-mean)*rstd*(1+scale) + shift;  mean, rstd fp32 [rows] are saved. */
+int anima_adaln_fwd(const void* x, const void* scale, const void* shift, float eps,
+                    int64_t rows, int64_t hw, int64_t d, void* y, float* mean, float* rstd,
+                    void* stream);
+
+/* ref: adaln_kernel.py:71-154 (_bwd_dx_kernel, _bwd_dsdb_kernel), :209-255.
+ * One pass over dy and x yields dx bf16 [rows,d] and, through per-block partial
+ * sums in the workspace plus a fixed-order final sum, dscale / dshift bf16 [rows/hw, d]
+ * (bit-reproducible; the reference accumulates these with fp32 atomics). */
+int64_t anima_adaln_bwd_workspace_bytes(int64_t rows, int64_t hw, int64_t d);
+int anima_adaln_bwd(const void* dy, const void* x, const void* scale, const float* mean,
+                    const float* rstd, int64_t rows, int64_t hw, int64_t d, void* dx,
+                    void* dscale, void* dshift, void* workspace, int64_t workspace_bytes,
+                    void* stream);
+
+/* ---------------------------------------------------------------- gated residual
+ * ref: adaln_kernel.py:272-295 (_gated_add_fwd_kernel), :332-380.
+ * out = x + gate[r / hw] * y, all bf16, evaluated in fp32 and rounded once. */
+int anima_gated_add_fwd(const void* x, const void* gate, const void* y, int64_t rows,
+                        int64_t hw, int64_t d, void* out, void* stream);
+
+/* ref: adaln_kernel.py:298-329 (_gated_add_bwd_dgate_kernel), :382-419.
+ * dy = gate * dout (bf16), dgate[bt] = sum over the hw rows of dout * y (fp32 sum,
+ * fixed order, stored bf16). dx is dout itself and is not written. */
+int64_t anima_gated_add_bwd_workspace_bytes(int64_t rows, int64_t hw, int64_t d);
+int anima_gated_add_bwd(const void* dout, const void* y, const void* gate, int64_t rows,
+                        int64_t hw, int64_t d, void* dy, void* dgate, void* workspace,
+                        int64_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------- T-LoKr rank mix
+ * ref: tlokr_kernels.py:15-82, :125-166 (rank_mix).
+ * hidden, out bf16 [batch, n, 8, rank]; c bf16 [8,8]; mask bf16 [batch, rank] or NULL.
+ *   out[b,n,i,r] = (sum_j (transpose ? c[j,i] : c[i,j]) * hidden[b,n,j,r]) * mask[b,r]
+ * fp32 accumulation in j order. rank % 8 == 0. */
+int anima_tlokr_rank_mix(const void* hidden, const void* c, const void* mask, int64_t batch,
+                         int64_t n_per_batch, int64_t rank, int transpose, void* out,
+                         void* stream);
+
+/* ref: tlokr_kernels.py:85-122, :168-204 (rank_mix_wgrad).
+ *   dc[i,j] = sum_{b,n,r} grad_mixed[b,n,i,r] * hidden[b,n,j,r] * mask[b,r]   (fp32 [8,8])
+ * Reads both tensors once (the reference reads them once per (i,j) pair). */
+int64_t anima_tlokr_rank_mix_wgrad_workspace_bytes(int64_t batch, int64_t n_per_batch,
+                                                   int64_t rank);
+int anima_tlokr_rank_mix_wgrad(const void* grad_mixed, const void* hidden, const void* mask,
+                               int64_t batch, int64_t n_per_batch, int64_t rank, float* dc,
+                               void* workspace, int64_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ANIMA_B200_H_ */

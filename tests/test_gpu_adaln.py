@@ -1,0 +1,173 @@
+"""GPU parity: fused AdaLN and gated residual through the C ABI vs the CPU oracle, the golden
+vectors of the reference kernels, and eager PyTorch. Tolerance for floating-point outputs is
+rtol 1e-2 / atol 2e-2 (bf16 I/O); elementwise outputs whose fp32 value is exact are bit-compared.
+Cases follow tests/sanity_adaln_kernel.py:105-112 of the reference (shapes, seeds 0 / 1, eps 1e-6,
+scale / shift ~ 0.1 N(0,1))."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import bf16_from_bits
+from oracle import adaln as OA
+
+pytestmark = pytest.mark.gpu
+RTOL, ATOL = 1e-2, 2e-2
+BF16 = torch.bfloat16
+
+
+def _ops():
+    from anima_trainer_sm120_b200 import ops
+    return ops
+
+
+def _close(got, want, rtol=RTOL, atol=ATOL):
+    torch.testing.assert_close(got.float().cpu(), want.float().cpu(), rtol=rtol, atol=atol)
+
+
+def _case(BT, HW, D, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(BT * HW, D, generator=g).to(BF16)
+    s = (torch.randn(BT, D, generator=g) * 0.1).to(BF16)
+    b = (torch.randn(BT, D, generator=g) * 0.1).to(BF16)
+    gate = (torch.randn(BT, D, generator=g) * 0.1).to(BF16)
+    y2 = torch.randn(BT * HW, D, generator=g).to(BF16)
+    g1 = torch.Generator().manual_seed(seed + 1)
+    dy = torch.randn(BT * HW, D, generator=g1).to(BF16)
+    return x, s, b, gate, y2, dy
+
+
+@pytest.mark.parametrize("BT,HW,D", [(2, 24, 256), (3, 8, 768), (8, 1024, 2048), (4, 256, 1024), (1, 5, 8),
+                                       (2, 7, 2056), (2, 33, 4096)])
+def test_adaln_forward_backward_vs_oracle(BT, HW, D):
+    ops = _ops()
+    x, s, b, _, _, dy = _case(BT, HW, D)
+    y, mean, rstd = ops.adaln_fwd(x.cuda(), s.cuda(), b.cuda(), 1e-6, HW)
+    y_o, mean_o, rstd_o = OA.adaln_fwd_fp32(x, s, b, 1e-6, HW)
+    _close(mean, mean_o, 1e-5, 1e-5)
+    _close(rstd, rstd_o, 1e-5, 1e-5)
+    _close(y, y_o.to(BF16))
+    assert (y.cpu().view(torch.int16) != y_o.to(BF16).view(torch.int16)).float().mean() < 0.02
+    dx, ds, db = ops.adaln_bwd(dy.cuda(), x.cuda(), s.cuda(), mean, rstd, HW)
+    dx_o, ds_o, db_o = OA.adaln_bwd_fp32(dy, x, s, mean.cpu(), rstd.cpu(), HW)
+    _close(dx, dx_o.to(BF16))
+    # H*W reductions: judged against the fp32 truth rounded to bf16 (sanity_adaln_kernel.py:81-96)
+    _close(ds, ds_o.to(BF16))
+    _close(db, db_o.to(BF16))
+
+
+def test_adaln_golden_reference_kernel_outputs(golden):
+    ops = _ops()
+    g = golden("adaln")
+    for n in ("a", "b"):
+        BT, HW, D = (int(v) for v in g[f"{n}_shape"])
+        x, s, b, gate, y2, dy = (bf16_from_bits(g[f"{n}_{k}"]).cuda() for k in ("x", "s", "b", "gate", "y2", "dy"))
+        y, mean, rstd = ops.adaln_fwd(x, s, b, 1e-6, HW)
+        _close(y, bf16_from_bits(g[f"{n}_y"]))
+        _close(mean, torch.from_numpy(g[f"{n}_mean"]), 1e-5, 1e-5)
+        _close(rstd, torch.from_numpy(g[f"{n}_rstd"]), 1e-5, 1e-5)
+        dx, ds, db = ops.adaln_bwd(dy, x, s, mean, rstd, HW)
+        _close(dx, bf16_from_bits(g[f"{n}_dx"]))
+        _close(ds, torch.from_numpy(g[f"{n}_ds"]).to(BF16))
+        _close(db, torch.from_numpy(g[f"{n}_db"]).to(BF16))
+        out = ops.gated_add_fwd(x, gate, y2, HW)
+        _close(out, bf16_from_bits(g[f"{n}_go"]))
+        _, dg = ops.gated_add_bwd(dy, y2, gate, HW)
+        _close(dg, torch.from_numpy(g[f"{n}_dg"]).to(BF16))
+
+
+@pytest.mark.parametrize("B,H,W,D", [(8, 32, 32, 2048), (2, 8, 8, 768)])
+def test_autograd_ops_vs_eager(B, H, W, D):
+    """FusedAdaLN / FusedGatedAdd (the reference's operator signatures) against eager autograd;
+    dscale / dgate are held to the reference's own criterion: no further from the fp32 truth than
+    1.5x eager's error (tests/sanity_adaln_kernel.py:58-65, 81-96)."""
+    from anima_trainer_sm120_b200.adaln_kernel import FusedAdaLN, FusedGatedAdd
+    torch.manual_seed(0)
+    dev = "cuda"
+    x = torch.randn(B, 1, H, W, D, dtype=BF16, device=dev)
+    scale = (torch.randn(B, 1, 1, 1, D, device=dev) * 0.1).to(BF16)
+    shift = (torch.randn(B, 1, 1, 1, D, device=dev) * 0.1).to(BF16)
+    gate = (torch.randn(B, 1, 1, 1, D, device=dev) * 0.1).to(BF16)
+    torch.manual_seed(1)
+    dy = torch.randn_like(x)
+
+    def run(fn, dtype):
+        leaves = [t.detach().to(dtype).clone().requires_grad_(True) for t in (x, scale, shift, gate)]
+        xx, ss, bb, gg = leaves
+        out = fn(xx, ss, bb, gg)
+        out.backward(dy.to(dtype))
+        return out.detach(), [t.grad for t in leaves]
+
+    def fused(xx, ss, bb, gg):
+        return FusedGatedAdd.apply(xx, gg, FusedAdaLN.apply(xx, ss, bb, 1e-6))
+
+    def eager(xx, ss, bb, gg):
+        return OA.gated_add_eager(xx, gg, OA.adaln_eager(xx, ss, bb, 1e-6))
+
+    out_k, grads_k = run(fused, BF16)
+    out_e, grads_e = run(eager, BF16)
+    out_t, grads_t = run(eager, torch.float32)
+    _close(out_k, out_t.to(BF16))
+    _close(out_k, out_e, 5e-2, 5e-2)                      # reference's own bf16 tolerance (:105)
+    _close(grads_k[0], grads_t[0].to(BF16))               # dx
+    _close(grads_k[2], grads_t[2].to(BF16))               # dshift
+    for i in (1, 3):                                      # dscale, dgate
+        err_k = (grads_k[i].float() - grads_t[i]).abs().max().item()
+        err_e = (grads_e[i].float() - grads_t[i]).abs().max().item()
+        assert err_k <= max(1.5 * err_e, 1e-3), (i, err_k, err_e)
+
+
+def test_gated_add_elementwise_outputs_bit_exact():
+    """x + g*y and g*dout: the product of two bf16 values is exact in fp32, so the kernel must
+    reproduce the fp32 oracle bit for bit after the single rounding."""
+    ops = _ops()
+    x, _, _, gate, y2, dy = _case(4, 96, 1024, seed=3)
+    out = ops.gated_add_fwd(x.cuda(), gate.cuda(), y2.cuda(), 96).cpu()
+    assert torch.equal(out.view(torch.int16), OA.gated_add_fwd_fp32(x, gate, y2, 96).to(BF16).view(torch.int16))
+    d_y, d_g = ops.gated_add_bwd(dy.cuda(), y2.cuda(), gate.cuda(), 96)
+    dy_o, dg_o = OA.gated_add_bwd_fp32(dy, y2, gate, 96)
+    assert torch.equal(d_y.cpu().view(torch.int16), dy_o.to(BF16).view(torch.int16))
+    _close(d_g, dg_o.to(BF16))
+
+
+def test_reductions_are_bit_reproducible():
+    ops = _ops()
+    x, s, b, gate, y2, dy = (t.cuda() for t in _case(8, 512, 2048, seed=7))
+    _, mean, rstd = ops.adaln_fwd(x, s, b, 1e-6, 512)
+    first = ops.adaln_bwd(dy, x, s, mean, rstd, 512)
+    g_first = ops.gated_add_bwd(dy, y2, gate, 512)
+    for _ in range(3):
+        again = ops.adaln_bwd(dy, x, s, mean, rstd, 512)
+        assert all(torch.equal(a, b_) for a, b_ in zip(first, again))
+        assert all(torch.equal(a, b_) for a, b_ in zip(g_first, ops.gated_add_bwd(dy, y2, gate, 512)))
+
+
+def test_full_size_config3_properties():
+    """Config 3 shape x [8, 4096, 2048]: oracle on one sample, and size-independent properties —
+    LN output rows have zero mean / unit variance when scale = shift = 0; dshift equals the column
+    sum of dy; linearity of gated add in gate."""
+    ops = _ops()
+    BT, HW, D = 8, 4096, 2048
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(BT * HW, D, generator=g, device="cuda").to(BF16)
+    zeros = torch.zeros(BT, D, dtype=BF16, device="cuda")
+    y, mean, rstd = ops.adaln_fwd(x, zeros, zeros, 1e-6, HW)
+    yf = y.float()
+    assert yf.mean(dim=1).abs().max() < 5e-3
+    assert (yf.var(dim=1, unbiased=False) - 1).abs().max() < 2e-2
+    mod = (torch.randn(BT, 3 * D, generator=g, device="cuda") * 0.1).to(BF16)
+    shift, scale, gate = (t.contiguous() for t in mod.chunk(3, dim=-1))
+    y, mean, rstd = ops.adaln_fwd(x, scale, shift, 1e-6, HW)
+    sl = slice(3 * HW, 3 * HW + 512)
+    y_o, _, _ = OA.adaln_fwd_fp32(x[sl].cpu(), scale[3:4].cpu(), shift[3:4].cpu(), 1e-6, 512)
+    _close(y[sl], y_o.to(BF16))
+    dy = torch.randn(BT * HW, D, generator=g, device="cuda").to(BF16)
+    dx, ds, db = ops.adaln_bwd(dy, x, scale, mean, rstd, HW)
+    _close(db, dy.float().view(BT, HW, D).sum(dim=1).to(BF16))
+    dx_o, _, _ = OA.adaln_bwd_fp32(dy[sl].cpu(), x[sl].cpu(), scale[3:4].cpu(), mean[sl].cpu(), rstd[sl].cpu(), 512)
+    _close(dx[sl], dx_o.to(BF16))
+    out1 = ops.gated_add_fwd(x, gate, y, HW).float()
+    out0 = ops.gated_add_fwd(x, torch.zeros_like(gate), y, HW)
+    assert torch.equal(out0, x)
+    _close(out1, x.float() + gate.float().repeat_interleave(HW, dim=0) * y.float())

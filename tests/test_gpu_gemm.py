@@ -1,0 +1,217 @@
+"""GPU parity: the tcgen05 block-scaled MXFP8 GEMM through the C ABI.
+
+Gate 1 (kernel correctness): kernel vs the dequantise-then-matmul oracle on IDENTICAL codes and
+scales, rtol 1e-2 / atol 2e-2 (differences are accumulation order and the bf16 store).
+Gate 2 (the reference's own acceptance, tests/sanity_mxfp8_triton.py:29-37, :86-90): quantised
+forward / dgrad (and wgrad) vs the bf16 path, max_err / max|ref| < 0.10.
+Full-size checks use size-independent properties (linearity in a scale byte, agreement of an
+output tile with the oracle, transposition symmetry)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import bf16_from_bits
+from oracle import mxfp8 as OQ
+
+pytestmark = pytest.mark.gpu
+RTOL, ATOL = 1e-2, 2e-2
+BF16 = torch.bfloat16
+
+
+def _ops():
+    from anima_trainer_sm120_b200 import _lib, ops
+    return ops, _lib
+
+
+def _acts(rows, cols, seed, std=1.0, outliers=True):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, cols, generator=g) * std
+    if outliers:
+        idx = torch.randperm(cols, generator=g)[: max(1, -(-cols // 1000))]
+        x[:, idx] *= 50.0
+    return x.to(BF16)
+
+
+def _oracle_product(a, b, bias=None, out_bf16=True):
+    """Oracle on the kernel's own operands (PLAIN scales)."""
+    return OQ.matmul(a.codes.cpu().numpy(), a.scales.cpu().numpy(), b.codes.cpu().numpy(), b.scales.cpu().numpy(),
+                     None if bias is None else bias.float().cpu().numpy(), out_bf16=out_bf16)
+
+
+def _gemm_case(M, N, K, seed, bias=False, out_dtype=BF16):
+    ops, lib = _ops()
+    x = _acts(M, K, seed).cuda()
+    w = _acts(N, K, seed + 1, std=0.02, outliers=False).cuda()
+    xa, _ = ops.mx_quantize(x, rowwise=True, layout=0)
+    wb, _ = ops.mx_quantize(w, rowwise=True, layout=0)
+    b = (torch.randn(N, generator=torch.Generator().manual_seed(seed + 2)) * 0.5).to(BF16).cuda() if bias else None
+    c = ops.mx_gemm(ops.mx_retile(xa), ops.mx_retile(wb), bias=b, out_dtype=out_dtype)
+    torch.cuda.synchronize()
+    lib.check_status_word(c.device)
+    want = _oracle_product(xa, wb, b, out_bf16=out_dtype == BF16)
+    np.testing.assert_allclose(c.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+    return c, want
+
+
+def test_golden_operands(golden):
+    """The reference's own codes and scales in, the reference's dequantise+matmul product out."""
+    ops, lib = _ops()
+    g = golden("gemm")
+    def op(c, s):
+        return ops.mx_retile(ops.MXOperand(torch.from_numpy(g[c]).cuda(), torch.from_numpy(g[s]).cuda(), 0))
+    y = ops.mx_gemm(op("x_codes", "x_scales"), op("w_codes", "w_scales"))
+    gx = ops.mx_gemm(op("g_codes", "g_scales"), op("wT_codes", "wT_scales"))
+    lib.check_status_word(y.device)
+    np.testing.assert_allclose(y.float().cpu().numpy(), OQ.bf16_bits_to_f32(g["y"]), rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(gx.float().cpu().numpy(), OQ.bf16_bits_to_f32(g["gx"]), rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("M,N,K", [
+    (128, 128, 128),     # one tile, one K-block, narrow-N kernel
+    (128, 256, 128),     # one tile of the wide kernel
+    (128, 256, 512),     # ring wraps once
+    (256, 512, 1024),    # several tiles per CTA are not needed yet: 4 tiles
+    (384, 128, 2048),    # narrow kernel, long K (ring wraps 4x)
+    (1024, 2048, 256),   # 64 tiles
+])
+def test_tile_aligned_shapes(M, N, K):
+    _gemm_case(M, N, K, seed=M + N + K)
+
+
+@pytest.mark.parametrize("M,N,K", [
+    (100, 72, 96),       # every dimension ragged (K % 32 == 0, N % 8 == 0)
+    (130, 264, 160),     # one row / 8 columns past a tile edge, K tail of 32
+    (1, 8, 32),          # smallest legal problem
+    (257, 384, 416),     # N = 1.5 wide tiles: second scale chunk of the last tile is clamped
+    (4096, 2048, 1024),  # cross-attn k/v shape (8 x 512 text tokens)
+])
+def test_ragged_shapes(M, N, K):
+    _gemm_case(M, N, K, seed=M * 3 + N)
+
+
+def test_more_tiles_than_sms_exercises_both_accumulator_buffers():
+    # 20480/128 * 512/256 = 320 tiles on <= 148 persistent CTAs: every CTA runs >= 2 tiles
+    _gemm_case(20480, 512, 256, seed=11)
+    _gemm_case(20480, 128, 384, seed=12)
+
+
+def test_bias_and_fp32_output():
+    _gemm_case(256, 512, 256, seed=5, bias=True)
+    _gemm_case(256, 512, 256, seed=6, bias=True, out_dtype=torch.float32)
+    _gemm_case(200, 136, 96, seed=7, out_dtype=torch.float32)
+
+
+def test_scale_bytes_are_applied_per_block():
+    """Doubling one operand's scale byte for a single (row-tile, K-block) changes exactly the rows
+    of that block's contribution: checks the shared->tensor-memory scale path and the sf_id
+    selection of each of the four K sub-blocks."""
+    ops, lib = _ops()
+    M, N, K = 128, 256, 256
+    x = _acts(M, K, 1, outliers=False).cuda()
+    w = _acts(N, K, 2, std=0.02, outliers=False).cuda()
+    xa, _ = ops.mx_quantize(x, rowwise=True, layout=0)
+    wb, _ = ops.mx_quantize(w, rowwise=True, layout=0)
+    for kb in range(K // 32):
+        for who in ("a", "b"):
+            xs, ws = xa.scales.clone(), wb.scales.clone()
+            (xs if who == "a" else ws)[5:40, kb] += 1
+            a2 = ops.MXOperand(xa.codes, xs, 0)
+            b2 = ops.MXOperand(wb.codes, ws, 0)
+            c = ops.mx_gemm(ops.mx_retile(a2), ops.mx_retile(b2), out_dtype=torch.float32)
+            want = _oracle_product(a2, b2, out_bf16=False)
+            np.testing.assert_allclose(c.cpu().numpy(), want, rtol=1e-3, atol=1e-3)
+    lib.check_status_word(x.device)
+
+
+def _rel_max(ref, got):
+    return float((ref.float() - got.float()).abs().max() / (ref.float().abs().max() + 1e-9))
+
+
+@pytest.mark.parametrize("D_in,D_out", [(2048, 2048), (1024, 2048), (2048, 8192), (8192, 2048)])
+def test_reference_acceptance_fwd_dgrad_wgrad(D_in, D_out):
+    """The reference's sanity shapes (tests/sanity_mxfp8_triton.py:86-90) at BS = 4096 rows: forward,
+    dgrad and wgrad through the quantiser + GEMM vs bf16 matmuls, rel_max < 0.10; and the frozen
+    linear autograd op with the reference's signature."""
+    ops, lib = _ops()
+    from anima_trainer_sm120_b200 import mxfp8_gemm as mg
+    torch.manual_seed(0)
+    BS = 4096
+    x = torch.randn(BS, D_in, device="cuda", dtype=BF16)
+    W = (torch.randn(D_out, D_in, device="cuda") / D_in ** 0.5).to(BF16)
+    gy = torch.randn(BS, D_out, device="cuda", dtype=BF16)
+    xr, xc = ops.mx_quantize(x, rowwise=True, colwise=True)
+    wr, wc = ops.mx_quantize(W, rowwise=True, colwise=True)
+    gr, gc = ops.mx_quantize(gy, rowwise=True, colwise=True)
+    y = ops.mx_gemm(xr, wr)                 # x . W^T
+    dx = ops.mx_gemm(gr, wc)                # gy . W      (contraction over D_out)
+    dw = ops.mx_gemm(gc, xc)                # gy^T . x    (contraction over the rows)
+    lib.check_status_word(x.device)
+    assert _rel_max(x @ W.t(), y) < 0.10
+    assert _rel_max(gy @ W, dx) < 0.10
+    assert _rel_max(gy.t() @ x, dw) < 0.10
+    # autograd op, reference signature (mxfp8_gemm.py:342-419)
+    W_fwd, W_bwd = mg.quantize_weight_for_lhs(W), mg.quantize_weight_for_dgrad(W)
+    assert W_bwd.data.shape == W.shape and W_bwd.scales.shape == (D_in, D_out // 32)
+    xk = x.clone().requires_grad_(True)
+    yk = mg.mxfp8_frozen_linear_triton(xk, W_fwd, W_bwd, None)
+    yk.float().pow(2).mean().backward()
+    xr_ = x.clone().requires_grad_(True)
+    yr = torch.nn.functional.linear(xr_, W)
+    yr.float().pow(2).mean().backward()
+    assert _rel_max(yr, yk) < 0.10 and _rel_max(xr_.grad, xk.grad) < 0.10
+    assert torch.equal(yk, y)
+
+
+def test_reference_call_pattern_mxfp8_matmul():
+    """mxfp8_matmul with the stride arguments of both reference call sites (:375-380, :409-414)."""
+    ops, _ = _ops()
+    from anima_trainer_sm120_b200 import mxfp8_gemm as mg
+    x = _acts(256, 512, 3).cuda()
+    W = _acts(384, 512, 4, std=0.02, outliers=False).cuda()
+    gy = _acts(256, 384, 5, outliers=False).cuda()
+    xb, W_fwd, W_bwd, gb = mg.quantize_rowwise(x), mg.quantize_weight_for_lhs(W), mg.quantize_weight_for_dgrad(W), mg.quantize_rowwise(gy)
+    y = mg.mxfp8_matmul(xb, W_fwd.data, W_fwd.scales, M=256, N=384, K=512,
+                        B_stride_k=W_fwd.data.stride(1), B_stride_n=W_fwd.data.stride(0))
+    gx = mg.mxfp8_matmul(gb, W_bwd.data, W_bwd.scales, M=256, N=512, K=384,
+                         B_stride_k=W_bwd.data.stride(0), B_stride_n=W_bwd.data.stride(1))
+    want_y = OQ.matmul(xb.data.cpu().numpy(), xb.scales.cpu().numpy(), W_fwd.data.cpu().numpy(), W_fwd.scales.cpu().numpy())
+    np.testing.assert_allclose(y.float().cpu().numpy(), want_y, rtol=RTOL, atol=ATOL)
+    wT = W_bwd.data.t().contiguous()
+    want_gx = OQ.matmul(gb.data.cpu().numpy(), gb.scales.cpu().numpy(), wT.cpu().numpy(), W_bwd.scales.cpu().numpy())
+    np.testing.assert_allclose(gx.float().cpu().numpy(), want_gx, rtol=RTOL, atol=ATOL)
+    with pytest.raises(NotImplementedError):
+        mg.mxfp8_matmul(xb, W_fwd.data, W_fwd.scales, M=256, N=384, K=512, B_stride_k=512, B_stride_n=1)
+    deq = mg.dequantize_rowwise(xb, tuple(x.shape))
+    assert _rel_max(x, deq) < 0.10
+
+
+def test_full_size_config2_properties():
+    """Config 2, (N, K) = (8192, 2048) at M = 32768: three disjoint output tiles against the oracle
+    on identical codes, the wgrad GEMM against its transposed formulation, and exact zero rows for
+    zero activations."""
+    ops, lib = _ops()
+    M, N, K = 32768, 8192, 2048
+    x = _acts(M, K, 42).cuda()
+    x[777] = 0
+    w = _acts(N, K, 43, std=0.02, outliers=False).cuda()
+    xa, _ = ops.mx_quantize(x, rowwise=True, layout=0)
+    wb, _ = ops.mx_quantize(w, rowwise=True, layout=0)
+    c = ops.mx_gemm(ops.mx_retile(xa), ops.mx_retile(wb))
+    lib.check_status_word(c.device)
+    assert not bool(c[777].any())
+    for r0, c0 in [(0, 0), (32768 - 128, 8192 - 256), (12345 // 128 * 128, 4096)]:
+        a = ops.MXOperand(xa.codes[r0:r0 + 128], xa.scales[r0:r0 + 128], 0)
+        b = ops.MXOperand(wb.codes[c0:c0 + 256], wb.scales[c0:c0 + 256], 0)
+        np.testing.assert_allclose(c[r0:r0 + 128, c0:c0 + 256].float().cpu().numpy(), _oracle_product(a, b),
+                                   rtol=RTOL, atol=ATOL)
+    # wgrad: dW = gy^T x over 32768 rows; (gy^T x)^T == x^T gy with the operands swapped
+    gy = _acts(M, 2048, 44, outliers=False).cuda()
+    _, gc = ops.mx_quantize(gy, rowwise=False, colwise=True)
+    _, xc = ops.mx_quantize(x, rowwise=False, colwise=True)
+    dw = ops.mx_gemm(gc, xc, out_dtype=torch.float32)
+    dw_t = ops.mx_gemm(xc, gc, out_dtype=torch.float32)
+    lib.check_status_word(c.device)
+    torch.testing.assert_close(dw, dw_t.t(), rtol=1e-5, atol=1e-4)
+    assert _rel_max(gy.float().t() @ x.float(), dw) < 0.10

@@ -1,0 +1,139 @@
+"""GPU parity: the MXFP8 quantiser through the C ABI vs the CPU oracle — bit-exact codes and
+scale bytes — on the golden vectors, on seeded data with config-2 statistics, on ragged and
+edge shapes, and at full size through size-independent properties."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import bf16_from_bits
+from oracle import mxfp8 as OQ
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from anima_trainer_sm120_b200 import ops
+    return ops
+
+
+def _activations(rows, cols, seed, outliers=True):
+    """bf16 ~N(0,1) with 0.1 % of the channels scaled x50 (config 2)."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, cols, generator=g)
+    if outliers:
+        idx = torch.randperm(cols, generator=g)[: max(1, -(-cols // 1000))]
+        x[:, idx] *= 50.0
+    return x.to(torch.bfloat16)
+
+
+def _check(x_cpu, *, rowwise, colwise, layout):
+    ops = _ops()
+    xf = x_cpu.float().numpy()
+    row, col = ops.mx_quantize(x_cpu.cuda(), rowwise=rowwise, colwise=colwise, layout=layout)
+    torch.cuda.synchronize()
+    if rowwise:
+        codes, scales = OQ.quantize_rowwise(xf)
+        assert np.array_equal(row.codes.cpu().numpy(), codes)
+        want = scales if layout == 0 else OQ.scales_to_tiled(scales)
+        assert np.array_equal(row.scales.cpu().numpy().reshape(want.shape), want)
+    if colwise:
+        codes, scales = OQ.quantize_colwise_T(xf)
+        assert np.array_equal(col.codes.cpu().numpy(), codes)
+        want = scales if layout == 0 else OQ.scales_to_tiled(scales)
+        assert np.array_equal(col.scales.cpu().numpy().reshape(want.shape), want)
+
+
+def test_golden_vectors_bit_exact(golden):
+    """Scale bytes equal the reference quantiser's everywhere; codes equal the oracle's, which the
+    golden test pins against the reference (hardware round-to-nearest-even cast)."""
+    ops = _ops()
+    g = golden("quantiser")
+    x = bf16_from_bits(g["x"])
+    row, col = ops.mx_quantize(x.cuda(), rowwise=True, colwise=True, layout=0)
+    assert np.array_equal(row.scales.cpu().numpy(), g["scales"])
+    codes, _ = OQ.quantize_rowwise(x.float().numpy())
+    assert np.array_equal(row.codes.cpu().numpy(), codes)
+    w = bf16_from_bits(g["w"])
+    _, wcol = ops.mx_quantize(w.cuda(), rowwise=False, colwise=True, layout=0)
+    assert np.array_equal(wcol.scales.cpu().numpy(), g["dgrad_scales"])
+    # dequantise of the reference's codes reproduces the reference's dequantize_rowwise bits
+    op = ops.MXOperand(torch.from_numpy(g["codes"]).cuda(), torch.from_numpy(g["scales"]).cuda(), 0)
+    deq = ops.mx_dequantize(op).cpu()
+    assert torch.equal(deq.view(torch.int16), bf16_from_bits(g["deq"]).view(torch.int16))
+
+
+@pytest.mark.parametrize("layout", [0, 1])
+@pytest.mark.parametrize("rows,cols", [(128, 128), (256, 384), (32, 32), (96, 160), (160, 2048), (512, 96)])
+def test_row_and_column_forms_bit_exact(rows, cols, layout):
+    _check(_activations(rows, cols, seed=rows * 7 + cols), rowwise=True, colwise=True, layout=layout)
+
+
+@pytest.mark.parametrize("layout", [0, 1])
+def test_ragged_rows_rowwise_only(layout):
+    # rows not a multiple of 32 (row-wise form only needs cols % 32 == 0), incl. a single row
+    for rows, cols in [(1, 64), (45, 96), (130, 256)]:
+        _check(_activations(rows, cols, seed=rows), rowwise=True, colwise=False, layout=layout)
+
+
+def test_column_only_and_strided_input():
+    _check(_activations(64, 200, seed=3), rowwise=False, colwise=True, layout=1)
+    ops = _ops()
+    big = _activations(64, 512, seed=9).cuda()
+    view = big[:, 128:384]                       # row pitch 512, 256 columns
+    row, _ = ops.mx_quantize(view, rowwise=True, layout=0)
+    codes, scales = OQ.quantize_rowwise(view.cpu().float().numpy())
+    assert np.array_equal(row.codes.cpu().numpy(), codes) and np.array_equal(row.scales.cpu().numpy(), scales)
+
+
+def test_edge_values():
+    x = torch.zeros(32, 64, dtype=torch.bfloat16)
+    x[0, :] = 0.0
+    x[1, :32] = float("inf"); x[1, 32:] = -3.0e38
+    x[2, :] = 1e-38
+    x[3, 0] = 448.0; x[3, 1] = -449.0; x[3, 2] = 1.75
+    x[4, :] = torch.tensor(2.0 ** -126)
+    _check(x, rowwise=True, colwise=True, layout=0)
+
+
+def test_empty_input_is_a_noop():
+    ops = _ops()
+    row, _ = ops.mx_quantize(torch.empty(0, 64, dtype=torch.bfloat16, device="cuda"), rowwise=True, layout=0)
+    assert row.codes.numel() == 0
+
+
+def test_retile_and_dequantise_roundtrip():
+    ops = _ops()
+    x = _activations(200, 320, seed=5)
+    plain, _ = ops.mx_quantize(x.cuda(), rowwise=True, layout=0)
+    tiled, _ = ops.mx_quantize(x.cuda(), rowwise=True, layout=1)
+    assert torch.equal(ops.mx_retile(plain).scales, tiled.scales)
+    d0, d1 = ops.mx_dequantize(plain), ops.mx_dequantize(tiled)
+    assert torch.equal(d0, d1)
+    want = OQ.round_to_bf16(OQ.dequantize_rowwise(plain.codes.cpu().numpy(), plain.scales.cpu().numpy()))
+    assert np.array_equal(d0.float().cpu().numpy(), want)
+    # quantise -> dequantise noise, the reference's own acceptance (tests/sanity_mxfp8_triton.py:49-52)
+    rel = (d0.float().cpu() - x.float()).abs().max() / x.float().abs().max()
+    assert rel < 0.10
+
+
+def test_full_size_properties():
+    """x [32768, 2048] (config 2): oracle on a 512-row slice, plus properties that hold at any size:
+    the column form equals the row form of the transpose, dequantised values re-quantise to
+    themselves, and |dequant - x| <= 2^(e-4) * ... bounded by one e4m3 half-step."""
+    ops = _ops()
+    x = _activations(32768, 2048, seed=42).cuda()
+    row, col = ops.mx_quantize(x, rowwise=True, colwise=True, layout=0)
+    sl = slice(13 * 512, 14 * 512)
+    codes, scales = OQ.quantize_rowwise(x[sl].cpu().float().numpy())
+    assert np.array_equal(row.codes[sl].cpu().numpy(), codes) and np.array_equal(row.scales[sl].cpu().numpy(), scales)
+    rowT, _ = ops.mx_quantize(x.t().contiguous(), rowwise=True, layout=0)
+    assert torch.equal(rowT.codes, col.codes) and torch.equal(rowT.scales, col.scales)
+    deq = ops.mx_dequantize(row)
+    again, _ = ops.mx_quantize(deq, rowwise=True, layout=0)   # representable values survive exactly
+    assert torch.equal(ops.mx_dequantize(again), deq)
+    # relative step of e4m3 is 2^-3; error <= half a step of the block's top binade
+    step = torch.ldexp(torch.ones((), device="cuda"), row.scales.int() - 127 + 8 - 4)   # 2^(e+8) * 2^-4
+    err = (deq.float() - x.float()).abs().view(32768, 64, 32).amax(dim=2)
+    assert bool((err <= step).all())
