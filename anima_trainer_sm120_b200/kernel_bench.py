@@ -1,0 +1,152 @@
+"""Per-kernel throughput of ``libanima_b200.so`` at the production shapes.
+
+    python -m anima_trainer_sm120_b200.kernel_bench [--iters 20] [--only gemm|hbm] [--small]
+
+Every kernel is timed alone with CUDA events on the launching stream (warm-ups, then the median
+over ``--iters`` replays of a CUDA graph holding 4 launches, an L2-sized buffer rewritten before
+each replay; all tensor sets are larger than L2) and reported as
+one JSON line: achieved HBM GB/s for the memory-bound kernels (algorithmic bytes, i.e. each
+tensor read or written once) or TFLOP/s for the GEMMs (2*M*N*K), next to the measured peak of
+``MEASURED_PEAKS.json`` when that file is present. ``--small`` shrinks every shape (for ncu
+captures, which should hold a few GB at most and end quickly).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+from . import _lib, ops
+
+BF16 = torch.bfloat16
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    return json.loads(p.read_text()) if p.exists() else {}
+
+
+class Timer:
+    """Median device time of one launch. The launch is captured ``reps`` times into a CUDA graph so
+    that host-side launch overhead (allocation of the outputs, ctypes) cannot show up as idle time
+    between the two events; every tensor set here is larger than L2, and an L2-sized buffer is
+    rewritten before each replay."""
+
+    def __init__(self, iters: int, reps: int = 4):
+        self.iters, self.reps = iters, reps
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def __call__(self, fn) -> float:
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(self.reps):
+                fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(self.iters):
+            self.flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            graph.replay()
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1) / self.reps)
+        times.sort()
+        return times[len(times) // 2]
+
+
+def _acts(rows, cols, std=1.0):
+    return (torch.randn(rows, cols, device="cuda") * std).to(BF16)
+
+
+def run(iters: int, only: str | None, small: bool) -> list[dict]:
+    _lib.load()
+    torch.manual_seed(0)
+    peaks = _peaks()
+    hbm_peak = peaks.get("hbm_gbs")
+    tf_peak = 2.0 * peaks["bf16_tflops"] if "bf16_tflops" in peaks else None  # timed alone: burst figure
+    t = Timer(iters)
+    out: list[dict] = []
+    M = 4096 if small else 32768
+
+    def hbm(name, shape, nbytes, fn):
+        ms = t(fn)
+        gbs = nbytes / ms / 1e6
+        out.append({"kernel": name, "shape": shape, "ms": round(ms, 4), "bound": "hbm", "achieved": round(gbs, 1),
+                    "unit": "GB/s", "algorithmic_bytes": nbytes, "peak": hbm_peak,
+                    "frac_of_measured": round(gbs / hbm_peak, 3) if hbm_peak else None,
+                    "frac_of_nominal_8000": round(gbs / 8000.0, 3)})
+        print(json.dumps(out[-1]), flush=True)
+
+    def tensor(name, shape, flops, fn):
+        ms = t(fn)
+        tf = flops / ms / 1e9
+        out.append({"kernel": name, "shape": shape, "ms": round(ms, 4), "bound": "tensor", "achieved": round(tf, 1),
+                    "unit": "TFLOP/s", "algorithmic_flops": flops, "peak": tf_peak,
+                    "peak_note": "2 x measured burst bf16 cuBLAS (no measured fp8 figure)",
+                    "frac_of_measured": round(tf / tf_peak, 3) if tf_peak else None,
+                    "frac_of_nominal_4500": round(tf / 4500.0, 3)})
+        print(json.dumps(out[-1]), flush=True)
+
+    if only in (None, "hbm"):
+        K = 2048
+        x = _acts(M, K)
+        n = M * K
+        hbm("mx_quantize rowwise", [M, K], int(n * 3.03125), lambda: ops.mx_quantize(x, rowwise=True))
+        hbm("mx_quantize row+col", [M, K], int(n * 4.0625), lambda: ops.mx_quantize(x, rowwise=True, colwise=True))
+        hbm("mx_quantize colwise", [M, K], int(n * 3.03125), lambda: ops.mx_quantize(x, rowwise=False, colwise=True))
+        W = _acts(8192, 2048, 0.02)
+        w1 = torch.randn(8, 8, device="cuda") * 0.1
+        w2 = torch.randn(1024, 256, device="cuda") * 0.02
+        hbm("lokr_merge_quantize row+col", [8192, 2048], int(8192 * 2048 * 4.0625),
+            lambda: ops.lokr_merge_quantize(W, w1, w2, 1.0, want_merged=False, rowwise=True, colwise=True))
+        dW = torch.randn(8192, 2048, device="cuda")
+        hbm("lokr_kron_backward (fp32 dW)", [8192, 2048], 8192 * 2048 * 4, lambda: ops.lokr_kron_backward(dW, w1, w2, 1.0))
+        BT, D = 8, 2048
+        HW = M // BT
+        xa, dy, y2 = _acts(M, D), _acts(M, D), _acts(M, D)
+        sc, sh, ga = _acts(BT, D, 0.1), _acts(BT, D, 0.1), _acts(BT, D, 0.1)
+        _, mean, rstd = ops.adaln_fwd(xa, sc, sh, 1e-6, HW)
+        hbm("adaln_fwd", [BT, HW, D], M * D * 4 + M * 8, lambda: ops.adaln_fwd(xa, sc, sh, 1e-6, HW))
+        hbm("adaln_bwd (dx+dscale+dshift)", [BT, HW, D], M * D * 6 + M * 8, lambda: ops.adaln_bwd(dy, xa, sc, mean, rstd, HW))
+        hbm("gated_add_fwd", [BT, HW, D], M * D * 6, lambda: ops.gated_add_fwd(xa, ga, y2, HW))
+        hbm("gated_add_bwd (dy+dgate)", [BT, HW, D], M * D * 6, lambda: ops.gated_add_bwd(dy, y2, ga, HW))
+        hid = (torch.randn(8, M // 8, 8, 128, device="cuda")).to(BF16)
+        gm = torch.randn_like(hid)
+        c = _acts(8, 8)
+        mask = (torch.rand(8, 128, device="cuda") > 0.3).to(BF16)
+        hbm("tlokr_rank_mix", list(hid.shape), hid.numel() * 4, lambda: ops.tlokr_rank_mix(hid, c, mask, False))
+        hbm("tlokr_rank_mix_wgrad", list(hid.shape), hid.numel() * 4, lambda: ops.tlokr_rank_mix_wgrad(gm, hid, mask))
+
+    if only in (None, "gemm"):
+        for (N, K) in [(2048, 2048), (6144, 2048), (8192, 2048), (2048, 8192)]:
+            x, w, gy = _acts(M, K), _acts(N, K, 0.02), _acts(M, N, 0.01)
+            xr, xc = ops.mx_quantize(x, rowwise=True, colwise=True)
+            wr, wc = ops.mx_quantize(w, rowwise=True, colwise=True)
+            gr, gc = ops.mx_quantize(gy, rowwise=True, colwise=True)
+            fl = 2.0 * M * N * K
+            y = torch.empty(M, N, dtype=BF16, device="cuda")
+            dx = torch.empty(M, K, dtype=BF16, device="cuda")
+            dw = torch.empty(N, K, dtype=torch.float32, device="cuda")
+            tensor("mx_gemm fwd", [M, N, K], fl, lambda: ops.mx_gemm(xr, wr, out=y))
+            tensor("mx_gemm dgrad", [M, K, N], fl, lambda: ops.mx_gemm(gr, wc, out=dx))
+            tensor("mx_gemm wgrad (fp32 out)", [N, K, M], fl, lambda: ops.mx_gemm(gc, xc, out_dtype=torch.float32, out=dw))
+            del x, w, gy, xr, xc, wr, wc, gr, gc, y, dx, dw
+        _lib.check_status_word(torch.device("cuda", torch.cuda.current_device()))
+    return out
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--only", choices=["gemm", "hbm"], default=None)
+    ap.add_argument("--small", action="store_true")
+    a = ap.parse_args()
+    run(a.iters, a.only, a.small)

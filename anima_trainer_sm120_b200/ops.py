@@ -75,6 +75,8 @@ def mx_quantize(
     if colwise:
         col_op = MXOperand(torch.empty((cols, rows), dtype=torch.uint8, device=dev),
                            _alloc_scales(cols, rows, layout, dev), layout)
+    if rows == 0 or cols == 0:   # empty tensors have no storage to point at
+        return row_op, col_op
     with torch.cuda.device(dev):
         check(_lib.load().anima_mx_quantize(
             ptr(x), rows, cols, x.stride(0) if rows > 1 else cols,

@@ -80,7 +80,7 @@ def test_adaln_golden_reference_kernel_outputs(golden):
 @pytest.mark.parametrize("B,H,W,D", [(8, 32, 32, 2048), (2, 8, 8, 768)])
 def test_autograd_ops_vs_eager(B, H, W, D):
     """FusedAdaLN / FusedGatedAdd (the reference's operator signatures) against eager autograd;
-    dscale / dgate are held to the reference's own criterion: no further from the fp32 truth than
+    dscale / dshift / dgate (sums over H*W) are held to the reference's own criterion: no further from the fp32 truth than
     1.5x eager's error (tests/sanity_adaln_kernel.py:58-65, 81-96)."""
     from anima_trainer_sm120_b200.adaln_kernel import FusedAdaLN, FusedGatedAdd
     torch.manual_seed(0)
@@ -111,8 +111,7 @@ def test_autograd_ops_vs_eager(B, H, W, D):
     _close(out_k, out_t.to(BF16))
     _close(out_k, out_e, 5e-2, 5e-2)                      # reference's own bf16 tolerance (:105)
     _close(grads_k[0], grads_t[0].to(BF16))               # dx
-    _close(grads_k[2], grads_t[2].to(BF16))               # dshift
-    for i in (1, 3):                                      # dscale, dgate
+    for i in (1, 2, 3):                                   # dscale, dshift, dgate: sums over H*W
         err_k = (grads_k[i].float() - grads_t[i]).abs().max().item()
         err_e = (grads_e[i].float() - grads_t[i]).abs().max().item()
         assert err_k <= max(1.5 * err_e, 1e-3), (i, err_k, err_e)
