@@ -1,6 +1,7 @@
 """Per-kernel throughput of ``libanima_b200.so`` at the production shapes.
 
     python -m anima_trainer_sm120_b200.kernel_bench [--iters 20] [--only gemm|hbm] [--small]
+                                                   [--pick TEXT] [--direct]
 
 Every kernel is timed alone with CUDA events on the launching stream (warm-ups, then the median
 over ``--iters`` replays of a CUDA graph holding 4 launches, an L2-sized buffer rewritten before
@@ -35,11 +36,24 @@ class Timer:
     between the two events; every tensor set here is larger than L2, and an L2-sized buffer is
     rewritten before each replay."""
 
-    def __init__(self, iters: int, reps: int = 4):
-        self.iters, self.reps = iters, reps
+    def __init__(self, iters: int, reps: int = 4, direct: bool = False):
+        self.iters, self.reps, self.direct = iters, reps, direct
         self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
 
     def __call__(self, fn) -> float:
+        if self.direct:                            # plain launches: what a profiler capture wants
+            fn()
+            times = []
+            for _ in range(self.iters):
+                self.flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                e1.synchronize()
+                times.append(e0.elapsed_time(e1))
+            times.sort()
+            return times[len(times) // 2]
         for _ in range(3):
             fn()
         torch.cuda.synchronize()
@@ -66,17 +80,22 @@ def _acts(rows, cols, std=1.0):
     return (torch.randn(rows, cols, device="cuda") * std).to(BF16)
 
 
-def run(iters: int, only: str | None, small: bool) -> list[dict]:
+def run(iters: int, only: str | None, small: bool, pick: str | None = None, direct: bool = False) -> list[dict]:
     _lib.load()
     torch.manual_seed(0)
     peaks = _peaks()
     hbm_peak = peaks.get("hbm_gbs")
     tf_peak = 2.0 * peaks["bf16_tflops"] if "bf16_tflops" in peaks else None  # timed alone: burst figure
-    t = Timer(iters)
+    t = Timer(iters, direct=direct)
     out: list[dict] = []
     M = 4096 if small else 32768
 
+    def wanted(name, shape):
+        return pick is None or pick in f"{name} {shape}"
+
     def hbm(name, shape, nbytes, fn):
+        if not wanted(name, shape):
+            return
         ms = t(fn)
         gbs = nbytes / ms / 1e6
         out.append({"kernel": name, "shape": shape, "ms": round(ms, 4), "bound": "hbm", "achieved": round(gbs, 1),
@@ -86,6 +105,8 @@ def run(iters: int, only: str | None, small: bool) -> list[dict]:
         print(json.dumps(out[-1]), flush=True)
 
     def tensor(name, shape, flops, fn):
+        if not wanted(name, shape):
+            return
         ms = t(fn)
         tf = flops / ms / 1e9
         out.append({"kernel": name, "shape": shape, "ms": round(ms, 4), "bound": "tensor", "achieved": round(tf, 1),
@@ -148,5 +169,7 @@ if __name__ == "__main__":
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--only", choices=["gemm", "hbm"], default=None)
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--pick", default=None, help="run only entries whose 'name [shape]' contains this text")
+    ap.add_argument("--direct", action="store_true", help="plain launches instead of CUDA-graph replays")
     a = ap.parse_args()
-    run(a.iters, a.only, a.small)
+    run(a.iters, a.only, a.small, a.pick, a.direct)
