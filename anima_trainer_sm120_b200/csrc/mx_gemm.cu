@@ -6,27 +6,29 @@
 // e8m0 scale per 32 K-elements in the 128x4 tiled layout (see anima_b200.h), so the
 // forward, dgrad and wgrad GEMMs are all this one "TN" form.
 //
-// Design (one persistent CTA per SM, 192 threads, warp-specialised):
-//   warp 0  TMA producer: per K-block of 128 one 128x128 A box and one BNx128 B box
-//           (128-byte swizzle) plus the 512-byte scale chunks (bulk copies), all
-//           completing on the stage's "full" mbarrier; 4-stage shared-memory ring.
-//   warp 1  MMA issuer: copies the stage's scale chunks shared -> tensor memory
-//           (tcgen05.cp 32x128b.warpx4), issues four
-//           tcgen05.mma.kind::mxf8f6f4.block_scale (M128 x N{128,256} x K32) per
-//           stage, and frees the stage / publishes the accumulator with
-//           tcgen05.commit. Accumulators live in tensor memory (fp32).
-//   warps 2-5 epilogue: tcgen05.ld the 128 x BN accumulator in 32-column chunks,
-//           add bias, round to bf16 (or keep fp32) and store 64/128 contiguous bytes
-//           per thread.
-// Two accumulator buffers let the epilogue of tile i overlap the main loop of tile
-// i+1. For BN = 256 the 512 tensor-memory columns cannot hold two full buffers plus
-// the scale columns, so buffer 1 starts 32 columns before the end of buffer 0 and
-// the epilogue always drains those shared 32 columns first, then releases the MMA
-// warp. Every wait is bounded; on a timeout the kernel raises *status, lets copies
-// in flight land, frees its tensor memory and returns.
-// Tensor-pipe bound: 2*M*N*K flop; no TMA multicast is used anywhere.
+// Two kernel families, both persistent and warp-specialised (192 threads: warp 0 TMA producer,
+// warp 1 MMA issuer, warps 2-5 epilogue), accumulating in tensor memory (fp32):
+//
+//  * mx_gemm2_kernel — the main one (M > 128 and N > 128): a cluster of two CTAs owns a 256 x 192
+//    tile and issues tcgen05.mma.cta_group::2 (M256 x N192 x K32); see the comment above it.
+//  * mx_gemm_kernel<BN> — one CTA per 128 x BN tile (BN = 128 or 256) for small or narrow problems:
+//      warp 0  per K-block of 128 one 128x128 A box and one BNx128 B box (128-byte swizzle) plus the
+//              512-byte scale chunks (bulk copies), all completing on the stage's "full" mbarrier;
+//              4-stage shared-memory ring.
+//      warp 1  copies the stage's scale chunks shared -> tensor memory (tcgen05.cp 32x128b.warpx4),
+//              issues four tcgen05.mma.kind::mxf8f6f4.block_scale per stage, frees the stage and
+//              publishes the accumulator with tcgen05.commit.
+//      warps 2-5  tcgen05.ld the accumulator in 32-column chunks, add bias, round to bf16 (or keep
+//              fp32) and store 64/128 contiguous bytes per thread.
+//    Two accumulator buffers let the epilogue of tile i overlap the main loop of tile i+1. For
+//    BN = 256 the 512 tensor-memory columns cannot hold two full buffers plus the scale columns, so
+//    buffer 1 starts 32 columns before the end of buffer 0 and the epilogue drains those shared
+//    columns first, then releases the MMA warp.
+// Every wait is bounded; on a timeout a kernel raises *status, lets copies in flight land, frees its
+// tensor memory and returns. Tensor-pipe bound: 2*M*N*K flop. No TMA multicast is used anywhere.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -87,10 +89,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: false if another role already aborted or ~2 s passed.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// sleep_ns > 0 backs off between polls (for long waits such as the epilogue's, to leave power to the tensor pipe).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          uint32_t sleep_ns = 0) {
   uint64_t t0 = 0;
   for (uint32_t spins = 0;; ++spins) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (sleep_ns) __nanosleep(sleep_ns);
     if ((spins & 63u) == 63u) {
       if (*abort_flag) return false;
       const uint64_t now = global_timer_ns();
@@ -173,6 +178,43 @@ struct GemmParams {
   int m_tiles, n_tiles, k_blocks;
   int sfa_rt, sfb_rt;  // number of 128-row scale tiles of A and B
 };
+
+
+// Epilogue store of one 32-column accumulator chunk of one row: bias, rounding, predicated 16-byte stores.
+__device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int col, const uint32_t (&v)[32]) {
+  if (row >= p.M || col >= p.N) return;
+  float f[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+  if (p.bias) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      if (col + j < p.N) {
+        float b[8];
+        unpack8(*reinterpret_cast<const uint4*>(p.bias + col + j), b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[j + e] += b[e];
+      }
+    }
+  }
+  if (p.out_fp32) {
+    float* dst = static_cast<float*>(p.c) + static_cast<int64_t>(row) * p.ldc + col;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4)
+      if (col + j < p.N) *reinterpret_cast<float4*>(dst + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+  } else {
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + static_cast<int64_t>(row) * p.ldc + col;
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      if (col + j < p.N) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = f[j + e];
+        *reinterpret_cast<uint4*>(dst + j) = pack8(o);
+      }
+    }
+  }
+}
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -311,40 +353,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           __syncwarp();
           if (lane == 0) mbar_arrive(acc_free_bar);
         }
-        const int col = nt * BN + chunk * 32;
-        if (row < p.M && col < p.N) {
-          float f[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
-          if (p.bias) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (col + j < p.N) {
-                float b[8];
-                unpack8(*reinterpret_cast<const uint4*>(p.bias + col + j), b);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) f[j + e] += b[e];
-              }
-            }
-          }
-          if (p.out_fp32) {
-            float* dst = static_cast<float*>(p.c) + static_cast<int64_t>(row) * p.ldc + col;
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              if (col + j < p.N) *reinterpret_cast<float4*>(dst + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
-          } else {
-            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + static_cast<int64_t>(row) * p.ldc + col;
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (col + j < p.N) {
-                float o[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = f[j + e];
-                *reinterpret_cast<uint4*>(dst + j) = pack8(o);
-              }
-            }
-          }
-        }
+        store_chunk(p, row, nt * BN + chunk * 32, v);
       }
     }
   }
@@ -361,6 +370,356 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::kTmemCols) : "memory");
+  }
+}
+
+// ================================================================== 2-CTA variant
+// A cluster of two CTAs (two SMs) owns one 256 x 192 output tile. CTA r stages rows
+// [128 r, 128 r + 128) of the A tile and rows [96 r, 96 r + 96) of the B tile, so every
+// tcgen05.mma (cta_group::2, M256 x N192 x K32) is fed by 7 KB of shared-memory fill per
+// SM (the one-CTA kernel needs 12 KB per M128 x N256 x K32), and 7 stages are in flight.
+// N = 192 leaves room in tensor memory for two DISJOINT accumulator buffers (2 x 192
+// columns) next to the 12 scale columns, so the next tile's MMAs start the moment the
+// previous tile's are issued; with N = 256 the buffers must share columns and the tensor
+// pipe idles at every tile boundary until the epilogue has drained them.
+// Only the leader CTA (cluster rank 0) issues scale copies, MMAs and commits; the commits
+// are delivered to the mbarriers of both CTAs, and both CTAs' TMA loads complete on the
+// leader's "full" barrier. Each CTA drains its own 128 accumulator rows. The loads carry no
+// multicast: each CTA fetches its own boxes.
+constexpr int kStages2 = 6;
+constexpr int kBN2 = 192;
+
+struct Cfg2 {
+  static constexpr int kABytes = 128 * BK;
+  static constexpr int kBBytes = (kBN2 / 2) * BK;  // this CTA's half of the B rows
+  static constexpr int kAcc1Col = kBN2;            // second accumulator buffer
+  static constexpr int kSfaCol = 2 * kBN2;         // 4 columns
+  static constexpr int kSfbCol = kSfaCol + 4;      // 8 columns: two 128-column chunks
+  static constexpr int kTmemCols = 512;
+  static constexpr int kSfBytes = kSfChunk * 3;  // SFA chunk + both SFB chunks
+  static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
+  static constexpr int kStoreBytes = 128 * 128;  // one 128-row x 32-column output chunk (fp32 worst case)
+  static constexpr int kSmemBytes = kStages2 * kStageBytes + 2 * kStoreBytes + 1024 + 256;
+  static constexpr uint32_t kTxBytes = 2u * kStageBytes;  // both CTAs land on the leader's barrier
+};
+
+// True in exactly one (converged) lane of the warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.b32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma2_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma2_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int c0, int c1,
+                                             int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tc2_commit_both(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(static_cast<uint16_t>(3))
+               : "memory");
+}
+// One K-block of the pair kernel as straight-line PTX: scale chunks shared -> tensor memory, four
+// M256 x N192 x K32 block-scaled MMAs (scale-factor id k selects the k-th byte of each scale word;
+// +32 bytes along K = +2 in the descriptor's 16-byte address field), then the commit that frees the
+// stage in both CTAs. Descriptor high words: stride 1024 B (operands, 128-byte swizzle) / 128 B (scales).
+__device__ __forceinline__ void tc2_kblock(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t sf_lo, uint32_t sfa_t,
+                                           uint32_t sfb_t, uint32_t sfb_use, uint32_t accumulate, uint32_t empty_bar) {
+  constexpr uint32_t kOpHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+  constexpr uint32_t kSfHi = (128u >> 4) | (1u << 14);
+  constexpr uint32_t kI = (static_cast<uint32_t>(kBN2 >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>(256 >> 4) << 24);
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, pt;\n\t"
+      ".reg .b32 t;\n\t"
+      ".reg .b64 da, db, ds;\n\t"
+      ".reg .b16 m;\n\t"
+      "mov.b16 m, 3;\n\t"
+      "setp.ne.b32 p, %7, 0;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      "mov.b64 ds, {%3, %10};\n\t"
+      "tcgen05.cp.cta_group::2.32x128b.warpx4 [%4], ds;\n\t"
+      "add.u32 t, %3, 32;\n\t"
+      "mov.b64 ds, {t, %10};\n\t"
+      "tcgen05.cp.cta_group::2.32x128b.warpx4 [%5], ds;\n\t"
+      "add.u32 t, %3, 64;\n\t"
+      "mov.b64 ds, {t, %10};\n\t"
+      "add.u32 t, %5, 4;\n\t"
+      "tcgen05.cp.cta_group::2.32x128b.warpx4 [t], ds;\n\t"
+      "mov.b64 da, {%1, %9};\n\t"
+      "mov.b64 db, {%2, %9};\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], da, db, %11, [%4], [%6], p;\n\t"
+      "add.u32 t, %1, 2;\n\t"
+      "mov.b64 da, {t, %9};\n\t"
+      "add.u32 t, %2, 2;\n\t"
+      "mov.b64 db, {t, %9};\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], da, db, %12, [%4], [%6], pt;\n\t"
+      "add.u32 t, %1, 4;\n\t"
+      "mov.b64 da, {t, %9};\n\t"
+      "add.u32 t, %2, 4;\n\t"
+      "mov.b64 db, {t, %9};\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], da, db, %13, [%4], [%6], pt;\n\t"
+      "add.u32 t, %1, 6;\n\t"
+      "mov.b64 da, {t, %9};\n\t"
+      "add.u32 t, %2, 6;\n\t"
+      "mov.b64 db, {t, %9};\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], da, db, %14, [%4], [%6], pt;\n\t"
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%8], m;\n\t"
+      "}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(sf_lo), "r"(sfa_t), "r"(sfb_t), "r"(sfb_use), "r"(accumulate),
+        "r"(empty_bar), "r"(kOpHi), "r"(kSfHi), "r"(kI), "r"(kI | (1u << 29) | (1u << 4)),
+        "r"(kI | (2u << 29) | (2u << 4)), "r"(kI | (3u << 29) | (3u << 4))
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
+                const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
+  using C = Cfg2;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ volatile int abort_flag;
+  __shared__ uint32_t tmem_base_slot;
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t store_base = base + kStages2 * (Cfg2::kABytes + Cfg2::kBBytes);  // 1024-aligned staging for C
+  const uint32_t sf_base = store_base + 2 * Cfg2::kStoreBytes;
+  const uint32_t bar_base = sf_base + kStages2 * Cfg2::kSfBytes;
+  auto a_smem = [&](int s) { return base + s * (Cfg2::kABytes + Cfg2::kBBytes); };
+  auto b_smem = [&](int s) { return a_smem(s) + Cfg2::kABytes; };
+  auto sfa_smem = [&](int s) { return sf_base + s * Cfg2::kSfBytes; };
+  auto sfb_smem = [&](int s) { return sfa_smem(s) + kSfChunk; };
+  auto full_bar = [&](int s) { return bar_base + 8 * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8 * (kStages2 + s); };
+  auto acc_full_bar = [&](int s) { return bar_base + 8 * (2 * kStages2 + s); };
+  auto acc_empty_bar = [&](int s) { return bar_base + 8 * (2 * kStages2 + 2 + s); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages2; ++s) {
+      mbar_init(full_bar(s), 1);   // the leader producer's arrive.expect_tx; bytes come from both CTAs
+      mbar_init(empty_bar(s), 1);  // one multicast commit
+    }
+    mbar_init(acc_full_bar(0), 1);
+    mbar_init(acc_full_bar(1), 1);
+    mbar_init(acc_empty_bar(0), 8);  // 4 epilogue warps of each CTA arrive on the leader's barriers
+    mbar_init(acc_empty_bar(1), 8);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfa) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfb) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
+  }
+  if (warp == 1) {  // the same warp of both CTAs performs the pair allocation
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"(C::kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before any remote arrive or TMA completion
+  tc_fence_after();
+  // The kernel owns all 512 columns, so the allocation can only start at column 0; using the constant keeps
+  // every tensor-memory address warp-uniform. Anything else is reported through *status and nothing runs.
+  const uint32_t tmem_alloc = tmem_base_slot;
+  constexpr uint32_t tmem_base = 0;
+  const int total_tiles = (tmem_alloc == 0) ? p.m_tiles * p.n_tiles : 0;  // 256 x 192 tiles
+  if (tmem_alloc != 0 && threadIdx.x == 0 && p.status) atomicExch(p.status, 2);
+
+  // Warps 0 and 1 run their loops with all 32 lanes so that every loop variable is warp-uniform (the
+  // compiler then keeps descriptors and addresses in uniform registers); only the asynchronous
+  // instructions themselves are issued by one elected lane.
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      const uint32_t leader_full0 = map_to_cta(full_bar(0), 0);
+      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+        const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
+        const int row_a = mt * 256 + static_cast<int>(rank) * 128;
+        const int row_b = nt * kBN2 + static_cast<int>(rank) * (kBN2 / 2);
+        const int sfa_rt = mt * 2 + static_cast<int>(rank), sfb_rt = (nt * kBN2) >> 7;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_try_wait(empty_bar(s), ph ^ 1u)) ok = mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          if (elect_one()) {
+            if (rank == 0) mbar_expect_tx(full_bar(s), Cfg2::kTxBytes);
+            const uint32_t leader_full = leader_full0 + 8 * s;
+            tma2_load_2d(a_smem(s), &map_a, leader_full, kb * BK, row_a);
+            tma2_load_2d(b_smem(s), &map_b, leader_full, kb * BK, row_b);
+            tma2_load_3d(sfa_smem(s), &map_sfa, leader_full, 0, kb, sfa_rt);
+            tma2_load_3d(sfb_smem(s), &map_sfb, leader_full, 0, kb, sfb_rt);  // the two 128-column chunks it spans
+          }
+          __syncwarp();
+          if (++s == kStages2) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (rank == 0) {
+      const uint32_t a_lo0 = (a_smem(0) >> 4) & 0x3fffu;
+      const uint32_t sf_lo0 = (sfa_smem(0) >> 4) & 0x3fffu;
+      const uint32_t sfa_t = tmem_base + C::kSfaCol, sfb_t = tmem_base + C::kSfbCol;
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      int it = 0;
+      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++it) {
+        const int as = it & 1;
+        // the epilogues of both CTAs must have drained this buffer (used by tile it - 2)
+        ok = __all_sync(0xffffffffu, mbar_wait(acc_empty_bar(as), ((it >> 1) & 1u) ^ 1u, &abort_flag));
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (as ? C::kAcc1Col : 0);
+        const int nt = tile % p.n_tiles;
+        // a 192-column tile starts 0 or 64 columns into its first 128-column scale chunk: 32 columns per TMEM column
+        const uint32_t sfb_use = sfb_t + (((nt * kBN2) & 127) >> 5);
+        uint32_t acc = 0;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_try_wait(full_bar(s), ph)) ok = mbar_wait(full_bar(s), ph, &abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_lo = a_lo0 + s * ((Cfg2::kABytes + Cfg2::kBBytes) >> 4);
+          const uint32_t sf_lo = sf_lo0 + s * (Cfg2::kSfBytes >> 4);
+          if (elect_one())
+            tc2_kblock(d_tmem, a_lo, a_lo + (Cfg2::kABytes >> 4), sf_lo, sfa_t, sfb_t, sfb_use, acc, empty_bar(s));
+          __syncwarp();
+          acc = 1;
+          if (++s == kStages2) { s = 0; ph ^= 1u; }
+        }
+        if (ok && elect_one()) tc2_commit_both(acc_full_bar(as));
+        __syncwarp();
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+    // Each 128-row x 32-column chunk goes tensor memory -> registers -> (bias, rounding) -> a swizzled
+    // shared-memory staging buffer -> one TMA store, which writes full lines and clips rows / columns that
+    // lie outside C. Two staging buffers alternate; named barrier 1 joins the 128 epilogue threads.
+    const int quad = warp & 3;
+    const int r_in = quad * 32 + lane;  // row inside this CTA's 128 accumulator rows
+    const bool issuer = threadIdx.x == 64;
+    const uint32_t leader_empty[2] = {map_to_cta(acc_empty_bar(0), 0), map_to_cta(acc_empty_bar(1), 0)};
+    bool ok = true;
+    int it = 0;
+    uint32_t buf = 0;
+    for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++it) {
+      const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
+      const int as = it & 1;
+      if (!mbar_wait(acc_full_bar(as), (it >> 1) & 1u, &abort_flag, 200)) { ok = false; break; }
+      tc_fence_after();
+      const int row0 = mt * 256 + static_cast<int>(rank) * 128;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + (as ? C::kAcc1Col : 0);
+#pragma unroll 1
+      for (int chunk = 0; chunk < kBN2 / 32; ++chunk, buf ^= 1u) {
+        uint32_t v[32];
+        tc_ld32(t_row + chunk * 32, v);
+        tc_wait_ld();
+        if (chunk == kBN2 / 32 - 1) {  // buffer fully read: hand it back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(leader_empty[as]);
+        }
+        const int col0 = nt * kBN2 + chunk * 32;
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+        if (p.bias) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (col0 + j < p.N) {
+              float bv[8];
+              unpack8(*reinterpret_cast<const uint4*>(p.bias + col0 + j), bv);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[j + e] += bv[e];
+            }
+          }
+        }
+        const uint32_t stage = store_base + buf * Cfg2::kStoreBytes;
+        // the store that last read this staging buffer (two chunks ago) was waited for by the issuer
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (p.out_fp32) {  // 128-byte rows, 128-byte swizzle: 16-byte piece j of row r sits at piece j ^ (r & 7)
+          const uint32_t rb = stage + r_in * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(rb + (((j ^ (r_in & 7))) << 4)), "f"(f[4 * j]),
+                         "f"(f[4 * j + 1]), "f"(f[4 * j + 2]), "f"(f[4 * j + 3])
+                         : "memory");
+          }
+        } else {  // 64-byte rows, 64-byte swizzle: piece j of row r sits at piece j ^ ((r >> 1) & 3)
+          const uint32_t rb = stage + r_in * 64;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float o[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = f[8 * j + e];
+            const uint4 w = pack8(o);
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(rb + ((j ^ ((r_in >> 1) & 3)) << 4)), "r"(w.x),
+                         "r"(w.y), "r"(w.z), "r"(w.w)
+                         : "memory");
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the TMA engine
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (issuer) {
+          asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&map_c),
+                       "r"(stage), "r"(col0), "r"(row0)
+                       : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // the other buffer may be rewritten
+        }
+      }
+    }
+    if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncwarp();
+  if (abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, 1);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA releases shared or tensor memory while its peer may still use it
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_alloc), "r"(C::kTmemCols) : "memory");
   }
 }
 
@@ -393,6 +752,75 @@ bool make_map(CUtensorMap* map, const uint8_t* ptr, int64_t rows, int64_t k, int
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(ptr), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// TILED scale tensor viewed as u32 [row_tiles][k_blocks][128]: one 512-byte chunk per (row tile, K-block);
+// box = box_rt chunks of consecutive row tiles at one K-block. Row tiles past the end read as 0.
+bool make_sf_map(CUtensorMap* map, const uint8_t* ptr, int64_t row_tiles, int64_t k_blocks, int box_rt) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(k_blocks), static_cast<cuuint64_t>(row_tiles)};
+  const cuuint64_t strides[2] = {512, static_cast<cuuint64_t>(512 * k_blocks)};
+  const cuuint32_t box[3] = {128, 1, static_cast<cuuint32_t>(box_rt)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<uint8_t*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// C [M, N] (bf16 or fp32, row pitch ldc) for the epilogue's TMA stores: box = 32 columns x 128 rows, swizzled
+// like the staging buffer (64-byte rows for bf16, 128-byte rows for fp32). Stores outside [M, N] are dropped.
+bool make_c_map(CUtensorMap* map, const GemmParams& p) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const int elt = p.out_fp32 ? 4 : 2;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(p.N), static_cast<cuuint64_t>(p.M)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(p.ldc) * elt};
+  const cuuint32_t box[2] = {32, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, p.out_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.c, dims, strides,
+            box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, p.out_fp32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmParams p, cudaStream_t s) {
+  static std::once_flag once;
+  static cudaError_t attr_rc = cudaSuccess;
+  std::call_once(once, [] {
+    attr_rc = cudaFuncSetAttribute(mx_gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg2::kSmemBytes);
+  });
+  ANIMA_REQUIRE(attr_rc == cudaSuccess, ANIMA_E_CUDA, "mx_gemm: cannot reserve %d bytes of shared memory: %s",
+                Cfg2::kSmemBytes, cudaGetErrorString(attr_rc));
+  CUtensorMap ma, mb, msa, msb, mc;
+  ANIMA_REQUIRE(make_map(&ma, a_codes, p.M, p.K, 128) && make_map(&mb, b_codes, p.N, p.K, kBN2 / 2) &&
+                    make_sf_map(&msa, p.a_scales, p.sfa_rt, p.k_blocks, 1) &&
+                    make_sf_map(&msb, p.b_scales, p.sfb_rt, p.k_blocks, 2) && make_c_map(&mc, p),
+                ANIMA_E_CUDA, "mx_gemm: cuTensorMapEncodeTiled failed (driver entry point missing or bad operand)");
+  p.m_tiles = static_cast<int>(ceil_div(p.M, 256));
+  p.n_tiles = static_cast<int>(ceil_div(p.N, kBN2));
+  const int tiles = p.m_tiles * p.n_tiles;
+  const int pairs = std::max(1, std::min(tiles, sm_count() / 2));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = Cfg2::kSmemBytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t rc = cudaLaunchKernelEx(&cfg, mx_gemm2_kernel, ma, mb, msa, msb, mc, p);
+  ANIMA_REQUIRE(rc == cudaSuccess, ANIMA_E_CUDA, "mx_gemm: cluster launch failed: %s", cudaGetErrorString(rc));
+  return ANIMA_OK;
+}
+
+// 0 = choose by shape, 1 = one CTA per tile, 2 = CTA pairs (ANIMA_MX_GEMM_VARIANT, read per call; for tests).
+int forced_variant() {
+  const char* v = getenv("ANIMA_MX_GEMM_VARIANT");
+  return v ? atoi(v) : 0;
 }
 
 template <int BN>
@@ -434,10 +862,6 @@ extern "C" int anima_mx_gemm(const uint8_t* a_codes, const uint8_t* a_scales, co
   ANIMA_REQUIRE(aligned16(a_codes) && aligned16(b_codes) && aligned16(a_scales) && aligned16(b_scales) &&
                     aligned16(c) && (!bias || aligned16(bias)),
                 ANIMA_E_ALIGN, "mx_gemm: all buffers must be 16-byte aligned");
-  CUtensorMap ma, mb;
-  const bool wide = N > 128;
-  ANIMA_REQUIRE(make_map(&ma, a_codes, M, K, BM) && make_map(&mb, b_codes, N, K, wide ? 256 : 128), ANIMA_E_CUDA,
-                "mx_gemm: cuTensorMapEncodeTiled failed (driver entry point missing or bad operand)");
   GemmParams p{};
   p.a_scales = a_scales;
   p.b_scales = b_scales;
@@ -454,5 +878,13 @@ extern "C" int anima_mx_gemm(const uint8_t* a_codes, const uint8_t* a_scales, co
   p.sfa_rt = static_cast<int>(ceil_div(M, 128));
   p.sfb_rt = static_cast<int>(ceil_div(N, 128));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool wide = N > 128;
+  const int variant = forced_variant();
+  // CTA pairs pay off once a 256 x 256 tile is mostly full; small or narrow problems keep one CTA per tile.
+  const bool pair = variant == 2 || (variant == 0 && wide && M > 128);
+  if (pair) return launch_pair(a_codes, b_codes, p, s);
+  CUtensorMap ma, mb;
+  ANIMA_REQUIRE(make_map(&ma, a_codes, M, K, BM) && make_map(&mb, b_codes, N, K, wide ? 256 : 128), ANIMA_E_CUDA,
+                "mx_gemm: cuTensorMapEncodeTiled failed (driver entry point missing or bad operand)");
   return wide ? launch<256>(ma, mb, p, s) : launch<128>(ma, mb, p, s);
 }

@@ -40,6 +40,13 @@ def _oracle_product(a, b, bias=None, out_bf16=True):
                      None if bias is None else bias.float().cpu().numpy(), out_bf16=out_bf16)
 
 
+@pytest.fixture(params=["1", "2"], ids=["one-cta-tiles", "cta-pair-tiles"])
+def variant(request, monkeypatch):
+    """Run a test once per GEMM kernel family (the library reads the variable on every call)."""
+    monkeypatch.setenv("ANIMA_MX_GEMM_VARIANT", request.param)
+    return request.param
+
+
 def _gemm_case(M, N, K, seed, bias=False, out_dtype=BF16):
     ops, lib = _ops()
     x = _acts(M, K, seed).cuda()
@@ -76,7 +83,7 @@ def test_golden_operands(golden):
     (384, 128, 2048),    # narrow kernel, long K (ring wraps 4x)
     (1024, 2048, 256),   # 64 tiles
 ])
-def test_tile_aligned_shapes(M, N, K):
+def test_tile_aligned_shapes(M, N, K, variant):
     _gemm_case(M, N, K, seed=M + N + K)
 
 
@@ -87,28 +94,29 @@ def test_tile_aligned_shapes(M, N, K):
     (257, 384, 416),     # N = 1.5 wide tiles: second scale chunk of the last tile is clamped
     (4096, 2048, 1024),  # cross-attn k/v shape (8 x 512 text tokens)
 ])
-def test_ragged_shapes(M, N, K):
+def test_ragged_shapes(M, N, K, variant):
     _gemm_case(M, N, K, seed=M * 3 + N)
 
 
-def test_more_tiles_than_sms_exercises_both_accumulator_buffers():
-    # 20480/128 * 512/256 = 320 tiles on <= 148 persistent CTAs: every CTA runs >= 2 tiles
+def test_more_tiles_than_sms_exercises_both_accumulator_buffers(variant):
+    # 320 (one CTA) / 160 (pair) tiles on 148 CTAs / 74 pairs: every CTA runs >= 2 tiles
     _gemm_case(20480, 512, 256, seed=11)
+    _gemm_case(40960, 512, 128, seed=13)
     _gemm_case(20480, 128, 384, seed=12)
 
 
-def test_bias_and_fp32_output():
+def test_bias_and_fp32_output(variant):
     _gemm_case(256, 512, 256, seed=5, bias=True)
     _gemm_case(256, 512, 256, seed=6, bias=True, out_dtype=torch.float32)
     _gemm_case(200, 136, 96, seed=7, out_dtype=torch.float32)
 
 
-def test_scale_bytes_are_applied_per_block():
+def test_scale_bytes_are_applied_per_block(variant):
     """Doubling one operand's scale byte for a single (row-tile, K-block) changes exactly the rows
     of that block's contribution: checks the shared->tensor-memory scale path and the sf_id
     selection of each of the four K sub-blocks."""
     ops, lib = _ops()
-    M, N, K = 128, 256, 256
+    M, N, K = 256, 256, 256
     x = _acts(M, K, 1, outliers=False).cuda()
     w = _acts(N, K, 2, std=0.02, outliers=False).cuda()
     xa, _ = ops.mx_quantize(x, rowwise=True, layout=0)
@@ -117,6 +125,7 @@ def test_scale_bytes_are_applied_per_block():
         for who in ("a", "b"):
             xs, ws = xa.scales.clone(), wb.scales.clone()
             (xs if who == "a" else ws)[5:40, kb] += 1
+            (xs if who == "a" else ws)[130:250, kb] += 2
             a2 = ops.MXOperand(xa.codes, xs, 0)
             b2 = ops.MXOperand(wb.codes, ws, 0)
             c = ops.mx_gemm(ops.mx_retile(a2), ops.mx_retile(b2), out_dtype=torch.float32)
