@@ -39,11 +39,19 @@ struct MergeLoader {
     const int64_t i = r / vp, p = r - i * vp;
     const int64_t j = c / vq, q = c - j * vq;  // vq % 8 == 0: the 8 columns share j
     const float a = to_f32(w1[i * uq + j]);
-    float wv[8], o[8];
+    float wv[8], o[8], f2[8];
     unpack8(ldg_stream16(w + r * K + c), wv);
+    const F* w2p = w2 + p * vq + q;  // 8 consecutive factors: vq % 8 == 0 keeps them 16/32-byte aligned
+    if constexpr (sizeof(F) == 4) {
+      const float4 lo = *reinterpret_cast<const float4*>(w2p), hi = *reinterpret_cast<const float4*>(w2p + 4);
+      f2[0] = lo.x; f2[1] = lo.y; f2[2] = lo.z; f2[3] = lo.w;
+      f2[4] = hi.x; f2[5] = hi.y; f2[6] = hi.z; f2[7] = hi.w;
+    } else {
+      unpack8(*reinterpret_cast<const uint4*>(w2p), f2);
+    }
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      const float diff = __bfloat162float(__float2bfloat16_rn(a * to_f32(w2[p * vq + q + e])));
+      const float diff = __bfloat162float(__float2bfloat16_rn(a * f2[e]));
       o[e] = fmaf(alpha, diff, wv[e]);
     }
     const uint4 packed = pack8(o);
@@ -208,9 +216,9 @@ extern "C" int anima_lokr_merge_quantize(const void* w, const void* w1, const vo
   ANIMA_REQUIRE(!row || K % 32 == 0, ANIMA_E_SHAPE, "lokr_merge_quantize: rowwise needs K %% 32 == 0");
   ANIMA_REQUIRE(!col || N % 32 == 0, ANIMA_E_SHAPE, "lokr_merge_quantize: columnwise needs N %% 32 == 0");
   ANIMA_REQUIRE(ceil_div(N, kTile) <= 65535, ANIMA_E_TOO_LARGE, "lokr_merge_quantize: N too large");
-  ANIMA_REQUIRE(aligned16(w) && (!merged || aligned16(merged)) && (!row || aligned16(codes_row)) &&
+  ANIMA_REQUIRE(aligned16(w) && aligned16(w2) && (!merged || aligned16(merged)) && (!row || aligned16(codes_row)) &&
                     (!col || aligned16(codes_colT)),
-                ANIMA_E_ALIGN, "lokr_merge_quantize: W, merged and code buffers must be 16-byte aligned");
+                ANIMA_E_ALIGN, "lokr_merge_quantize: W, w2, merged and code buffers must be 16-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (factors_are_fp32)
     launch_merge<float>(w, w1, w2, alpha, N, K, up, uq, merged, codes_row, scales_row, codes_colT,

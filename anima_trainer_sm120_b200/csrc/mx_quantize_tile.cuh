@@ -50,7 +50,7 @@ __device__ __forceinline__ int tiled_offset(int r, int j) {
 // Loader: __device__ uint4 operator()(int64_t row, int64_t col) const — the 8 bf16
 // values at (row, col .. col+7), both in range.
 template <bool ROW, bool COL, class Loader>
-__global__ void __launch_bounds__(kThreads) mx_quantize_kernel(const QuantParams p, const Loader load) {
+__global__ void __launch_bounds__(kThreads, COL ? 3 : 4) mx_quantize_kernel(const QuantParams p, const Loader load) {
   __shared__ uint4 tile[COL ? kTile * 16 : 1];  // 128 rows x 256 B
   __shared__ __align__(16) uint8_t sc_row[ROW ? 512 : 16];
   __shared__ __align__(16) uint8_t sc_col[COL ? 512 : 16];
@@ -112,13 +112,14 @@ __global__ void __launch_bounds__(kThreads) mx_quantize_kernel(const QuantParams
     const int cp = t & 63;  // column pair
     const int g = t >> 6;   // 32-row group within the tile
     const uint32_t* tile32 = reinterpret_cast<const uint32_t*>(tile);
+    // one pass over the column pair: 32 packed bf16x2 words stay in registers for amax and conversion
+    uint32_t cw[32];
     float amax0 = 0.f, amax1 = 0.f;
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
-      const uint32_t w = tile32[(32 * g + i) * 64 + cp];
-      const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
-      amax0 = fmaxf(amax0, fabsf(v.x));
-      amax1 = fmaxf(amax1, fabsf(v.y));
+      cw[i] = tile32[(32 * g + i) * 64 + cp];
+      amax0 = fmaxf(amax0, fabsf(__uint_as_float(cw[i] << 16)));
+      amax1 = fmaxf(amax1, fabsf(__uint_as_float(cw[i] & 0xffff0000u)));
     }
     const int e0 = mx_exponent(fmaxf(amax0, kAmaxFloor));
     const int e1 = mx_exponent(fmaxf(amax1, kAmaxFloor));
@@ -129,28 +130,37 @@ __global__ void __launch_bounds__(kThreads) mx_quantize_kernel(const QuantParams
       float a[4], b[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const uint32_t w = tile32[(32 * g + 4 * q + k) * 64 + cp];
-        const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
-        a[k] = v.x * inv0;
-        b[k] = v.y * inv1;
+        a[k] = __uint_as_float(cw[4 * q + k] << 16) * inv0;
+        b[k] = __uint_as_float(cw[4 * q + k] & 0xffff0000u) * inv1;
       }
       w0[q] = e4m3x2(a[0], a[1]) | (e4m3x2(a[2], a[3]) << 16);
       w1[q] = e4m3x2(b[0], b[1]) | (e4m3x2(b[2], b[3]) << 16);
     }
-    const int64_t c0 = tile_c + 2 * cp;
-    const int64_t rg = tile_r + 32 * g;
-    if (c0 < p.cols && rg < p.rows) {  // rows % 32 == 0: the group is all in or all out
-      uint8_t* d0 = p.codes_colT + c0 * p.rows + rg;
-      stg_stream16(d0, make_uint4(w0[0], w0[1], w0[2], w0[3]));
-      stg_stream16(d0 + 16, make_uint4(w0[4], w0[5], w0[6], w0[7]));
-      sc_col[p.tiled ? tiled_offset(2 * cp, g) : (2 * cp) * 4 + g] = static_cast<uint8_t>(e0 + 127);
-      if (c0 + 1 < p.cols) {
-        uint8_t* d1 = d0 + p.rows;
-        stg_stream16(d1, make_uint4(w1[0], w1[1], w1[2], w1[3]));
-        stg_stream16(d1 + 16, make_uint4(w1[4], w1[5], w1[6], w1[7]));
-        sc_col[p.tiled ? tiled_offset(2 * cp + 1, g) : (2 * cp + 1) * 4 + g] =
-            static_cast<uint8_t>(e1 + 127);
+    // Transposed codes go through shared memory (the input tile is dead once every thread holds its
+    // column pair in registers) so that the global writes are full 128-byte lines: column c of the tile
+    // owns 128 bytes = 8 pieces of 16; piece q is stored at q ^ ((c >> 1) & 7) to keep both the
+    // per-thread writes and the cooperative reads free of bank conflicts.
+    __syncthreads();
+    {
+      const int c0 = 2 * cp, sw = cp & 7;
+      tile[c0 * 8 + ((2 * g) ^ sw)] = make_uint4(w0[0], w0[1], w0[2], w0[3]);
+      tile[c0 * 8 + ((2 * g + 1) ^ sw)] = make_uint4(w0[4], w0[5], w0[6], w0[7]);
+      tile[(c0 + 1) * 8 + ((2 * g) ^ sw)] = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+      tile[(c0 + 1) * 8 + ((2 * g + 1) ^ sw)] = make_uint4(w1[4], w1[5], w1[6], w1[7]);
+      if (tile_c + c0 < p.cols && tile_r + 32 * g < p.rows) {
+        sc_col[p.tiled ? tiled_offset(c0, g) : c0 * 4 + g] = static_cast<uint8_t>(e0 + 127);
+        if (tile_c + c0 + 1 < p.cols)
+          sc_col[p.tiled ? tiled_offset(c0 + 1, g) : (c0 + 1) * 4 + g] = static_cast<uint8_t>(e1 + 127);
       }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      const int idx = t + h * kThreads;  // 1024 pieces: column idx / 8, piece idx % 8
+      const int c = idx >> 3, q = idx & 7;
+      const int64_t col_g = tile_c + c, row_g = tile_r + q * 16;  // rows % 32 == 0: a piece is all in or all out
+      if (col_g < p.cols && row_g < p.rows)
+        stg_stream16(p.codes_colT + col_g * p.rows + row_g, tile[c * 8 + (q ^ ((c >> 1) & 7))]);
     }
   }
 
