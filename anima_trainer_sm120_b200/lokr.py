@@ -93,7 +93,12 @@ class LokrModule(nn.Module):
         return base + F.linear(x, delta, None)
 
     def custom_state_dict(self) -> dict:
-        return {"lokr_w1": self.lokr_w1, "lokr_w2": self.lokr_w2, "alpha": torch.tensor(self.scale * self.lora_dim)}
+        state = {"lokr_w1": self.lokr_w1, "alpha": torch.tensor(self.scale * self.lora_dim)}
+        if hasattr(self, "lokr_w2"):
+            state["lokr_w2"] = self.lokr_w2
+        else:                                   # T-LoKr: the large factor is stored as A @ B
+            state["lokr_w2_a"], state["lokr_w2_b"] = self.lokr_w2_a, self.lokr_w2_b
+        return state
 
 
 class LokrNetwork(nn.Module):

@@ -1,0 +1,82 @@
+"""50-step LoKr loss-curve parity and step timing of the Anima-shaped training step.
+
+    python -m anima_trainer_sm120_b200.loss_curve [--steps 50] [--depth 28] [--batch 8] [--latent 128]
+                                                  [--variant lokr|tlokr] [--arms bf16,mxfp8] [--lr 1e-4]
+    torchrun --nproc-per-node N ... -m anima_trainer_sm120_b200.loss_curve    (data parallel, NCCL)
+
+Both arms start from the same seeded random-init stand-in DiT and adapters, see the same seeded
+synthetic batch, noise and timesteps at every step and use the same AdamW optimizer; only the kernels
+differ (``train_step.Trainer``). Prints one JSON line: per-step losses of each arm, the largest
+per-step relative difference (criterion: <= 2 %), and steps/s of each arm (CUDA events, after 2
+warm-up steps, max over ranks). Synthetic data stands in for the reference's private dataset and
+AdamW for its Prodigy + ScheduleFree optimizer, neither of which is available.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from .anima_dit import AnimaConfig
+from .train_step import StepConfig, Trainer
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--depth", type=int, default=28)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--latent", type=int, default=128, help="latent height = width (128 -> 4096 tokens)")
+    ap.add_argument("--text", type=int, default=512)
+    ap.add_argument("--variant", default="lokr", choices=["lokr", "tlokr"])
+    ap.add_argument("--arms", default="bf16,mxfp8")
+    ap.add_argument("--lr", type=float, default=1e-4)
+    a = ap.parse_args()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    rank = dist.get_rank() if world > 1 else 0
+    mcfg = AnimaConfig(depth=a.depth)
+    out = {"config": {"depth": a.depth, "batch_per_gpu": a.batch, "tokens": (a.latent // 2) ** 2, "text_tokens": a.text,
+                      "variant": a.variant, "n_gpus": world, "steps": a.steps, "optimizer": "AdamW (stand-in)",
+                      "data": "synthetic"}, "losses": {}, "steps_per_s": {}}
+    for arm in a.arms.split(","):
+        tr = Trainer(mcfg, StepConfig(precision=arm, variant=a.variant, lr=a.lr), dev)
+        losses, times = [], []
+        for s in range(a.steps):
+            lat, ctx, seed = tr.synthetic_batch(a.batch, a.latent, a.text, s)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            losses.append(tr.step(lat, ctx, seed))
+            e1.record()
+            e1.synchronize()
+            if s >= 2:
+                times.append(e0.elapsed_time(e1))
+        ms = torch.tensor([sum(times) / max(len(times), 1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        out["losses"][arm] = losses
+        out["steps_per_s"][arm] = 1000.0 / float(ms) if float(ms) > 0 else None
+        out.setdefault("peak_mem_gb", {})[arm] = torch.cuda.max_memory_allocated(dev) / 2 ** 30
+        del tr
+        torch.cuda.empty_cache()
+    if "bf16" in out["losses"] and "mxfp8" in out["losses"]:
+        rel = [abs(b - m) / b for b, m in zip(out["losses"]["bf16"], out["losses"]["mxfp8"])]
+        out["max_rel_diff"] = max(rel)
+        out["within_2pct"] = max(rel) <= 0.02
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,308 @@
+"""Timestep-aware LoKr (T-LoKr) with the call surface of anima-trainer's ``tlokr.py``.
+
+``W2`` of a full-matrix LoKr adapter is factored as ``A @ B`` (rank r) and a per-sample prefix
+of that rank is active: ``active(t) = floor((r - r_min) * (1 - t) + r_min)`` (reference
+``active_rank_for_timestep`` :40-57, mask :84-92). The adapter output for a linear input is
+evaluated structurally (reference :472-492), never forming ``kron(W1, A @ B)``:
+
+    grouped = x.view(B, L*, uq, vq);  hidden = grouped @ B.T;  mixed = W1 @ (hidden * mask)
+    out = mixed @ A.T  ->  (B, L*, up * vp)
+
+Mirrored interface: ``active_rank_for_timestep``, ``set_timestep`` / ``clear_timestep`` (:110-130),
+``install_root_timestep_hooks`` (:270-292), ``convert_network`` (:330-448), ``_StructuredLoKr``
+(:451-540), ``_FP8StructuredLoKr`` (:543-676, here MXFP8), ``forward`` (:738-759).
+
+Kernels: the 8x8 mix, its transpose and its fp32 weight gradient run in ``csrc/tlokr_mix.cu``;
+in the quantised variant the factor GEMMs (2 forward, 2 recomputed + 4 in backward) run as
+MXFP8 tcgen05 GEMMs with the quantiser producing both operand forms per tensor. The bf16
+variant uses ``torch.matmul`` for the factor GEMMs (a library GEMM, as in the reference).
+"""
+from __future__ import annotations
+
+import math
+from contextvars import ContextVar
+from dataclasses import dataclass, field
+from types import MethodType
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import ops
+from .tlokr_kernels import rank_mix, rank_mix_wgrad
+
+_FORMAT_VERSION = 1
+BF16 = torch.bfloat16
+
+
+def active_rank_for_timestep(timestep: float, *, max_rank: int, min_rank: int) -> int:
+    """Prefix rank for a scalar flow timestep (t = 1 is the noisiest point)."""
+    if max_rank <= 0:
+        raise ValueError(f"max_rank must be positive; got {max_rank}")
+    if not 1 <= min_rank <= max_rank:
+        raise ValueError(f"min_rank must be in [1, {max_rank}]; got {min_rank}")
+    t = min(1.0, max(0.0, float(timestep)))
+    return max(min_rank, min(max_rank, math.floor((max_rank - min_rank) * (1.0 - t) + min_rank)))
+
+
+@dataclass
+class _TimestepState:
+    timesteps: torch.Tensor
+    uniform_timestep: float | None = None   # known single timestep: factors are sliced, no mask
+    masks: dict = field(default_factory=dict)
+
+    def mask(self, *, max_rank: int, min_rank: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+        """[B, max_rank] 0/1 prefix mask; built once per forward and shared by all modules."""
+        key = (max_rank, min_rank, dtype, device)
+        hit = self.masks.get(key)
+        if hit is None:
+            t = self.timesteps.detach().to(device=device, dtype=torch.float32).reshape(-1)
+            active = torch.floor((max_rank - min_rank) * (1.0 - t.clamp(0.0, 1.0)) + min_rank).to(torch.int64)
+            active.clamp_(min=min_rank, max=max_rank)
+            hit = (torch.arange(max_rank, device=device).unsqueeze(0) < active.unsqueeze(1)).to(dtype)
+            self.masks[key] = hit
+        return hit
+
+
+_STATE: ContextVar[_TimestepState | None] = ContextVar("anima_b200_tlokr_state", default=None)
+
+
+def set_timestep(timesteps: torch.Tensor, *, uniform_timestep: float | None = None) -> None:
+    """Set the timestep context for every T-LoKr module; it stays live through backward because
+    activation checkpointing re-runs adapter forwards there. Pair with :func:`clear_timestep`."""
+    if not torch.is_tensor(timesteps):
+        raise TypeError("T-LoKr timesteps must be a torch.Tensor")
+    _STATE.set(_TimestepState(timesteps=timesteps, uniform_timestep=uniform_timestep))
+
+
+def clear_timestep() -> None:
+    _STATE.set(None)
+
+
+def _current_state() -> _TimestepState:
+    state = _STATE.get()
+    if state is None:
+        raise RuntimeError("T-LoKr forward has no timestep context; call "
+                           "anima_trainer_sm120_b200.tlokr.set_timestep() around the DiT forward")
+    return state
+
+
+def install_root_timestep_hooks(dit: nn.Module) -> None:
+    """Derive a context from the root forward's ``timesteps`` argument when none was set explicitly,
+    restore the previous one afterwards, and keep it alive for checkpoint recomputation: each
+    block's ``_forward`` is wrapped so the callable the checkpoint retains re-enters the state."""
+    if getattr(dit, "_tlokr_timestep_hooks_installed", False):
+        return
+
+    def pre(_m, args, kwargs):
+        if _STATE.get() is not None:
+            dit._tlokr_tokens.append(None)
+            return
+        t = next((kwargs[k] for k in ("timesteps", "timesteps_B_T", "timestep") if kwargs.get(k) is not None), None)
+        if t is None and len(args) >= 2:
+            t = args[1]
+        if not torch.is_tensor(t):
+            raise RuntimeError("T-LoKr could not derive a tensor timestep from the DiT forward arguments")
+        dit._tlokr_tokens.append(_STATE.set(_TimestepState(timesteps=t)))
+
+    def post(_m, _args, _kwargs, _out):
+        token = dit._tlokr_tokens.pop() if dit._tlokr_tokens else None
+        if token is not None:
+            _STATE.reset(token)
+
+    dit._tlokr_tokens = []
+    dit.register_forward_pre_hook(pre, with_kwargs=True)
+    dit.register_forward_hook(post, with_kwargs=True, always_call=True)
+    for blk in dit.modules():
+        if hasattr(blk, "_forward") and hasattr(blk, "gradient_checkpointing") and "_forward" not in blk.__dict__:
+            inner = blk._forward
+
+            def contextual(self_blk, *a, __inner=inner, **kw):
+                captured = getattr(self_blk, "_tlokr_captured_state", None)
+                if _STATE.get() is not None or captured is None:
+                    self_blk._tlokr_captured_state = _STATE.get()
+                    return __inner(*a, **kw)
+                token = _STATE.set(captured)        # recomputation during backward
+                try:
+                    return __inner(*a, **kw)
+                finally:
+                    _STATE.reset(token)
+
+            object.__setattr__(blk, "_forward", MethodType(contextual, blk))
+    dit._tlokr_timestep_hooks_installed = True
+
+
+def convert_network(network: nn.Module, *, rank: int, min_rank_ratio: float) -> int:
+    """Convert freshly created full-matrix LoKr adapters in place: ``lokr_w2`` becomes the pair
+    ``lokr_w2_a`` (kaiming-uniform) / ``lokr_w2_b`` (zeros), so the adapted model starts at the base
+    model exactly. Returns the number of converted modules."""
+    from .lokr import LokrModule
+
+    if rank <= 0:
+        raise ValueError(f"T-LoKr rank must be positive; got {rank}")
+    if not 0.0 < min_rank_ratio <= 1.0:
+        raise ValueError(f"T-LoKr min_rank_ratio must be in (0, 1]; got {min_rank_ratio}")
+    min_rank = max(1, min(rank, math.ceil(rank * min_rank_ratio)))
+    pending = list(getattr(network, "unet_loras", ()))
+    converted = 0
+    for module in (pending if pending else list(network.modules())):
+        if not isinstance(module, LokrModule):
+            continue
+        if module.module_type != "linear":
+            raise TypeError(f"T-LoKr supports Linear targets only; {module.lora_name} wraps {module.module_type}")
+        if not module.use_w1 or not module.use_w2:
+            raise ValueError(f"{module.lora_name}: T-LoKr conversion requires full_matrix=true")
+        if module.wd or module.bypass_mode:
+            raise ValueError(f"{module.lora_name}: T-LoKr does not support weight decomposition or bypass mode")
+        if module.rank_dropout or module.dropout:
+            raise ValueError(f"{module.lora_name}: T-LoKr does not support rank/dropout")
+        old = module.lokr_w2
+        vp, vq = old.shape
+        if rank > min(vp, vq):
+            raise ValueError(f"T-LoKr rank {rank} exceeds the large Kronecker factor {tuple(old.shape)} "
+                             f"in {module.lora_name}")
+        del module.lokr_w2
+        a = nn.Parameter(torch.empty(vp, rank, device=old.device, dtype=old.dtype))
+        b = nn.Parameter(torch.zeros(rank, vq, device=old.device, dtype=old.dtype))
+        nn.init.kaiming_uniform_(a, a=math.sqrt(5))
+        module.register_parameter("lokr_w2_a", a)
+        module.register_parameter("lokr_w2_b", b)
+        module.use_w2 = False
+        module.full_matrix = False
+        module.lora_dim = rank
+        module._tlokr_enabled, module._tlokr_rank, module._tlokr_min_rank = True, rank, min_rank
+        scalar = module.scalar.item() if torch.is_tensor(module.scalar) else module.scalar
+        module._tlokr_alpha = float(module.scale) * float(scalar) * float(module.multiplier)
+        module.register_buffer("tlokr_schedule", torch.tensor([_FORMAT_VERSION, rank, min_rank], dtype=torch.int32))
+        converted += 1
+    if converted == 0:
+        raise RuntimeError("T-LoKr conversion found no LoKr modules")
+    network._tlokr_enabled, network._tlokr_rank, network._tlokr_min_rank = True, rank, min_rank
+    return converted
+
+
+def _grouped(x: torch.Tensor, uq: int) -> torch.Tensor:
+    return x.reshape(x.shape[0], -1, uq, x.shape[-1] // uq)
+
+
+class _StructuredLoKr(torch.autograd.Function):
+    """bf16 structured delta with manual backward; saves only x and the small factors and
+    recomputes the rank-space intermediates per module in backward (reference :451-540)."""
+
+    @staticmethod
+    def forward(ctx, x, w1, w2_a, w2_b, mask):
+        dt = x.dtype
+        c, a, b = w1.to(dt), w2_a.to(dt), w2_b.to(dt)
+        hidden = torch.matmul(_grouped(x, c.shape[1]), b.t())
+        out = torch.matmul(rank_mix(hidden, c, mask), a.t())
+        ctx.save_for_backward(x, w1, w2_a, w2_b, *(() if mask is None else (mask,)))
+        ctx.has_mask = mask is not None
+        return out.reshape(*x.shape[:-1], -1)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, w1, w2_a, w2_b = ctx.saved_tensors[:4]
+        mask = ctx.saved_tensors[4] if ctx.has_mask else None
+        dt = x.dtype
+        c, a, b = w1.to(dt), w2_a.to(dt), w2_b.to(dt)
+        up, uq = c.shape
+        vp = a.shape[0]
+        grouped = _grouped(x, uq)
+        hidden = torch.matmul(grouped, b.t())
+        mixed = rank_mix(hidden, c, mask)
+        g_blocks = grad_output.to(dt).reshape(x.shape[0], -1, up, vp)
+        g_a = g_blocks.reshape(-1, vp).t() @ mixed.reshape(-1, mixed.shape[-1])
+        g_mixed = torch.matmul(g_blocks, a)
+        g_c = rank_mix_wgrad(g_mixed, hidden, mask)
+        g_hidden = rank_mix(g_mixed, c, mask, transpose=True)
+        g_b = g_hidden.reshape(-1, g_hidden.shape[-1]).t() @ grouped.reshape(-1, grouped.shape[-1])
+        g_x = torch.matmul(g_hidden, b).reshape(x.shape)
+        return g_x.to(x.dtype), g_c.to(w1.dtype), g_a.to(w2_a.dtype), g_b.to(w2_b.dtype), None
+
+
+def _q(t2d: torch.Tensor, *, col: bool = False):
+    return ops.mx_quantize(t2d.contiguous() if t2d.dtype == BF16 else t2d.to(BF16).contiguous(),
+                           rowwise=True, colwise=col)
+
+
+class _MXStructuredLoKr(torch.autograd.Function):
+    """The same delta with every factor GEMM in MXFP8 on the tensor cores (the reference's
+    ``_FP8StructuredLoKr`` uses TE block-FP8 for them); the 8x8 mix stays in bf16."""
+
+    @staticmethod
+    def forward(ctx, x, w1, w2_a, w2_b, mask):
+        c = w1.to(BF16)
+        aq, aq_col = _q(w2_a.detach(), col=True)      # A [vp, r]: row form for out, column form for dgrad
+        bq, bq_col = _q(w2_b.detach(), col=True)      # B [r, vq]
+        grouped = _grouped(x, c.shape[1])
+        g2 = grouped.reshape(-1, grouped.shape[-1])
+        gq, _ = _q(g2)
+        hidden = ops.mx_gemm(gq, bq).view(*grouped.shape[:-1], w2_b.shape[0])
+        mixed = rank_mix(hidden, c, mask)
+        mq, _ = _q(mixed.reshape(-1, mixed.shape[-1]))
+        out = ops.mx_gemm(mq, aq)
+        ctx.save_for_backward(x, w1, w2_a, w2_b, *(() if mask is None else (mask,)))
+        ctx.has_mask, ctx.ops = mask is not None, (aq_col, bq, bq_col)
+        return out.view(*x.shape[:-1], -1).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, w1, w2_a, w2_b = ctx.saved_tensors[:4]
+        mask = ctx.saved_tensors[4] if ctx.has_mask else None
+        aq_col, bq, bq_col = ctx.ops
+        c = w1.to(BF16)
+        up, uq = c.shape
+        vp, rank = w2_a.shape
+        grouped = _grouped(x, uq)
+        g2 = grouped.reshape(-1, grouped.shape[-1])
+        gq, gq_col = _q(g2, col=True)
+        hidden = ops.mx_gemm(gq, bq).view(*grouped.shape[:-1], rank)
+        mixed = rank_mix(hidden, c, mask)
+        _, mq_col = _q(mixed.reshape(-1, rank), col=True)
+        gb2 = grad_output.reshape(-1, vp)
+        gbq, gbq_col = _q(gb2, col=True)
+        g_a = ops.mx_gemm(gbq_col, mq_col, out_dtype=torch.float32)          # grad_blocks^T @ mixed   [vp, r]
+        g_mixed = ops.mx_gemm(gbq, aq_col).view(*mixed.shape)                # grad_blocks @ A         [.., r]
+        g_c = rank_mix_wgrad(g_mixed, hidden, mask)
+        g_hidden = rank_mix(g_mixed, c, mask, transpose=True)
+        ghq, ghq_col = _q(g_hidden.reshape(-1, rank), col=True)
+        g_b = ops.mx_gemm(ghq_col, gq_col, out_dtype=torch.float32)          # grad_hidden^T @ grouped [r, vq]
+        g_x = ops.mx_gemm(ghq, bq_col).view(x.shape)                         # grad_hidden @ B
+        return g_x.to(x.dtype), g_c.to(w1.dtype), g_a.to(w2_a.dtype), g_b.to(w2_b.dtype), None
+
+
+_FP8StructuredLoKr = _MXStructuredLoKr  # name used by anima-trainer
+
+
+def _structured_delta(module, x: torch.Tensor, *, fp8: bool) -> torch.Tensor:
+    """``x @ kron(W1, A @ B).T`` for the current timestep context (reference :679-735)."""
+    state = _current_state()
+    rank, min_rank = module._tlokr_rank, module._tlokr_min_rank
+    w1 = module.lokr_w1
+    if x.shape[-1] % w1.shape[1]:
+        raise RuntimeError(f"{module.lora_name}: input width {x.shape[-1]} is not divisible by the W1 "
+                           f"input factor {w1.shape[1]}")
+    if state.uniform_timestep is not None:
+        active = active_rank_for_timestep(state.uniform_timestep, max_rank=rank, min_rank=min_rank)
+        fn = _MXStructuredLoKr if fp8 and active % 32 == 0 else _StructuredLoKr
+        return fn.apply(x, w1, module.lokr_w2_a[:, :active], module.lokr_w2_b[:active], None)
+    mask = state.mask(max_rank=rank, min_rank=min_rank, dtype=x.dtype, device=x.device)
+    if x.shape[0] != mask.shape[0]:
+        raise RuntimeError(f"{module.lora_name}: activation batch {x.shape[0]} does not match timestep "
+                           f"batch {mask.shape[0]}")
+    return (_MXStructuredLoKr if fp8 else _StructuredLoKr).apply(x, w1, module.lokr_w2_a, module.lokr_w2_b, mask)
+
+
+def forward(module, x: torch.Tensor) -> torch.Tensor:
+    """T-LoKr forward called by ``lokr_patch``: frozen base projection (quantised once when
+    ``fp8_quant.quantize_tlokr_base_weights`` ran) plus ``alpha`` times the structured delta."""
+    org = module.org_module[0]
+    base_q = getattr(module, "_tlokr_fp8_base_weight", None)
+    quantised = base_q is not None and x.is_cuda and (x.numel() // x.shape[-1]) % 32 == 0
+    if quantised:
+        from .fp8_quant import fp8_frozen_linear
+        base = fp8_frozen_linear(x, base_q, org.weight, org.bias)
+    else:
+        base = F.linear(x, org.weight, org.bias)
+    delta = _structured_delta(module, x, fp8=quantised)
+    return torch.add(base, delta, alpha=module._tlokr_alpha)

@@ -1,0 +1,141 @@
+"""Data-parallel LoKr training step on the Anima-shaped DiT: the caller of the hot path.
+
+What anima-trainer's loop does per step (``train.py:410-457``; ``flow.py:11-36``): draw
+``t = sigmoid(N(0,1))`` per sample, ``noisy = (1-t) x + t noise``, ``target = noise - x``; forward
+under bf16 autocast, fp32 MSE, backward, ``clip_grad_norm_(1.0)``, optimizer step. The reference is
+single-GPU; here the batch is additionally sharded over the ranks of one node and the adapter
+gradients are summed with ONE all-reduce of a flat fp32 buffer between backward and the clip
+(the clip needs the global gradient), then scaled by 1 / world.
+
+Two precision arms share everything but the kernels:
+  ``bf16``   the reference's bf16 mode restated — eager LayerNorm / modulation / gated add, merged
+             weight ``F.linear`` for the adapters (``lokr_patch`` bf16 path). Runs on CPU too.
+  ``mxfp8``  this package's kernels behind the same module patches: fused AdaLN + gated residual,
+             merged modulation MLPs, MXFP8 frozen linears, fused MXFP8 LoKr linears (or T-LoKr).
+The optimizer is AdamW for both arms: the reference's Prodigy + ScheduleFree is not available, so
+loss-curve parity is between arms, not against the reference's optimizer trajectory.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from . import adaln_merge, adaln_patch, lokr_patch
+from .anima_dit import AnimaConfig, AnimaDiT, Block
+from .lokr import attach_lokr
+
+
+def noisy_input_and_target(latents: torch.Tensor, gen: torch.Generator | None = None):
+    """(noisy, target, t) for rectified flow; t = 1 is pure noise (reference ``flow.py:17-36``)."""
+    B = latents.shape[0]
+    t = torch.sigmoid(torch.randn(B, device=latents.device, generator=gen))
+    noise = torch.randn(latents.shape, device=latents.device, generator=gen).to(latents.dtype)
+    tb = t.view(B, *([1] * (latents.dim() - 1))).to(latents.dtype)
+    return (1 - tb) * latents + tb * noise, noise - latents, t
+
+
+@dataclass
+class StepConfig:
+    precision: str = "mxfp8"          # "bf16" | "mxfp8"
+    variant: str = "lokr"             # "lokr" | "tlokr"
+    preset: str = "anima-cross-mlp"
+    lokr_dim: int = 128
+    lokr_factor: int = 8
+    min_rank_ratio: float = 0.5
+    lr: float = 1e-4
+    gradient_checkpointing: bool = True
+    max_grad_norm: float = 1.0
+    seed: int = 42
+
+
+class Trainer:
+    """Builds model + adapters for one rank and runs optimizer steps on synthetic batches."""
+
+    def __init__(self, model_cfg: AnimaConfig, cfg: StepConfig, device: torch.device):
+        if cfg.precision not in ("bf16", "mxfp8"):
+            raise ValueError(f"precision must be 'bf16' or 'mxfp8', got {cfg.precision!r}")
+        self.cfg, self.model_cfg, self.device = cfg, model_cfg, device
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        torch.manual_seed(cfg.seed)                      # identical base weights and adapters on every rank
+        self.dit = AnimaDiT(model_cfg).to(device=device, dtype=torch.bfloat16)
+        self.dit.enable_gradient_checkpointing(cfg.gradient_checkpointing)
+        self.network = attach_lokr(self.dit, preset=cfg.preset, factor=cfg.lokr_factor, dim=cfg.lokr_dim,
+                                   alpha=cfg.lokr_dim, variant=cfg.variant,
+                                   timestep_min_rank_ratio=cfg.min_rank_ratio)
+        self.tlokr = cfg.variant == "tlokr"
+        if self.tlokr:
+            from . import tlokr
+            self._tlokr = tlokr
+        if cfg.precision == "mxfp8":
+            if device.type != "cuda":
+                raise RuntimeError("precision='mxfp8' needs a CUDA device: the kernels have no CPU path")
+            from . import fp8_quant
+            adaln_merge.merge_adaln_modulation(self.dit)
+            adaln_patch.install(Block)
+            wrapped = fp8_quant.collect_lokr_wrapped_linears(self.network)
+            self.n_frozen_quantised = fp8_quant.quantize_frozen_linears(self.dit, skip=wrapped)
+            if self.tlokr:
+                fp8_quant.quantize_tlokr_base_weights(self.network)
+            else:
+                lokr_patch.enable_fp8(self.network)
+        else:
+            adaln_patch.uninstall(Block)
+            lokr_patch.disable_fp8()
+        self.dit.train()
+        self.params = [p for p in self.network.parameters() if p.requires_grad]
+        # flat fp32 gradient buffer; every .grad is a view into it, so the DP exchange is one call
+        n = sum(p.numel() for p in self.params)
+        self.flat_grad = torch.zeros(n, dtype=torch.float32, device=device)
+        off = 0
+        for p in self.params:
+            p.grad = self.flat_grad[off:off + p.numel()].view_as(p)
+            off += p.numel()
+        self.opt = torch.optim.AdamW(self.params, lr=cfg.lr, betas=(0.9, 0.99), weight_decay=0.0)
+        self.step_idx = 0
+
+    # ---------------------------------------------------------------- data
+    def synthetic_batch(self, batch: int, latent_hw: int, text_tokens: int, step: int):
+        """Seeded per (step, rank): latents (B,16,1,h,w) ~ N(0,1), text embeddings ~ N(0,1)."""
+        g = torch.Generator(device="cpu").manual_seed(1000003 * step + 7919 * self.rank + self.cfg.seed)
+        c = self.model_cfg
+        lat = torch.randn(batch, c.latent_channels, 1, latent_hw, latent_hw, generator=g)
+        ctx = torch.randn(batch, text_tokens, c.context_dim, generator=g)
+        noise_seed = int(torch.randint(0, 2 ** 31 - 1, (1,), generator=g))
+        return lat.to(self.device, torch.bfloat16), ctx.to(self.device, torch.bfloat16), noise_seed
+
+    # ---------------------------------------------------------------- one step
+    def forward_and_loss(self, latents, ctx, noise_seed: int):
+        g = torch.Generator(device=self.device).manual_seed(noise_seed)
+        noisy, target, t = noisy_input_and_target(latents, g)
+        if self.tlokr:
+            self._tlokr.set_timestep(t)
+        with torch.autocast(device_type=self.device.type, dtype=torch.bfloat16):
+            pred = self.dit(noisy, t, ctx)
+        return F.mse_loss(pred.float(), target.float())
+
+    def step(self, latents, ctx, noise_seed: int) -> float:
+        self.flat_grad.zero_()
+        try:
+            loss = self.forward_and_loss(latents, ctx, noise_seed)
+            loss.backward()
+        finally:
+            if self.tlokr:
+                self._tlokr.clear_timestep()
+        if self.world > 1:                      # the only exchange of the data-parallel step
+            dist.all_reduce(self.flat_grad)
+            self.flat_grad.mul_(1.0 / self.world)
+        torch.nn.utils.clip_grad_norm_(self.params, self.cfg.max_grad_norm)
+        self.opt.step()
+        self.step_idx += 1
+        return float(loss.detach())
+
+    def run(self, steps: int, batch: int, latent_hw: int, text_tokens: int) -> list[float]:
+        losses = []
+        for s in range(steps):
+            lat, ctx, seed = self.synthetic_batch(batch, latent_hw, text_tokens, self.step_idx)
+            losses.append(self.step(lat, ctx, seed))
+        return losses
