@@ -115,16 +115,17 @@ def install_root_timestep_hooks(dit: nn.Module) -> None:
     dit.register_forward_hook(post, with_kwargs=True, always_call=True)
     for blk in dit.modules():
         if hasattr(blk, "_forward") and hasattr(blk, "gradient_checkpointing") and "_forward" not in blk.__dict__:
-            inner = blk._forward
 
-            def contextual(self_blk, *a, __inner=inner, **kw):
+            def contextual(self_blk, *a, **kw):
+                # the class attribute is looked up at call time so that a later adaln_patch.install() is honoured
+                inner = type(self_blk)._forward
                 captured = getattr(self_blk, "_tlokr_captured_state", None)
                 if _STATE.get() is not None or captured is None:
                     self_blk._tlokr_captured_state = _STATE.get()
-                    return __inner(*a, **kw)
-                token = _STATE.set(captured)        # recomputation during backward
+                    return inner(self_blk, *a, **kw)
+                token = _STATE.set(captured)        # recomputation during backward, on autograd's thread
                 try:
-                    return __inner(*a, **kw)
+                    return inner(self_blk, *a, **kw)
                 finally:
                     _STATE.reset(token)
 
@@ -201,8 +202,9 @@ class _StructuredLoKr(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output):
-        x, w1, w2_a, w2_b = ctx.saved_tensors[:4]
-        mask = ctx.saved_tensors[4] if ctx.has_mask else None
+        saved = ctx.saved_tensors        # read once: activation checkpointing unpacks on access
+        x, w1, w2_a, w2_b = saved[:4]
+        mask = saved[4] if ctx.has_mask else None
         dt = x.dtype
         c, a, b = w1.to(dt), w2_a.to(dt), w2_b.to(dt)
         up, uq = c.shape
@@ -247,8 +249,9 @@ class _MXStructuredLoKr(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output):
-        x, w1, w2_a, w2_b = ctx.saved_tensors[:4]
-        mask = ctx.saved_tensors[4] if ctx.has_mask else None
+        saved = ctx.saved_tensors        # read once: activation checkpointing unpacks on access
+        x, w1, w2_a, w2_b = saved[:4]
+        mask = saved[4] if ctx.has_mask else None
         aq_col, bq, bq_col = ctx.ops
         c = w1.to(BF16)
         up, uq = c.shape
@@ -283,9 +286,19 @@ def _structured_delta(module, x: torch.Tensor, *, fp8: bool) -> torch.Tensor:
         raise RuntimeError(f"{module.lora_name}: input width {x.shape[-1]} is not divisible by the W1 "
                            f"input factor {w1.shape[1]}")
     if state.uniform_timestep is not None:
+        # One known timestep for the whole batch: slice the factors to the active prefix, which drops the
+        # mask and the inactive-rank work. The mix kernel wants the rank in multiples of 8 (the MXFP8 GEMMs in
+        # multiples of 32); other prefixes keep the full factors and use an equivalent uniform mask.
         active = active_rank_for_timestep(state.uniform_timestep, max_rank=rank, min_rank=min_rank)
-        fn = _MXStructuredLoKr if fp8 and active % 32 == 0 else _StructuredLoKr
-        return fn.apply(x, w1, module.lokr_w2_a[:, :active], module.lokr_w2_b[:active], None)
+        if active % 8 == 0:
+            fn = _MXStructuredLoKr if fp8 and active % 32 == 0 else _StructuredLoKr
+            return fn.apply(x, w1, module.lokr_w2_a[:, :active], module.lokr_w2_b[:active], None)
+        key = ("uniform", rank, active, x.dtype, x.device, x.shape[0])
+        mask = state.masks.get(key)
+        if mask is None:
+            mask = (torch.arange(rank, device=x.device) < active).to(x.dtype).expand(x.shape[0], rank).contiguous()
+            state.masks[key] = mask
+        return (_MXStructuredLoKr if fp8 else _StructuredLoKr).apply(x, w1, module.lokr_w2_a, module.lokr_w2_b, mask)
     mask = state.mask(max_rank=rank, min_rank=min_rank, dtype=x.dtype, device=x.device)
     if x.shape[0] != mask.shape[0]:
         raise RuntimeError(f"{module.lora_name}: activation batch {x.shape[0]} does not match timestep "

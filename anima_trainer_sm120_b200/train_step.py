@@ -70,6 +70,9 @@ class Trainer:
         if self.tlokr:
             from . import tlokr
             self._tlokr = tlokr
+            # checkpoint recomputation runs on autograd's worker thread, which does not inherit the
+            # ContextVar: the block wrapper re-enters the forward's timestep state there
+            tlokr.install_root_timestep_hooks(self.dit)
         if cfg.precision == "mxfp8":
             if device.type != "cuda":
                 raise RuntimeError("precision='mxfp8' needs a CUDA device: the kernels have no CPU path")

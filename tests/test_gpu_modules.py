@@ -91,6 +91,14 @@ def test_tlokr_uniform_sliced_path_matches_masked_path():
     finally:
         tlokr.clear_timestep()
     torch.testing.assert_close(sliced.float(), masked.float(), rtol=2e-2, atol=2e-2)
+    try:                                   # t = 1.0 -> 8 active ranks: a multiple of 8, so the factors are really sliced
+        tlokr.set_timestep(torch.tensor([1.0], device=DEV))
+        masked8 = mod(x)
+        tlokr.set_timestep(torch.tensor([1.0], device=DEV), uniform_timestep=1.0)
+        sliced8 = mod(x)                   # truly sliced factors (A[:, :8], B[:8]), no mask
+    finally:
+        tlokr.clear_timestep()
+    torch.testing.assert_close(sliced8.float(), masked8.float(), rtol=2e-2, atol=2e-2)
 
 
 def test_tlokr_mxfp8_structured_matches_bf16_structured():
