@@ -14,6 +14,8 @@
 // The reductions over the hw rows of a sample are two-stage (per-block partials in
 // caller-provided scratch, then a fixed-order sum), so results are bit-reproducible;
 // the reference uses fp32 atomics.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace anima {
@@ -477,4 +479,52 @@ extern "C" int anima_gated_add_bwd(const void* dout, const void* y, const void* 
       ws, bt, sp.chunks, 1, (int)d, static_cast<__nv_bfloat16*>(dgate), nullptr);
   ANIMA_CHECK_LAUNCH("gated_add_bwd finalize");
   return ANIMA_OK;
+}
+
+// ------------------------------------------------------------------ adaln_bwd without caller scratch
+// Some hosts of this library may not allocate device memory at the point where they call it: a plugin that
+// is handed only its input and output buffers by a framework that owns every other byte of the GPU, or a
+// service whose memory plan is frozen after start-up so that a late cudaMalloc could fail or stall. For them
+// the partial sums of adaln_bwd live in this fixed array inside the library image instead of a workspace.
+namespace {
+constexpr int64_t kStaticScratchBytes = ANIMA_ADALN_BWD_NOALLOC_MAX_BYTES;  // resident on every GPU that loads the library
+__device__ __align__(256) float g_adaln_bwd_scratch[kStaticScratchBytes / sizeof(float)];
+
+// Device address of the array for the current device. The symbol name is only a host-side handle; the
+// address has to be asked for once per device, with that device current.
+int static_scratch(float** out) {
+  static std::mutex mu;
+  static float* cached[64];
+  int dev = 0;
+  ANIMA_REQUIRE(cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64, ANIMA_E_CUDA,
+                "adaln_bwd_noalloc: cannot identify the current device");
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    float* p = nullptr;
+    const cudaError_t rc = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_adaln_bwd_scratch);
+    ANIMA_REQUIRE(rc == cudaSuccess && p != nullptr, ANIMA_E_CUDA,
+                  "adaln_bwd_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(rc));
+    cached[dev] = p;
+  }
+  *out = cached[dev];
+  return ANIMA_OK;
+}
+}  // namespace
+
+extern "C" int anima_adaln_bwd_noalloc(const void* dy, const void* x, const void* scale, const float* mean,
+                                       const float* rstd, int64_t rows, int64_t hw, int64_t d, void* dx,
+                                       void* dscale, void* dshift, void* stream) {
+  const int64_t need = anima_adaln_bwd_workspace_bytes(rows, hw, d);
+  ANIMA_REQUIRE(need >= 0, ANIMA_E_SHAPE, "adaln_bwd_noalloc: rows=%lld is not a multiple of hw=%lld (or a size is not positive)",
+                (long long)rows, (long long)hw);
+  ANIMA_REQUIRE(need <= kStaticScratchBytes, ANIMA_E_TOO_LARGE,
+                "adaln_bwd_noalloc: this shape needs %lld bytes of scratch but the built-in array holds %lld; "
+                "use anima_adaln_bwd with a caller workspace",
+                (long long)need, (long long)kStaticScratchBytes);
+  float* scratch = nullptr;
+  if (int rc = static_scratch(&scratch)) return rc;
+  // Every partial-sum slot that the final pass reads is written earlier in this same call, so nothing in the
+  // array has to start at zero and what an earlier call left behind is never read.
+  return anima_adaln_bwd(dy, x, scale, mean, rstd, rows, hw, d, dx, dscale, dshift, scratch, kStaticScratchBytes,
+                         stream);
 }

@@ -148,6 +148,27 @@ int anima_adaln_bwd(const void* dy, const void* x, const void* scale, const floa
                     void* dscale, void* dshift, void* workspace, int64_t workspace_bytes,
                     void* stream);
 
+/* anima_adaln_bwd for callers that cannot hand over scratch memory (no counterpart in anima-trainer).
+ *
+ * Who needs it: code that runs where allocating device memory is not an option — an operator plugged
+ * into a framework that passes it input and output buffers and nothing else, or a long-running service
+ * whose GPU memory is fully planned at start-up, where a later cudaMalloc may fail, fragment the plan or
+ * stall the device. Same arguments and results as anima_adaln_bwd minus the workspace: the per-block
+ * partial sums go to a fixed array compiled into the library (ANIMA_ADALN_BWD_NOALLOC_MAX_BYTES bytes of
+ * global memory on every GPU that loads it, held until the process exits). The call itself performs no
+ * cudaMalloc / cudaFree and calls no allocating routine.
+ *   - Limit: shapes whose anima_adaln_bwd_workspace_bytes(rows, hw, d) exceeds the array are refused with
+ *     ANIMA_E_TOO_LARGE (config 3, x [8, 4096, 2048], needs 4.6 MiB and fits).
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current); make that first call outside any stream capture.
+ *   - All calls on a device share the one array. Calls that may overlap on the GPU (different streams
+ *     without ordering between them) race on it; stream-ordered calls are safe, and nothing in the array
+ *     needs clearing between calls because every slot that is read was written earlier in the same call. */
+#define ANIMA_ADALN_BWD_NOALLOC_MAX_BYTES (8ll << 20)
+int anima_adaln_bwd_noalloc(const void* dy, const void* x, const void* scale, const float* mean,
+                            const float* rstd, int64_t rows, int64_t hw, int64_t d, void* dx,
+                            void* dscale, void* dshift, void* stream);
+
 /* ---------------------------------------------------------------- gated residual
  * ref: adaln_kernel.py:272-295 (_gated_add_fwd_kernel), :332-380.
  * out = x + gate[r / hw] * y, all bf16, evaluated in fp32 and rounded once. */
