@@ -84,14 +84,20 @@ class Attention(nn.Module):
         self.q_norm = RMSNorm(cfg.head_dim, cfg.eps)
         self.k_norm = RMSNorm(cfg.head_dim, cfg.eps)
 
+    def _prepare_qk(self, q, k, rope_emb):
+        """Per-head RMSNorm, then RoPE on self-attention. ``qk_norm_rope.install`` swaps in one fused kernel."""
+        q, k = self.q_norm(q), self.k_norm(k)
+        if rope_emb is not None:
+            q, k = apply_rotary_pos_emb(q, rope_emb), apply_rotary_pos_emb(k, rope_emb)
+        return q, k
+
     def forward(self, x, attn_params=None, context=None, rope_emb=None):
         B, L, _ = x.shape
         ctx = x if context is None else context
-        q = self.q_norm(self.q_proj(x).view(B, L, self.heads, self.head_dim))
-        k = self.k_norm(self.k_proj(ctx).view(B, ctx.shape[1], self.heads, self.head_dim))
+        q = self.q_proj(x).view(B, L, self.heads, self.head_dim)
+        k = self.k_proj(ctx).view(B, ctx.shape[1], self.heads, self.head_dim)
         v = self.v_proj(ctx).view(B, ctx.shape[1], self.heads, self.head_dim)
-        if rope_emb is not None and not self.is_cross:
-            q, k = apply_rotary_pos_emb(q, rope_emb), apply_rotary_pos_emb(k, rope_emb)
+        q, k = self._prepare_qk(q, k, None if self.is_cross else rope_emb)
         out = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
         return self.output_proj(out.transpose(1, 2).reshape(B, L, -1))
 

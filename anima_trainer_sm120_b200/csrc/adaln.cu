@@ -25,9 +25,11 @@ constexpr int kThreads = 256;
 constexpr int kRowsPerIter = 4;
 
 // ------------------------------------------------------------------ forward
-// One warp per row; lane l owns the 16-byte chunks l, l+32, ... of the row.
+// One warp per row; lane l owns the 16-byte chunks l, l+32, ... of the row. The row stays packed (bf16)
+// in registers and is unpacked in each of the three passes (sum, centred squares, output): that keeps the
+// kernel at ~50 registers, so 4 CTAs (32 warps, 128 KB of loads in flight) fit on an SM.
 template <int NCH>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, NCH <= 8 ? 4 : 2)
 adaln_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ scale,
                  const __nv_bfloat16* __restrict__ shift, float eps, int64_t rows, int64_t hw,
                  int d, __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out,
@@ -38,26 +40,33 @@ adaln_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
   const int64_t bt = row / hw;
   const __nv_bfloat16* xr = x + row * d;
 
-  float v[NCH][8];
-  float sum = 0.f;
+  uint4 raw[NCH];
 #pragma unroll
   for (int i = 0; i < NCH; ++i) {
     const int col = (i * 32 + lane) * 8;
-    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-    if (col < d) raw = ldg_stream16(xr + col);
-    unpack8(raw, v[i]);
+    raw[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (col < d) raw[i] = ldg_stream16(xr + col);
+  }
+  float sum = 0.f;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) sum += v[i][k];
+  for (int i = 0; i < NCH; ++i) {
+    float v[8];
+    unpack8(raw[i], v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) sum += v[k];
   }
   const float mean = warp_sum(sum) / static_cast<float>(d);
   float sq = 0.f;
 #pragma unroll
   for (int i = 0; i < NCH; ++i) {
-    const bool ok = (i * 32 + lane) * 8 < d;
+    if ((i * 32 + lane) * 8 < d) {  // padded tail must not add mean^2 (adaln_kernel.py:55-57)
+      float v[8];
+      unpack8(raw[i], v);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      v[i][k] = ok ? v[i][k] - mean : 0.f;  // padded tail must not add mean^2 (adaln_kernel.py:55-57)
-      sq += v[i][k] * v[i][k];
+      for (int k = 0; k < 8; ++k) {
+        const float c = v[k] - mean;
+        sq += c * c;
+      }
     }
   }
   const float var = warp_sum(sq) / static_cast<float>(d);
@@ -66,11 +75,12 @@ adaln_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
   for (int i = 0; i < NCH; ++i) {
     const int col = (i * 32 + lane) * 8;
     if (col < d) {
-      float s[8], b[8], o[8];
+      float v[8], s[8], b[8], o[8];
+      unpack8(raw[i], v);
       unpack8(*reinterpret_cast<const uint4*>(scale + bt * d + col), s);
       unpack8(*reinterpret_cast<const uint4*>(shift + bt * d + col), b);
 #pragma unroll
-      for (int k = 0; k < 8; ++k) o[k] = v[i][k] * rstd * (1.0f + s[k]) + b[k];
+      for (int k = 0; k < 8; ++k) o[k] = (v[k] - mean) * rstd * (1.0f + s[k]) + b[k];
       stg_stream16(y + row * d + col, pack8(o));
     }
   }

@@ -145,6 +145,14 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
         mask = (torch.rand(8, 128, device="cuda") > 0.3).to(BF16)
         hbm("tlokr_rank_mix", list(hid.shape), hid.numel() * 4, lambda: ops.tlokr_rank_mix(hid, c, mask, False))
         hbm("tlokr_rank_mix_wgrad", list(hid.shape), hid.numel() * 4, lambda: ops.tlokr_rank_mix_wgrad(gm, hid, mask))
+        L = M // BT
+        q, dq = _acts(M, D).view(BT, L, 16, 128), _acts(M, D).view(BT, L, 16, 128)
+        wn = torch.ones(128, device="cuda")
+        ang = torch.rand(L, 128, device="cuda") * 60
+        cos, sin = ang.cos(), ang.sin()
+        _, rs = ops.rmsnorm_rope_fwd(q, wn, cos, sin, 1e-6)
+        hbm("rmsnorm_rope_fwd", [BT, L, 16, 128], M * D * 4 + M * 16 * 4, lambda: ops.rmsnorm_rope_fwd(q, wn, cos, sin, 1e-6))
+        hbm("rmsnorm_rope_bwd", [BT, L, 16, 128], M * D * 6 + M * 16 * 4, lambda: ops.rmsnorm_rope_bwd(dq, q, wn, cos, sin, rs))
 
     if only in (None, "gemm"):
         for (N, K) in [(2048, 2048), (6144, 2048), (8192, 2048), (2048, 8192)]:

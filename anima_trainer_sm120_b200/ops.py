@@ -268,3 +268,36 @@ def tlokr_rank_mix_wgrad(grad_mixed: torch.Tensor, hidden: torch.Tensor, mask: t
         check(lib.anima_tlokr_rank_mix_wgrad(ptr(grad_mixed), ptr(hidden), ptr(mask), batch, n, rank, ptr(dc),
                                              ptr(ws), ws.numel(), _lib.stream_ptr(dev)))
     return dc
+
+
+def rmsnorm_rope_fwd(x: torch.Tensor, weight: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tensor | None,
+                     eps: float) -> tuple[torch.Tensor, torch.Tensor]:
+    """x bf16 (..., tokens-major, heads, 128) contiguous; weight fp32 [128]; cos / sin fp32 [seq_len, 128] or None.
+    Returns (out bf16 like x, rstd fp32 [tokens * heads])."""
+    dev = _lib.require_cuda(x, weight, cos, sin)
+    heads, d = x.shape[-2], x.shape[-1]
+    tokens = x.numel() // (heads * d) if x.numel() else 0
+    out = torch.empty_like(x)
+    rstd = torch.empty(tokens * heads, dtype=torch.float32, device=dev)
+    if tokens == 0:
+        return out, rstd
+    seq = cos.shape[0] if cos is not None else 1
+    with torch.cuda.device(dev):
+        check(_lib.load().anima_rmsnorm_rope_fwd(ptr(x), ptr(weight), ptr(cos), ptr(sin), float(eps), tokens, heads, d,
+                                                 seq, ptr(out), ptr(rstd), _lib.stream_ptr(dev)))
+    return out, rstd
+
+
+def rmsnorm_rope_bwd(dout: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, cos: torch.Tensor | None,
+                     sin: torch.Tensor | None, rstd: torch.Tensor) -> torch.Tensor:
+    dev = _lib.require_cuda(dout, x, weight, cos, sin, rstd)
+    heads, d = x.shape[-2], x.shape[-1]
+    tokens = x.numel() // (heads * d) if x.numel() else 0
+    dx = torch.empty_like(x)
+    if tokens == 0:
+        return dx
+    seq = cos.shape[0] if cos is not None else 1
+    with torch.cuda.device(dev):
+        check(_lib.load().anima_rmsnorm_rope_bwd(ptr(dout), ptr(x), ptr(weight), ptr(cos), ptr(sin), ptr(rstd), tokens,
+                                                 heads, d, seq, ptr(dx), _lib.stream_ptr(dev)))
+    return dx

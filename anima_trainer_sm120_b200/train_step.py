@@ -11,7 +11,7 @@ Two precision arms share everything but the kernels:
   ``bf16``   the reference's bf16 mode restated — eager LayerNorm / modulation / gated add, merged
              weight ``F.linear`` for the adapters (``lokr_patch`` bf16 path). Runs on CPU too.
   ``mxfp8``  this package's kernels behind the same module patches: fused AdaLN + gated residual,
-             merged modulation MLPs, MXFP8 frozen linears, fused MXFP8 LoKr linears (or T-LoKr).
+             fused q / k RMSNorm + RoPE, merged modulation MLPs, MXFP8 frozen linears, fused MXFP8 LoKr linears (or T-LoKr).
 The optimizer is AdamW for both arms: the reference's Prodigy + ScheduleFree is not available, so
 loss-curve parity is between arms, not against the reference's optimizer trajectory.
 """
@@ -23,8 +23,8 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from . import adaln_merge, adaln_patch, lokr_patch
-from .anima_dit import AnimaConfig, AnimaDiT, Block
+from . import adaln_merge, adaln_patch, lokr_patch, qk_norm_rope
+from .anima_dit import AnimaConfig, AnimaDiT, Attention, Block
 from .lokr import attach_lokr
 
 
@@ -79,6 +79,7 @@ class Trainer:
             from . import fp8_quant
             adaln_merge.merge_adaln_modulation(self.dit)
             adaln_patch.install(Block)
+            qk_norm_rope.install(Attention)
             wrapped = fp8_quant.collect_lokr_wrapped_linears(self.network)
             self.n_frozen_quantised = fp8_quant.quantize_frozen_linears(self.dit, skip=wrapped)
             if self.tlokr:
@@ -87,6 +88,7 @@ class Trainer:
                 lokr_patch.enable_fp8(self.network)
         else:
             adaln_patch.uninstall(Block)
+            qk_norm_rope.uninstall(Attention)
             lokr_patch.disable_fp8()
         self.dit.train()
         self.params = [p for p in self.network.parameters() if p.requires_grad]

@@ -201,6 +201,25 @@ int anima_tlokr_rank_mix_wgrad(const void* grad_mixed, const void* hidden, const
                                int64_t batch, int64_t n_per_batch, int64_t rank, float* dc,
                                void* workspace, int64_t workspace_bytes, void* stream);
 
+/* ---------------------------------------------------------------- q / k preparation
+ * Per-head RMSNorm followed by rotary embedding in one pass (head_dim must be 128).
+ * ref: the two third-party kernels the trainer patches in at this point — Liger RMSNorm
+ * (liger_patch.py:31-47, rms_norm casting mode "llama") and Transformer Engine's fused RoPE,
+ * rotate-half / non-interleaved (rope_patch.py:28-56).
+ * x, out bf16 [tokens, heads, 128]; weight fp32 [128]; cos_tab, sin_tab fp32 [seq_len, 128] or
+ * both NULL (norm only; cross-attention q / k); position of a token = token index % seq_len.
+ *   n = x * rsqrt(mean(x^2) + eps) * weight;  out = n * cos + rotate_half(n) * sin   (fp32 math)
+ * rstd fp32 [tokens, heads] is written by fwd and read by bwd. bwd gives dx only: the norm
+ * weight is frozen in adapter training. */
+int anima_rmsnorm_rope_fwd(const void* x, const float* weight, const float* cos_tab,
+                           const float* sin_tab, float eps, int64_t tokens, int64_t heads,
+                           int64_t head_dim, int64_t seq_len, void* out, float* rstd,
+                           void* stream);
+int anima_rmsnorm_rope_bwd(const void* dout, const void* x, const float* weight,
+                           const float* cos_tab, const float* sin_tab, const float* rstd,
+                           int64_t tokens, int64_t heads, int64_t head_dim, int64_t seq_len,
+                           void* dx, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
