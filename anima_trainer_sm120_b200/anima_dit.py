@@ -144,7 +144,9 @@ class Block(nn.Module):
 
     def forward(self, *args, **kwargs):
         if self.training and self.gradient_checkpointing:
-            return torch_checkpoint(self._forward, *args, use_reentrant=False, **kwargs)
+            from .fp8_quant import first_pass      # this pass's saved tensors are dropped and recomputed
+            with first_pass():
+                return torch_checkpoint(self._forward, *args, use_reentrant=False, **kwargs)
         return self._forward(*args, **kwargs)
 
     def _mod(self, seq, emb, adaln_lora):

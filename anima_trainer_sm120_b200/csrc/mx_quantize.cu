@@ -27,6 +27,73 @@ struct PlainLoader {
   __device__ __forceinline__ uint4 operator()(int64_t r, int64_t c) const { return ldg_stream16(x + r * ld + c); }
 };
 
+// erf(t) for t >= 0 as 1 - erfc(t), erfc(t) = 2^(-t q(t)) with q a degree-10 least-squares fit of
+// -log2(erfc(t)) / t on [0, 4] (beyond 4, erf rounds to 1 in fp32). Absolute error about 1e-7, i.e.
+// one or two fp32 steps of erf: branch-free and a quarter of the instructions of the libm erff,
+// which otherwise makes this loader compute-bound.
+__device__ __forceinline__ float erf_nonneg(float t) {
+  t = fminf(t, 4.0f);
+  float q = -1.434943897e-07f;
+  q = fmaf(q, t, 3.633767847e-06f);
+  q = fmaf(q, t, -4.095852273e-05f);
+  q = fmaf(q, t, 2.688576060e-04f);
+  q = fmaf(q, t, -1.106124022e-03f);
+  q = fmaf(q, t, 2.616207348e-03f);
+  q = fmaf(q, t, -3.566088853e-04f);
+  q = fmaf(q, t, -2.759680524e-02f);
+  q = fmaf(q, t, 1.482741833e-01f);
+  q = fmaf(q, t, 9.184474349e-01f);
+  q = fmaf(q, t, 1.627907038e+00f);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-t * q));
+  return 1.f - e;
+}
+
+// Exact-form (erf) GELU of a pre-activation, evaluated in fp32 in the order an eager bf16 GELU uses,
+// x * 0.5 * (1 + erf(x / sqrt 2)), and rounded to bf16 where that kernel would store it. Over all
+// finite bf16 inputs the rounded result equals the libm-erff form for x > -3.1; in the negative tail,
+// where 1 + erf cancels in fp32 and either form carries only a few significant bits, a tenth of the
+// inputs differ by a few bf16 steps of values below 3e-3.
+__device__ __forceinline__ float gelu_f(float v) {
+  const float erf = copysignf(erf_nonneg(fabsf(v) * 0.70710678118654752440f), v);
+  return v * 0.5f * (1.f + erf);
+}
+__device__ __forceinline__ float gelu_grad_f(float v, float dy) {
+  const float erf = copysignf(erf_nonneg(fabsf(v) * 0.70710678118654752440f), v);
+  const float cdf = 0.5f * (1.f + erf);
+  float pdf;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pdf) : "f"(v * v * -0.72134752044448170368f));   // exp(-v^2 / 2)
+  pdf *= 0.39894228040143267794f;                                                           // 1 / sqrt(2 pi)
+  return dy * (cdf + v * pdf);
+}
+
+struct GeluLoader {
+  const __nv_bfloat16* h;
+  int64_t ld;
+  __device__ __forceinline__ uint4 operator()(int64_t r, int64_t c) const {
+    float f[8];
+    unpack8(ldg_stream16(h + r * ld + c), f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] = gelu_f(f[k]);
+    return pack8(f);
+  }
+};
+
+// d(pre-activation) = grad_act * gelu'(h), rounded to bf16.
+struct GeluBwdLoader {
+  const __nv_bfloat16* h;
+  const __nv_bfloat16* grad_act;
+  int64_t ld;
+  __device__ __forceinline__ uint4 operator()(int64_t r, int64_t c) const {
+    float f[8], g[8];
+    unpack8(ldg_stream16(h + r * ld + c), f);
+    unpack8(ldg_stream16(grad_act + r * ld + c), g);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] = gelu_grad_f(f[k], g[k]);
+    return pack8(f);
+  }
+};
+
 __global__ void mx_dequantize_kernel(const uint8_t* __restrict__ codes,
                                      const uint8_t* __restrict__ scales, int64_t rows, int64_t k,
                                      int tiled, __nv_bfloat16* __restrict__ out) {
@@ -83,39 +150,43 @@ extern "C" int64_t anima_mx_scales_bytes(int64_t rows, int64_t k, int scale_layo
   return scale_layout == ANIMA_SCALES_TILED ? ceil_div(rows, 128) * ceil_div(kb, 4) * 512 : rows * kb;
 }
 
-extern "C" int anima_mx_quantize(const void* x, int64_t rows, int64_t cols, int64_t ld,
-                                 uint8_t* codes_row, uint8_t* scales_row, uint8_t* codes_colT,
-                                 uint8_t* scales_col, int scale_layout, void* stream) {
+namespace {
+
+// Argument checks shared by the quantising entry points; returns ANIMA_OK or the failing status.
+int check_quantize_args(const char* who, const void* x, int64_t rows, int64_t cols, int64_t ld,
+                        const uint8_t* codes_row, const uint8_t* scales_row, const uint8_t* codes_colT,
+                        const uint8_t* scales_col, int scale_layout) {
   const bool row = codes_row != nullptr, col = codes_colT != nullptr;
-  ANIMA_REQUIRE(x != nullptr, ANIMA_E_ARG, "mx_quantize: x is null");
-  ANIMA_REQUIRE(row || col, ANIMA_E_ARG, "mx_quantize: no output requested");
+  ANIMA_REQUIRE(x != nullptr, ANIMA_E_ARG, "%s: x is null", who);
+  ANIMA_REQUIRE(row || col, ANIMA_E_ARG, "%s: no output requested", who);
   ANIMA_REQUIRE((codes_row == nullptr) == (scales_row == nullptr) &&
                     (codes_colT == nullptr) == (scales_col == nullptr),
-                ANIMA_E_ARG, "mx_quantize: codes and scales must be given in pairs");
+                ANIMA_E_ARG, "%s: codes and scales must be given in pairs", who);
   ANIMA_REQUIRE(scale_layout == ANIMA_SCALES_PLAIN || scale_layout == ANIMA_SCALES_TILED, ANIMA_E_ARG,
-                "mx_quantize: bad scale_layout %d", scale_layout);
-  ANIMA_REQUIRE(rows >= 0 && cols >= 0 && ld >= cols, ANIMA_E_ARG,
-                "mx_quantize: bad sizes rows=%lld cols=%lld ld=%lld", (long long)rows, (long long)cols,
-                (long long)ld);
-  ANIMA_REQUIRE(!row || cols % 32 == 0, ANIMA_E_SHAPE,
-                "mx_quantize: rowwise needs cols %% 32 == 0 (cols=%lld)", (long long)cols);
-  ANIMA_REQUIRE(!col || rows % 32 == 0, ANIMA_E_SHAPE,
-                "mx_quantize: columnwise needs rows %% 32 == 0 (rows=%lld)", (long long)rows);
-  ANIMA_REQUIRE(cols % 8 == 0 && ld % 8 == 0, ANIMA_E_SHAPE,
-                "mx_quantize: cols and ld must be multiples of 8");
+                "%s: bad scale_layout %d", who, scale_layout);
+  ANIMA_REQUIRE(rows >= 0 && cols >= 0 && ld >= cols, ANIMA_E_ARG, "%s: bad sizes rows=%lld cols=%lld ld=%lld", who,
+                (long long)rows, (long long)cols, (long long)ld);
+  ANIMA_REQUIRE(!row || cols % 32 == 0, ANIMA_E_SHAPE, "%s: rowwise needs cols %% 32 == 0 (cols=%lld)", who,
+                (long long)cols);
+  ANIMA_REQUIRE(!col || rows % 32 == 0, ANIMA_E_SHAPE, "%s: columnwise needs rows %% 32 == 0 (rows=%lld)", who,
+                (long long)rows);
+  ANIMA_REQUIRE(cols % 8 == 0 && ld % 8 == 0, ANIMA_E_SHAPE, "%s: cols and ld must be multiples of 8", who);
   ANIMA_REQUIRE(aligned16(x) && (!row || aligned16(codes_row)) && (!col || aligned16(codes_colT)),
-                ANIMA_E_ALIGN, "mx_quantize: x and code buffers must be 16-byte aligned");
+                ANIMA_E_ALIGN, "%s: x and code buffers must be 16-byte aligned", who);
   ANIMA_REQUIRE((!row || (reinterpret_cast<uintptr_t>(scales_row) & 3) == 0) &&
                     (!col || (reinterpret_cast<uintptr_t>(scales_col) & 3) == 0),
-                ANIMA_E_ALIGN, "mx_quantize: scale buffers must be 4-byte aligned");
-  if (rows == 0 || cols == 0) return ANIMA_OK;
-  const int64_t gy = ceil_div(rows, kTile), gx = ceil_div(cols, kTile);
-  ANIMA_REQUIRE(gy <= 65535, ANIMA_E_TOO_LARGE, "mx_quantize: rows=%lld exceeds 65535*128",
+                ANIMA_E_ALIGN, "%s: scale buffers must be 4-byte aligned", who);
+  ANIMA_REQUIRE(ceil_div(rows, kTile) <= 65535, ANIMA_E_TOO_LARGE, "%s: rows=%lld exceeds 65535*128", who,
                 (long long)rows);
-  QuantParams p{rows, cols, codes_row, scales_row, codes_colT, scales_col,
-                scale_layout == ANIMA_SCALES_TILED};
-  const PlainLoader load{static_cast<const __nv_bfloat16*>(x), ld};
-  const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
+  return ANIMA_OK;
+}
+
+template <class Loader>
+int launch_quantize(const char* who, const Loader& load, int64_t rows, int64_t cols, uint8_t* codes_row,
+                    uint8_t* scales_row, uint8_t* codes_colT, uint8_t* scales_col, int scale_layout, void* stream) {
+  const bool row = codes_row != nullptr, col = codes_colT != nullptr;
+  QuantParams p{rows, cols, codes_row, scales_row, codes_colT, scales_col, scale_layout == ANIMA_SCALES_TILED};
+  const dim3 grid(static_cast<unsigned>(ceil_div(cols, kTile)), static_cast<unsigned>(ceil_div(rows, kTile)));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (row && col)
     mx_quantize_kernel<true, true><<<grid, kThreads, 0, s>>>(p, load);
@@ -123,8 +194,41 @@ extern "C" int anima_mx_quantize(const void* x, int64_t rows, int64_t cols, int6
     mx_quantize_kernel<true, false><<<grid, kThreads, 0, s>>>(p, load);
   else
     mx_quantize_kernel<false, true><<<grid, kThreads, 0, s>>>(p, load);
-  ANIMA_CHECK_LAUNCH("mx_quantize");
+  ANIMA_CHECK_LAUNCH(who);
   return ANIMA_OK;
+}
+
+}  // namespace
+
+extern "C" int anima_mx_quantize(const void* x, int64_t rows, int64_t cols, int64_t ld,
+                                 uint8_t* codes_row, uint8_t* scales_row, uint8_t* codes_colT,
+                                 uint8_t* scales_col, int scale_layout, void* stream) {
+  if (int rc = check_quantize_args("mx_quantize", x, rows, cols, ld, codes_row, scales_row, codes_colT, scales_col,
+                                   scale_layout))
+    return rc;
+  if (rows == 0 || cols == 0) return ANIMA_OK;
+  const PlainLoader load{static_cast<const __nv_bfloat16*>(x), ld};
+  return launch_quantize("mx_quantize", load, rows, cols, codes_row, scales_row, codes_colT, scales_col,
+                         scale_layout, stream);
+}
+
+extern "C" int anima_mx_quantize_gelu(const void* h, const void* grad_act, int64_t rows, int64_t cols,
+                                      int64_t ld, uint8_t* codes_row, uint8_t* scales_row,
+                                      uint8_t* codes_colT, uint8_t* scales_col, int scale_layout,
+                                      void* stream) {
+  if (int rc = check_quantize_args("mx_quantize_gelu", h, rows, cols, ld, codes_row, scales_row, codes_colT,
+                                   scales_col, scale_layout))
+    return rc;
+  ANIMA_REQUIRE(!grad_act || aligned16(grad_act), ANIMA_E_ALIGN, "mx_quantize_gelu: grad_act must be 16-byte aligned");
+  if (rows == 0 || cols == 0) return ANIMA_OK;
+  if (grad_act) {
+    const GeluBwdLoader load{static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(grad_act), ld};
+    return launch_quantize("mx_quantize_gelu", load, rows, cols, codes_row, scales_row, codes_colT, scales_col,
+                           scale_layout, stream);
+  }
+  const GeluLoader load{static_cast<const __nv_bfloat16*>(h), ld};
+  return launch_quantize("mx_quantize_gelu", load, rows, cols, codes_row, scales_row, codes_colT, scales_col,
+                         scale_layout, stream);
 }
 
 extern "C" int anima_mx_dequantize(const uint8_t* codes, const uint8_t* scales, int64_t rows,

@@ -145,6 +145,13 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
         mask = (torch.rand(8, 128, device="cuda") > 0.3).to(BF16)
         hbm("tlokr_rank_mix", list(hid.shape), hid.numel() * 4, lambda: ops.tlokr_rank_mix(hid, c, mask, False))
         hbm("tlokr_rank_mix_wgrad", list(hid.shape), hid.numel() * 4, lambda: ops.tlokr_rank_mix_wgrad(gm, hid, mask))
+        hh, gg = _acts(M, 8192), _acts(M, 8192)
+        nh = M * 8192
+        hbm("mx_quantize_gelu row+col", [M, 8192], int(nh * 4.0625),
+            lambda: ops.mx_quantize_gelu(hh, rowwise=True, colwise=True))
+        hbm("mx_quantize_gelu backward row+col", [M, 8192], int(nh * 6.0625),
+            lambda: ops.mx_quantize_gelu(hh, gg, rowwise=True, colwise=True))
+        del hh, gg
         L = M // BT
         q, dq = _acts(M, D).view(BT, L, 16, 128), _acts(M, D).view(BT, L, 16, 128)
         wn = torch.ones(128, device="cuda")

@@ -2,6 +2,7 @@
 
     python -m anima_trainer_sm120_b200.loss_curve [--steps 50] [--depth 28] [--batch 8] [--latent 128]
                                                   [--variant lokr|tlokr] [--arms bf16,mxfp8] [--lr 1e-4]
+                                                  [--no-checkpoint]
     torchrun --nproc-per-node N ... -m anima_trainer_sm120_b200.loss_curve    (data parallel, NCCL)
 
 Both arms start from the same seeded random-init stand-in DiT and adapters, see the same seeded
@@ -34,6 +35,9 @@ def main() -> None:
     ap.add_argument("--variant", default="lokr", choices=["lokr", "tlokr"])
     ap.add_argument("--arms", default="bf16,mxfp8")
     ap.add_argument("--lr", type=float, default=1e-4)
+    ap.add_argument("--no-checkpoint", action="store_true",
+                    help="keep every block's activations instead of recomputing them (the reference's configuration "
+                         "recomputes; 180 GB of HBM leaves room not to)")
     a = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -47,9 +51,10 @@ def main() -> None:
     mcfg = AnimaConfig(depth=a.depth)
     out = {"config": {"depth": a.depth, "batch_per_gpu": a.batch, "tokens": (a.latent // 2) ** 2, "text_tokens": a.text,
                       "variant": a.variant, "n_gpus": world, "steps": a.steps, "optimizer": "AdamW (stand-in)",
-                      "data": "synthetic"}, "losses": {}, "steps_per_s": {}}
+                      "gradient_checkpointing": not a.no_checkpoint, "data": "synthetic"}, "losses": {}, "steps_per_s": {}}
     for arm in a.arms.split(","):
-        tr = Trainer(mcfg, StepConfig(precision=arm, variant=a.variant, lr=a.lr), dev)
+        tr = Trainer(mcfg, StepConfig(precision=arm, variant=a.variant, lr=a.lr,
+                                       gradient_checkpointing=not a.no_checkpoint), dev)
         losses, times = [], []
         for s in range(a.steps):
             lat, ctx, seed = tr.synthetic_batch(a.batch, a.latent, a.text, s)

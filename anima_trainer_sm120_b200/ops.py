@@ -50,19 +50,9 @@ def _alloc_scales(rows: int, k: int, layout: int, device) -> torch.Tensor:
     return torch.empty(scales_bytes(rows, k, layout), dtype=torch.uint8, device=device)
 
 
-def mx_quantize(
-    x: torch.Tensor, *, rowwise: bool = True, colwise: bool = False, layout: int = SCALES_TILED
-) -> tuple[MXOperand | None, MXOperand | None]:
-    """Quantise bf16 ``x [rows, cols]`` (last-dim stride 1) from one read.
-
-    Returns ``(row_op, col_op)``: ``row_op`` is x quantised along its columns
-    (``[rows, cols]``), ``col_op`` is x quantised along its rows and stored
-    transposed (``[cols, rows]``) — i.e. ``quantize_rowwise(x.t().contiguous())``.
-    """
-    _bf16_2d(x, "x")
+def _quantize_call(entry: str, x: torch.Tensor, extra: tuple, rowwise: bool, colwise: bool, layout: int
+                   ) -> tuple[MXOperand | None, MXOperand | None]:
     dev = _lib.require_cuda(x)
-    if x.stride(1) != 1 and x.shape[1] > 1:
-        x = x.contiguous()
     rows, cols = x.shape
     if rowwise and cols % 32:
         raise ValueError(f"rowwise quantisation needs cols % 32 == 0, got {cols}")
@@ -78,12 +68,44 @@ def mx_quantize(
     if rows == 0 or cols == 0:   # empty tensors have no storage to point at
         return row_op, col_op
     with torch.cuda.device(dev):
-        check(_lib.load().anima_mx_quantize(
-            ptr(x), rows, cols, x.stride(0) if rows > 1 else cols,
+        check(getattr(_lib.load(), entry)(
+            ptr(x), *extra, rows, cols, x.stride(0) if rows > 1 else cols,
             ptr(row_op.codes) if row_op else None, ptr(row_op.scales) if row_op else None,
             ptr(col_op.codes) if col_op else None, ptr(col_op.scales) if col_op else None,
             layout, _lib.stream_ptr(dev)))
     return row_op, col_op
+
+
+def mx_quantize(
+    x: torch.Tensor, *, rowwise: bool = True, colwise: bool = False, layout: int = SCALES_TILED
+) -> tuple[MXOperand | None, MXOperand | None]:
+    """Quantise bf16 ``x [rows, cols]`` (last-dim stride 1) from one read.
+
+    Returns ``(row_op, col_op)``: ``row_op`` is x quantised along its columns
+    (``[rows, cols]``), ``col_op`` is x quantised along its rows and stored
+    transposed (``[cols, rows]``) — i.e. ``quantize_rowwise(x.t().contiguous())``.
+    """
+    _bf16_2d(x, "x")
+    if x.stride(1) != 1 and x.shape[1] > 1:
+        x = x.contiguous()
+    return _quantize_call("anima_mx_quantize", x, (), rowwise, colwise, layout)
+
+
+def mx_quantize_gelu(
+    h: torch.Tensor, grad_act: torch.Tensor | None = None, *, rowwise: bool = True, colwise: bool = False,
+    layout: int = SCALES_TILED,
+) -> tuple[MXOperand | None, MXOperand | None]:
+    """MXFP8 forms of ``gelu(h)`` (``grad_act`` None) or of ``grad_act * gelu'(h)``, from one read of the bf16
+    pre-activation ``h [rows, cols]``; the activation / its gradient is never written as a bf16 tensor."""
+    _bf16_2d(h, "h")
+    h = h.contiguous()
+    if grad_act is not None:
+        _bf16_2d(grad_act, "grad_act")
+        if grad_act.shape != h.shape:
+            raise ValueError(f"grad_act {tuple(grad_act.shape)} does not match h {tuple(h.shape)}")
+        grad_act = grad_act.contiguous()
+        _lib.require_cuda(h, grad_act)
+    return _quantize_call("anima_mx_quantize_gelu", h, (ptr(grad_act),), rowwise, colwise, layout)
 
 
 def mx_dequantize(op: MXOperand) -> torch.Tensor:

@@ -11,7 +11,8 @@ Two precision arms share everything but the kernels:
   ``bf16``   the reference's bf16 mode restated — eager LayerNorm / modulation / gated add, merged
              weight ``F.linear`` for the adapters (``lokr_patch`` bf16 path). Runs on CPU too.
   ``mxfp8``  this package's kernels behind the same module patches: fused AdaLN + gated residual,
-             fused q / k RMSNorm + RoPE, merged modulation MLPs, MXFP8 frozen linears, fused MXFP8 LoKr linears (or T-LoKr).
+             fused q / k RMSNorm + RoPE, merged modulation MLPs, the LoKr MLP as one node
+             with GELU quantised in its producer, MXFP8 frozen linears, fused MXFP8 LoKr linears (or T-LoKr).
 The optimizer is AdamW for both arms: the reference's Prodigy + ScheduleFree is not available, so
 loss-curve parity is between arms, not against the reference's optimizer trajectory.
 """
@@ -23,8 +24,8 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from . import adaln_merge, adaln_patch, lokr_patch, qk_norm_rope
-from .anima_dit import AnimaConfig, AnimaDiT, Attention, Block
+from . import adaln_merge, adaln_patch, lokr_patch, mlp_patch, qk_norm_rope
+from .anima_dit import AnimaConfig, AnimaDiT, Attention, Block, GPT2FeedForward
 from .lokr import attach_lokr
 
 
@@ -80,6 +81,7 @@ class Trainer:
             adaln_merge.merge_adaln_modulation(self.dit)
             adaln_patch.install(Block)
             qk_norm_rope.install(Attention)
+            mlp_patch.install(GPT2FeedForward)       # takes effect for plain LoKr adapters on the quantised path
             wrapped = fp8_quant.collect_lokr_wrapped_linears(self.network)
             self.n_frozen_quantised = fp8_quant.quantize_frozen_linears(self.dit, skip=wrapped)
             if self.tlokr:
@@ -89,6 +91,7 @@ class Trainer:
         else:
             adaln_patch.uninstall(Block)
             qk_norm_rope.uninstall(Attention)
+            mlp_patch.uninstall(GPT2FeedForward)
             lokr_patch.disable_fp8()
         self.dit.train()
         self.params = [p for p in self.network.parameters() if p.requires_grad]

@@ -170,7 +170,7 @@ def run_gpu_arm(args) -> None:
     import torch.distributed as dist
 
     from anima_trainer_sm120_b200 import _lib, ops
-    from anima_trainer_sm120_b200.fp8_quant import lokr_linear_fused
+    from anima_trainer_sm120_b200.fp8_quant import clear_activation_memo, lokr_linear_fused
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -222,6 +222,7 @@ def run_gpu_arm(args) -> None:
                 s.x.copy_(s.x_host, non_blocking=True)
                 s.dy.copy_(s.dy_host, non_blocking=True)
             s.w1.grad = s.w2.grad = None
+            clear_activation_memo()     # x is the same tensor object every step: quantise it again, as training does
             y = lokr_linear_fused(s.x, s.W, None, s.w1, s.w2, 1.0)
             y.backward(s.dy)
             for p in (s.w1, s.w2):

@@ -71,6 +71,18 @@ int anima_mx_quantize(const void* x_bf16, int64_t rows, int64_t cols, int64_t ld
                       uint8_t* codes_colT, uint8_t* scales_col,
                       int scale_layout, void* stream);
 
+/* Quantise an MLP activation without materialising it (no reference counterpart: the reference
+ * runs GELU as a separate eager kernel between mlp.layer1 and mlp.layer2 and quantises its output).
+ * h bf16 [rows, cols] is the pre-activation.
+ *   grad_act == NULL : quantises bf16(gelu(h)), exact erf form.
+ *   grad_act != NULL : quantises bf16(grad_act * gelu'(h)), the gradient w.r.t. h; grad_act has h's
+ *                      shape and leading dimension.
+ * Outputs, scale layout and size rules are those of anima_mx_quantize. */
+int anima_mx_quantize_gelu(const void* h, const void* grad_act, int64_t rows, int64_t cols,
+                           int64_t ld, uint8_t* codes_row, uint8_t* scales_row,
+                           uint8_t* codes_colT, uint8_t* scales_col, int scale_layout,
+                           void* stream);
+
 /* Bytes of the scale tensor of a code matrix [rows, k] in the given layout. */
 int64_t anima_mx_scales_bytes(int64_t rows, int64_t k, int scale_layout);
 
