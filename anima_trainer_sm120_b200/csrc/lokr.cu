@@ -36,8 +36,9 @@ struct MergeLoader {
   float alpha;
   int64_t K, vp, vq, uq;
   __device__ __forceinline__ uint4 operator()(int64_t r, int64_t c) const {
-    const int64_t i = r / vp, p = r - i * vp;
-    const int64_t j = c / vq, q = c - j * vq;  // vq % 8 == 0: the 8 columns share j
+    const int ri = static_cast<int>(r), ci = static_cast<int>(c);   // N, K < 2^31 is checked on the host
+    const int i = ri / static_cast<int>(vp), p = ri - i * static_cast<int>(vp);
+    const int j = ci / static_cast<int>(vq), q = ci - j * static_cast<int>(vq);  // vq % 8 == 0: the 8 columns share j
     const float a = to_f32(w1[i * uq + j]);
     float wv[8], o[8], f2[8];
     unpack8(ldg_stream16(w + r * K + c), wv);
@@ -215,7 +216,7 @@ extern "C" int anima_lokr_merge_quantize(const void* w, const void* w1, const vo
                 "lokr_merge_quantize: bad scale_layout %d", scale_layout);
   ANIMA_REQUIRE(!row || K % 32 == 0, ANIMA_E_SHAPE, "lokr_merge_quantize: rowwise needs K %% 32 == 0");
   ANIMA_REQUIRE(!col || N % 32 == 0, ANIMA_E_SHAPE, "lokr_merge_quantize: columnwise needs N %% 32 == 0");
-  ANIMA_REQUIRE(ceil_div(N, kTile) <= 65535, ANIMA_E_TOO_LARGE, "lokr_merge_quantize: N too large");
+  ANIMA_REQUIRE(ceil_div(N, kTile) <= 65535 && K < (1ll << 31), ANIMA_E_TOO_LARGE, "lokr_merge_quantize: N or K too large");
   ANIMA_REQUIRE(aligned16(w) && aligned16(w2) && (!merged || aligned16(merged)) && (!row || aligned16(codes_row)) &&
                     (!col || aligned16(codes_colT)),
                 ANIMA_E_ALIGN, "lokr_merge_quantize: W, w2, merged and code buffers must be 16-byte aligned");

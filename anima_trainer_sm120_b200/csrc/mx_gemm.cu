@@ -177,6 +177,11 @@ struct GemmParams {
   int out_fp32;
   int m_tiles, n_tiles, k_blocks;
   int sfa_rt, sfb_rt;  // number of 128-row scale tiles of A and B
+  // Split-K (one-CTA kernel only): work item = (tile, split); split s contracts K-blocks
+  // [s * kb_per_split, min(k_blocks, (s + 1) * kb_per_split)) and, when splits > 1, stores its fp32
+  // partial tile to partial[s][M][N]; splitk_finalize_kernel then sums the splits in index order.
+  int splits, kb_per_split;
+  float* partial;
 };
 
 
@@ -265,16 +270,18 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
 
-  const int total_tiles = p.m_tiles * p.n_tiles;
+  const int total_items = p.m_tiles * p.n_tiles * p.splits;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t kiter = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        const int tile = item / p.splits, split = item - tile * p.splits;
+        const int kb0 = split * p.kb_per_split, kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
         const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
-        for (int kb = 0; kb < p.k_blocks; ++kb, ++kiter) {
+        for (int kb = kb0; kb < kb1; ++kb, ++kiter) {
           const int s = kiter % kStages;
           const uint32_t ph = (kiter / kStages) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag)) { ok = false; break; }
@@ -298,7 +305,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       uint32_t kiter = 0;
       bool ok = true;
       int it = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++it) {
+        const int split = item % p.splits;
+        const int kb0 = split * p.kb_per_split, kb1 = min(p.k_blocks, kb0 + p.kb_per_split);
         const int as = it & 1;
         if (it > 0) {
           // The previous tile's epilogue must have drained the columns shared by the two buffers
@@ -307,7 +316,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           tc_fence_after();
         }
         const uint32_t d_tmem = tmem_base + (as ? C::kAcc1Col : 0);
-        for (int kb = 0; kb < p.k_blocks; ++kb, ++kiter) {
+        for (int kb = kb0; kb < kb1; ++kb, ++kiter) {
           const int s = kiter % kStages;
           const uint32_t ph = (kiter / kStages) & 1u;
           if (!mbar_wait(full_bar(s), ph, &abort_flag)) { ok = false; break; }
@@ -322,7 +331,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           for (int k = 0; k < BK / 32; ++k) {
             // +32 bytes along K inside the 128-byte swizzle atom = +2 in the 16-byte address field.
             tc_mma_mxf8(d_tmem, a_desc + 2 * k, b_desc + 2 * k, make_idesc<BN>(k), tmem_base + C::kSfaCol,
-                        tmem_base + C::kSfbCol, (kb | k) != 0 ? 1u : 0u);
+                        tmem_base + C::kSfbCol, (kb != kb0 || k != 0) ? 1u : 0u);
           }
           tc_commit(empty_bar(s));  // stage reusable once these MMAs have read it
         }
@@ -334,9 +343,17 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int quad = warp & 3;  // tensor-memory lane quadrant this warp may access
     bool ok = true;
     int it = 0;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++it) {
+      const int tile = item / p.splits, split = item - tile * p.splits;
       const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
       const int as = it & 1;
+      GemmParams dst = p;
+      if (p.splits > 1) {  // this split's fp32 partial; bias and rounding happen in the finalize pass
+        dst.c = p.partial + static_cast<int64_t>(split) * p.M * p.N;
+        dst.ldc = p.N;
+        dst.out_fp32 = 1;
+        dst.bias = nullptr;
+      }
       if (!mbar_wait(acc_full_bar(as), (it >> 1) & 1u, &abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int row = mt * BM + quad * 32 + lane;
@@ -353,7 +370,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           __syncwarp();
           if (lane == 0) mbar_arrive(acc_free_bar);
         }
-        store_chunk(p, row, nt * BN + chunk * 32, v);
+        store_chunk(dst, row, nt * BN + chunk * 32, v);
       }
     }
   }
@@ -370,6 +387,35 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::kTmemCols) : "memory");
+  }
+}
+
+// C = sum over splits (in index order, so the result is reproducible) of partial[s] (+ bias), 4 columns per thread.
+__global__ void __launch_bounds__(256) splitk_finalize_kernel(const GemmParams p) {
+  const int64_t n4 = p.N / 4, total = static_cast<int64_t>(p.M) * n4, plane = static_cast<int64_t>(p.M) * p.N;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = i / n4, col = (i - row * n4) * 4;
+    const float* src = p.partial + row * p.N + col;
+    float4 acc = *reinterpret_cast<const float4*>(src);
+    for (int s = 1; s < p.splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(src + s * plane);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (p.bias) {
+      acc.x += __bfloat162float(p.bias[col]);
+      acc.y += __bfloat162float(p.bias[col + 1]);
+      acc.z += __bfloat162float(p.bias[col + 2]);
+      acc.w += __bfloat162float(p.bias[col + 3]);
+    }
+    if (p.out_fp32) {
+      *reinterpret_cast<float4*>(static_cast<float*>(p.c) + row * p.ldc + col) = acc;
+    } else {
+      uint2 o;
+      *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(acc.x, acc.y);
+      *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(acc.z, acc.w);
+      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.c) + row * p.ldc + col) = o;
+    }
   }
 }
 
@@ -834,11 +880,41 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, cudaStrea
   ANIMA_REQUIRE(attr_rc == cudaSuccess, ANIMA_E_CUDA, "mx_gemm: cannot reserve %d bytes of shared memory: %s",
                 Cfg<BN>::kSmemBytes, cudaGetErrorString(attr_rc));
   p.n_tiles = static_cast<int>(ceil_div(p.N, BN));
-  const int tiles = p.m_tiles * p.n_tiles;
-  const int grid = std::min(tiles, sm_count());
+  const int items = p.m_tiles * p.n_tiles * p.splits;
+  const int grid = std::min(items, sm_count());
   mx_gemm_kernel<BN><<<grid, kThreads, Cfg<BN>::kSmemBytes, s>>>(ma, mb, p);
   ANIMA_CHECK_LAUNCH("mx_gemm");
+  if (p.splits > 1) {
+    const int64_t groups = static_cast<int64_t>(p.M) * (p.N / 4);
+    splitk_finalize_kernel<<<static_cast<unsigned>(std::min<int64_t>(ceil_div(groups, 256), 4LL * sm_count())), 256, 0,
+                             s>>>(p);
+    ANIMA_CHECK_LAUNCH("mx_gemm split-K finalize");
+  }
   return ANIMA_OK;
+}
+
+// Does the shape go to the CTA-pair kernel?
+bool use_pair(int64_t M, int64_t N) {
+  const int variant = forced_variant();
+  // CTA pairs pay off once a 256 x 256 tile is mostly full; small or narrow problems keep one CTA per tile.
+  return variant == 2 || (variant == 0 && N > 128 && M > 128);
+}
+
+// Split-K plan of the one-CTA kernel: a small output with a long contraction (the T-LoKr factor
+// gradients are [128..1024, 128..1024] over K = rows * 8 = 262144) would otherwise occupy 1 - 8 SMs.
+// Splits are sized to fill the GPU once, with at least 8 K-blocks (1024 elements of K) per split.
+void plan_splits(int64_t M, int64_t N, int64_t K, int* splits, int* kb_per_split) {
+  const int kb = static_cast<int>(ceil_div(K, BK));
+  *splits = 1;
+  *kb_per_split = kb;
+  if (use_pair(M, N) || N % 4 != 0) return;
+  const int64_t tiles = ceil_div(M, BM) * ceil_div(N, N > 128 ? 256 : 128);
+  const int sms = sm_count();
+  if (tiles * 2 > sms || kb < 32) return;
+  const int want = static_cast<int>(std::min<int64_t>(sms / tiles, kb / 8));
+  if (want < 2) return;
+  *kb_per_split = static_cast<int>(ceil_div(kb, want));
+  *splits = static_cast<int>(ceil_div(kb, *kb_per_split));
 }
 
 }  // namespace
@@ -846,9 +922,10 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, cudaStrea
 
 using namespace anima;
 
-extern "C" int anima_mx_gemm(const uint8_t* a_codes, const uint8_t* a_scales, const uint8_t* b_codes,
-                             const uint8_t* b_scales, void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
-                             const void* bias, int out_dtype, int32_t* status, void* stream) {
+static int mx_gemm_impl(const uint8_t* a_codes, const uint8_t* a_scales, const uint8_t* b_codes,
+                        const uint8_t* b_scales, void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
+                        const void* bias, int out_dtype, void* workspace, int64_t workspace_bytes, int32_t* status,
+                        void* stream) {
   ANIMA_REQUIRE(a_codes && a_scales && b_codes && b_scales && c, ANIMA_E_ARG, "mx_gemm: null pointer");
   ANIMA_REQUIRE(M > 0 && N > 0 && K > 0 && ldc >= N, ANIMA_E_ARG, "mx_gemm: bad sizes M=%lld N=%lld K=%lld ldc=%lld",
                 (long long)M, (long long)N, (long long)K, (long long)ldc);
@@ -877,14 +954,48 @@ extern "C" int anima_mx_gemm(const uint8_t* a_codes, const uint8_t* a_scales, co
   p.k_blocks = static_cast<int>(ceil_div(K, BK));
   p.sfa_rt = static_cast<int>(ceil_div(M, 128));
   p.sfb_rt = static_cast<int>(ceil_div(N, 128));
+  p.splits = 1;
+  p.kb_per_split = p.k_blocks;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (use_pair(M, N)) return launch_pair(a_codes, b_codes, p, s);
+  if (workspace) {
+    ANIMA_REQUIRE(aligned16(workspace), ANIMA_E_ALIGN, "mx_gemm: workspace must be 16-byte aligned");
+    int splits, kb_per;
+    plan_splits(M, N, K, &splits, &kb_per);
+    if (splits > 1) {
+      ANIMA_REQUIRE(workspace_bytes >= static_cast<int64_t>(splits) * M * N * 4, ANIMA_E_WORKSPACE,
+                    "mx_gemm: workspace of %lld bytes is too small (need %lld)", (long long)workspace_bytes,
+                    (long long)(static_cast<int64_t>(splits) * M * N * 4));
+      p.splits = splits;
+      p.kb_per_split = kb_per;
+      p.partial = static_cast<float*>(workspace);
+    }
+  }
   const bool wide = N > 128;
-  const int variant = forced_variant();
-  // CTA pairs pay off once a 256 x 256 tile is mostly full; small or narrow problems keep one CTA per tile.
-  const bool pair = variant == 2 || (variant == 0 && wide && M > 128);
-  if (pair) return launch_pair(a_codes, b_codes, p, s);
   CUtensorMap ma, mb;
   ANIMA_REQUIRE(make_map(&ma, a_codes, M, K, BM) && make_map(&mb, b_codes, N, K, wide ? 256 : 128), ANIMA_E_CUDA,
                 "mx_gemm: cuTensorMapEncodeTiled failed (driver entry point missing or bad operand)");
   return wide ? launch<256>(ma, mb, p, s) : launch<128>(ma, mb, p, s);
+}
+
+extern "C" int anima_mx_gemm(const uint8_t* a_codes, const uint8_t* a_scales, const uint8_t* b_codes,
+                             const uint8_t* b_scales, void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
+                             const void* bias, int out_dtype, int32_t* status, void* stream) {
+  return mx_gemm_impl(a_codes, a_scales, b_codes, b_scales, c, M, N, K, ldc, bias, out_dtype, nullptr, 0, status,
+                      stream);
+}
+
+extern "C" int64_t anima_mx_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0) return ANIMA_E_ARG;
+  int splits, kb_per;
+  plan_splits(M, N, K, &splits, &kb_per);
+  return splits > 1 ? static_cast<int64_t>(splits) * M * N * 4 : 0;
+}
+
+extern "C" int anima_mx_gemm_ws(const uint8_t* a_codes, const uint8_t* a_scales, const uint8_t* b_codes,
+                                const uint8_t* b_scales, void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
+                                const void* bias, int out_dtype, void* workspace, int64_t workspace_bytes,
+                                int32_t* status, void* stream) {
+  return mx_gemm_impl(a_codes, a_scales, b_codes, b_scales, c, M, N, K, ldc, bias, out_dtype, workspace,
+                      workspace_bytes, status, stream);
 }

@@ -130,8 +130,9 @@ def mx_retile(op: MXOperand) -> MXOperand:
 
 
 def mx_gemm(a: MXOperand, b: MXOperand, *, bias: torch.Tensor | None = None,
-            out_dtype: torch.dtype = BF16, out: torch.Tensor | None = None) -> torch.Tensor:
-    """``C[M,N] = A[M,K] . B[N,K]^T (+ bias)`` on the tcgen05 block-scaled tensor path."""
+            out_dtype: torch.dtype = BF16, out: torch.Tensor | None = None, split_k: bool = True) -> torch.Tensor:
+    """``C[M,N] = A[M,K] . B[N,K]^T (+ bias)`` on the tcgen05 block-scaled tensor path. Small outputs with a
+    long contraction are split over K through a scratch buffer unless ``split_k`` is False."""
     dev = _lib.require_cuda(a.codes, a.scales, b.codes, b.scales, bias)
     if a.layout != SCALES_TILED or b.layout != SCALES_TILED:
         raise ValueError("mx_gemm needs TILED scales; convert with mx_retile()")
@@ -148,11 +149,14 @@ def mx_gemm(a: MXOperand, b: MXOperand, *, bias: torch.Tensor | None = None,
         out = torch.empty((M, N), dtype=out_dtype, device=dev)
     elif out.shape != (M, N) or out.dtype != out_dtype or out.stride(1) != 1:
         raise ValueError("out has the wrong shape, dtype or layout")
+    lib = _lib.load()
+    ws_bytes = check(lib.anima_mx_gemm_workspace_bytes(M, N, K)) if split_k else 0
+    ws = _lib.workspace(ws_bytes, dev, "gemm_splitk") if ws_bytes else None
     with torch.cuda.device(dev):
-        check(_lib.load().anima_mx_gemm(
+        check(lib.anima_mx_gemm_ws(
             ptr(a.codes), ptr(a.scales), ptr(b.codes), ptr(b.scales), ptr(out), M, N, K, out.stride(0),
-            ptr(bias), 1 if out_dtype == torch.float32 else 0, ptr(_lib.status_word(dev)),
-            _lib.stream_ptr(dev)))
+            ptr(bias), 1 if out_dtype == torch.float32 else 0, ptr(ws), ws.numel() if ws is not None else 0,
+            ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)))
     return out
 
 

@@ -147,6 +147,13 @@ def workload_config(n_gpus: int) -> dict:
 
 
 # ----------------------------------------------------------------------------- GPU arm
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the GEMM kernel, from the ncu capture
+# summarised in profiles/mx_gemm2_fwd_32768x8192x2048.md (a number from a profiler run, not re-measured here).
+NCU_TRAFFIC_BYTES = 584.0e6
+NCU_TRAFFIC_NOTE = ("ncu, forward launch 32768x8192x2048: 584 MB moved vs 623 MB algorithmic "
+                    "(codes of A and B, scales, bf16 C); the step's launches average 2 M N K = 825 GF")
+
+
 class Shape:
     """Device-resident operands of one linear shape plus pinned host copies for the e2e leg."""
 
@@ -215,16 +222,46 @@ def run_gpu_arm(args) -> None:
     ops.lokr_merge_quantize = count(ops.lokr_merge_quantize, 1)
     ops.lokr_kron_backward = count(ops.lokr_kron_backward, 2)
 
+    # e2e leg: every step's inputs come from pinned host memory. Two device slots per shape let the
+    # copy of the NEXT step's inputs (copy stream) run under the current step's kernels; the timed
+    # region waits for every copy it issued.
+    copy_stream = torch.cuda.Stream(device=dev)
+
+    class Slot:
+        def __init__(self, s):
+            self.x, self.dy = torch.empty_like(s.x), torch.empty_like(s.dy)
+            self.ready, self.free = torch.cuda.Event(), torch.cuda.Event()
+            self.free.record()
+
+    def prefetch(s, slot):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(slot.free)              # the kernels that read this slot are done
+            slot.x.copy_(s.x_host, non_blocking=True)
+            slot.dy.copy_(s.dy_host, non_blocking=True)
+            slot.ready.record(copy_stream)
+
+    def prime_e2e():
+        for s in shapes:
+            if not hasattr(s, "slots"):
+                s.slots, s.cur = [Slot(s), Slot(s)], 0
+            prefetch(s, s.slots[s.cur])
+
     def step(e2e: bool):
         off = 0
         for i, s in enumerate(shapes):
+            x, dy = s.x, s.dy
             if e2e:
-                s.x.copy_(s.x_host, non_blocking=True)
-                s.dy.copy_(s.dy_host, non_blocking=True)
+                slot = s.slots[s.cur]
+                torch.cuda.current_stream().wait_event(slot.ready)
+                x, dy = slot.x, slot.dy
             s.w1.grad = s.w2.grad = None
             clear_activation_memo()     # x is the same tensor object every step: quantise it again, as training does
-            y = lokr_linear_fused(s.x, s.W, None, s.w1, s.w2, 1.0)
-            y.backward(s.dy)
+            y = lokr_linear_fused(x, s.W, None, s.w1, s.w2, 1.0)
+            y.backward(dy)
+            if e2e:
+                slot.free.record()
+                s.cur ^= 1
+                prefetch(s, s.slots[s.cur])                # inputs of the next step
             for p in (s.w1, s.w2):
                 flat_grad[off:off + p.numel()].copy_(p.grad.reshape(-1))
                 off += p.numel()
@@ -251,6 +288,8 @@ def run_gpu_arm(args) -> None:
         e0.record()
         for _ in range(steps):
             step(e2e)
+        if e2e:
+            torch.cuda.current_stream().wait_stream(copy_stream)   # count every copy issued inside the region
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
@@ -272,6 +311,7 @@ def run_gpu_arm(args) -> None:
     gemm_ms = sum(a.elapsed_time(b) for a, b, _ in gemm_events)
     gemm_fl = sum(f for _, _, f in gemm_events)
     n_gemm = len(gemm_events)
+    prime_e2e()
     ms_e2e = timed(True, args.steps, 1)
     _lib.check_status_word(dev)
 
@@ -296,8 +336,9 @@ def run_gpu_arm(args) -> None:
             "e2e": {"value": fl / (ms_e2e / args.steps * 1e-3) / 1e12, "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": n_launch,
-            "roofline": {"bound": "tensor", "kernel": "mx_gemm_kernel", "achieved": achieved, "peak": peak,
-                         "unit": UNIT, "frac": achieved / peak, "traffic": None,
+            "roofline": {"bound": "tensor", "kernel": "mx_gemm2_kernel", "achieved": achieved, "peak": peak,
+                         "unit": UNIT, "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES,
+                         "traffic_note": NCU_TRAFFIC_NOTE,
                          "peak_source": ("2 x measured sustained bf16 cuBLAS TFLOP/s (MEASURED_PEAKS.json); "
                                          "no measured fp8 figure exists" if bf16_peak else
                                          "2 x 1400 TFLOP/s fallback"),
@@ -316,7 +357,7 @@ def run_gpu_arm(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     args = ap.parse_args()

@@ -112,6 +112,19 @@ int anima_mx_gemm(const uint8_t* a_codes, const uint8_t* a_scales,
                   void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
                   const void* bias_bf16, int out_dtype, int32_t* status, void* stream);
 
+/* The same GEMM with caller scratch for split-K. A small output with a long contraction (the
+ * T-LoKr factor gradients, ref: tlokr.py:619-667: [r, vq] and [vp, r] outputs contracted over
+ * rows * uq = 262144) has only 1 - 8 output tiles; with a workspace the contraction is split
+ * over the SMs into fp32 partial tiles that a second kernel sums in a fixed order (bit-
+ * reproducible, no atomics). anima_mx_gemm_workspace_bytes returns the scratch such a shape
+ * uses, or 0 when the shape is not split (workspace may then be NULL). */
+int64_t anima_mx_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int anima_mx_gemm_ws(const uint8_t* a_codes, const uint8_t* a_scales,
+                     const uint8_t* b_codes, const uint8_t* b_scales,
+                     void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
+                     const void* bias_bf16, int out_dtype, void* workspace,
+                     int64_t workspace_bytes, int32_t* status, void* stream);
+
 /* ---------------------------------------------------------------- LoKr merged weight
  * ref: lokr_patch.py:76-84 (merged = W + alpha * kron(w1, w2)) followed by the two
  *      weight quantisations of fp8_quant.py:234-235 / :501.

@@ -105,6 +105,42 @@ def test_more_tiles_than_sms_exercises_both_accumulator_buffers(variant):
     _gemm_case(20480, 128, 384, seed=12)
 
 
+@pytest.mark.parametrize("M,N,K", [
+    (128, 256, 32768),   # T-LoKr dB shape class: one tile, 256 K-blocks
+    (256, 128, 16384),   # dA shape class: two tiles
+    (128, 1024, 8192),   # four wide tiles
+    (1024, 128, 8192),   # eight narrow tiles
+    (100, 72, 4128),     # ragged tile, K tail of 32
+])
+@pytest.mark.parametrize("out_dtype", [BF16, torch.float32])
+def test_split_k_matches_oracle_and_single_pass(M, N, K, out_dtype):
+    """Small outputs with a long contraction are split over K into fp32 partial tiles summed in a fixed
+    order: same oracle tolerance, agreement with the unsplit kernel, bit-identical on repetition."""
+    ops, lib = _ops()
+    assert lib.load().anima_mx_gemm_workspace_bytes(M, N, K) > 0
+    x = _acts(M, K, M + K).cuda()
+    w = _acts(N, K, N + K, std=0.02, outliers=False).cuda()
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(3)) * 0.5).to(BF16).cuda()
+    xa, _ = ops.mx_quantize(x, rowwise=True, layout=0)
+    wb, _ = ops.mx_quantize(w, rowwise=True, layout=0)
+    a, b = ops.mx_retile(xa), ops.mx_retile(wb)
+    c = ops.mx_gemm(a, b, bias=bias, out_dtype=out_dtype)
+    again = ops.mx_gemm(a, b, bias=bias, out_dtype=out_dtype)
+    single = ops.mx_gemm(a, b, bias=bias, out_dtype=out_dtype, split_k=False)
+    torch.cuda.synchronize()
+    lib.check_status_word(c.device)
+    want = _oracle_product(xa, wb, bias, out_bf16=out_dtype == BF16)
+    np.testing.assert_allclose(c.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+    assert torch.equal(c, again)
+    torch.testing.assert_close(c.float(), single.float(), rtol=1e-2 if out_dtype == BF16 else 1e-4, atol=1e-3)
+
+
+def test_split_k_is_not_used_for_large_outputs_or_short_contractions():
+    _, lib = _ops()
+    f = lib.load().anima_mx_gemm_workspace_bytes
+    assert f(32768, 2048, 2048) == 0 and f(128, 128, 2048) == 0 and f(32768, 128, 32768) == 0
+
+
 def test_bias_and_fp32_output(variant):
     _gemm_case(256, 512, 256, seed=5, bias=True)
     _gemm_case(256, 512, 256, seed=6, bias=True, out_dtype=torch.float32)
