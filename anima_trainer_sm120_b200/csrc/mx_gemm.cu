@@ -182,6 +182,10 @@ struct GemmParams {
   // partial tile to partial[s][M][N]; splitk_finalize_kernel then sums the splits in index order.
   int splits, kb_per_split;
   float* partial;
+  // Epilogue: C = alpha * (A . B^T) + bias + residual (residual bf16 [M, N], row pitch ldr; may alias C).
+  const __nv_bfloat16* residual;
+  int64_t ldr;
+  float alpha;
 };
 
 
@@ -190,13 +194,25 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int co
   if (row >= p.M || col >= p.N) return;
   float f[32];
 #pragma unroll
-  for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+  for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
   if (p.bias) {
 #pragma unroll
     for (int j = 0; j < 32; j += 8) {
       if (col + j < p.N) {
         float b[8];
         unpack8(*reinterpret_cast<const uint4*>(p.bias + col + j), b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[j + e] += b[e];
+      }
+    }
+  }
+  if (p.residual) {
+    const __nv_bfloat16* res = p.residual + static_cast<int64_t>(row) * p.ldr + col;
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      if (col + j < p.N) {
+        float b[8];
+        unpack8(*reinterpret_cast<const uint4*>(res + j), b);
 #pragma unroll
         for (int e = 0; e < 8; ++e) f[j + e] += b[e];
       }
@@ -353,6 +369,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         dst.ldc = p.N;
         dst.out_fp32 = 1;
         dst.bias = nullptr;
+        dst.residual = nullptr;
+        dst.alpha = 1.f;
       }
       if (!mbar_wait(acc_full_bar(as), (it >> 1) & 1u, &abort_flag)) { ok = false; break; }
       tc_fence_after();
@@ -402,11 +420,19 @@ __global__ void __launch_bounds__(256) splitk_finalize_kernel(const GemmParams p
       const float4 v = *reinterpret_cast<const float4*>(src + s * plane);
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
+    acc.x *= p.alpha; acc.y *= p.alpha; acc.z *= p.alpha; acc.w *= p.alpha;
     if (p.bias) {
       acc.x += __bfloat162float(p.bias[col]);
       acc.y += __bfloat162float(p.bias[col + 1]);
       acc.z += __bfloat162float(p.bias[col + 2]);
       acc.w += __bfloat162float(p.bias[col + 3]);
+    }
+    if (p.residual) {
+      const __nv_bfloat16* res = p.residual + row * p.ldr + col;
+      acc.x += __bfloat162float(res[0]);
+      acc.y += __bfloat162float(res[1]);
+      acc.z += __bfloat162float(res[2]);
+      acc.w += __bfloat162float(res[3]);
     }
     if (p.out_fp32) {
       *reinterpret_cast<float4*>(static_cast<float*>(p.c) + row * p.ldc + col) = acc;
@@ -679,6 +705,9 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // lie outside C. Two staging buffers alternate; named barrier 1 joins the 128 epilogue threads.
     const int quad = warp & 3;
     const int r_in = quad * 32 + lane;  // row inside this CTA's 128 accumulator rows
+    // residual == C (bf16, same pitch): the tile is ADDED to C by the TMA store (bf16 add at the memory side)
+    // instead of being loaded by the epilogue threads, whose per-chunk loads would serialise on latency.
+    const bool reduce_add = p.residual && static_cast<const void*>(p.residual) == p.c && !p.out_fp32 && p.ldr == p.ldc;
     const bool issuer = threadIdx.x == 64;
     const uint32_t leader_empty[2] = {map_to_cta(acc_empty_bar(0), 0), map_to_cta(acc_empty_bar(1), 0)};
     bool ok = true;
@@ -704,13 +733,25 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int col0 = nt * kBN2 + chunk * 32;
         float f[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
         if (p.bias) {
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             if (col0 + j < p.N) {
               float bv[8];
               unpack8(*reinterpret_cast<const uint4*>(p.bias + col0 + j), bv);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[j + e] += bv[e];
+            }
+          }
+        }
+        if (p.residual && !reduce_add && row0 + r_in < p.M) {
+          const __nv_bfloat16* res = p.residual + static_cast<int64_t>(row0 + r_in) * p.ldr + col0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (col0 + j < p.N) {
+              float bv[8];
+              unpack8(*reinterpret_cast<const uint4*>(res + j), bv);
 #pragma unroll
               for (int e = 0; e < 8; ++e) f[j + e] += bv[e];
             }
@@ -743,9 +784,15 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the TMA engine
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (issuer) {
-          asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&map_c),
-                       "r"(stage), "r"(col0), "r"(row0)
-                       : "memory");
+          if (reduce_add)
+            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                             &map_c),
+                         "r"(stage), "r"(col0), "r"(row0)
+                         : "memory");
+          else
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&map_c),
+                         "r"(stage), "r"(col0), "r"(row0)
+                         : "memory");
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // the other buffer may be rewritten
         }
@@ -924,8 +971,10 @@ using namespace anima;
 
 static int mx_gemm_impl(const uint8_t* a_codes, const uint8_t* a_scales, const uint8_t* b_codes,
                         const uint8_t* b_scales, void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
-                        const void* bias, int out_dtype, void* workspace, int64_t workspace_bytes, int32_t* status,
-                        void* stream) {
+                        const void* bias, const void* residual, int64_t ldr, float alpha, int out_dtype,
+                        void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
+  ANIMA_REQUIRE(!residual || (aligned16(residual) && ldr >= N && ldr % 8 == 0), ANIMA_E_ALIGN,
+                "mx_gemm: residual must be 16-byte aligned with a row pitch that is a multiple of 8 elements");
   ANIMA_REQUIRE(a_codes && a_scales && b_codes && b_scales && c, ANIMA_E_ARG, "mx_gemm: null pointer");
   ANIMA_REQUIRE(M > 0 && N > 0 && K > 0 && ldc >= N, ANIMA_E_ARG, "mx_gemm: bad sizes M=%lld N=%lld K=%lld ldc=%lld",
                 (long long)M, (long long)N, (long long)K, (long long)ldc);
@@ -956,6 +1005,9 @@ static int mx_gemm_impl(const uint8_t* a_codes, const uint8_t* a_scales, const u
   p.sfb_rt = static_cast<int>(ceil_div(N, 128));
   p.splits = 1;
   p.kb_per_split = p.k_blocks;
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.ldr = ldr;
+  p.alpha = alpha;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (use_pair(M, N)) return launch_pair(a_codes, b_codes, p, s);
   if (workspace) {
@@ -981,8 +1033,8 @@ static int mx_gemm_impl(const uint8_t* a_codes, const uint8_t* a_scales, const u
 extern "C" int anima_mx_gemm(const uint8_t* a_codes, const uint8_t* a_scales, const uint8_t* b_codes,
                              const uint8_t* b_scales, void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
                              const void* bias, int out_dtype, int32_t* status, void* stream) {
-  return mx_gemm_impl(a_codes, a_scales, b_codes, b_scales, c, M, N, K, ldc, bias, out_dtype, nullptr, 0, status,
-                      stream);
+  return mx_gemm_impl(a_codes, a_scales, b_codes, b_scales, c, M, N, K, ldc, bias, nullptr, 0, 1.f, out_dtype, nullptr,
+                      0, status, stream);
 }
 
 extern "C" int64_t anima_mx_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
@@ -992,10 +1044,10 @@ extern "C" int64_t anima_mx_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K
   return splits > 1 ? static_cast<int64_t>(splits) * M * N * 4 : 0;
 }
 
-extern "C" int anima_mx_gemm_ws(const uint8_t* a_codes, const uint8_t* a_scales, const uint8_t* b_codes,
+extern "C" int anima_mx_gemm_ex(const uint8_t* a_codes, const uint8_t* a_scales, const uint8_t* b_codes,
                                 const uint8_t* b_scales, void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
-                                const void* bias, int out_dtype, void* workspace, int64_t workspace_bytes,
-                                int32_t* status, void* stream) {
-  return mx_gemm_impl(a_codes, a_scales, b_codes, b_scales, c, M, N, K, ldc, bias, out_dtype, workspace,
-                      workspace_bytes, status, stream);
+                                const void* bias, const void* residual, int64_t ldr, float alpha, int out_dtype,
+                                void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
+  return mx_gemm_impl(a_codes, a_scales, b_codes, b_scales, c, M, N, K, ldc, bias, residual, ldr, alpha, out_dtype,
+                      workspace, workspace_bytes, status, stream);
 }

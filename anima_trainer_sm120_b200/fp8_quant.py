@@ -137,9 +137,15 @@ class MXFP8FrozenLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, W_mx: QuantWeight, W_bf16, bias=None):
         x_row, _ = quantize_activation(x, colwise=False)
-        y = ops.mx_gemm(x_row, W_mx.row, bias=_bias_bf16(bias))
         ctx.W_mx, ctx.W_bf16, ctx.has_bias = W_mx, W_bf16, bias is not None
-        return y.reshape(*x.shape[:-1], W_bf16.shape[0]).to(x.dtype)
+        n_out = W_bf16.shape[0]
+        if x.dtype == BF16:
+            # allocated in its final shape (not a view of a 2-D result), so a following op may update it in place
+            y = torch.empty(*x.shape[:-1], n_out, dtype=BF16, device=x.device)
+            ops.mx_gemm(x_row, W_mx.row, bias=_bias_bf16(bias), out=y.view(-1, n_out))
+            return y
+        y = ops.mx_gemm(x_row, W_mx.row, bias=_bias_bf16(bias))
+        return y.reshape(*x.shape[:-1], n_out).to(x.dtype)
 
     @staticmethod
     def backward(ctx, grad_y):

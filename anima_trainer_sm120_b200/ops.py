@@ -130,9 +130,11 @@ def mx_retile(op: MXOperand) -> MXOperand:
 
 
 def mx_gemm(a: MXOperand, b: MXOperand, *, bias: torch.Tensor | None = None,
-            out_dtype: torch.dtype = BF16, out: torch.Tensor | None = None, split_k: bool = True) -> torch.Tensor:
-    """``C[M,N] = A[M,K] . B[N,K]^T (+ bias)`` on the tcgen05 block-scaled tensor path. Small outputs with a
-    long contraction are split over K through a scratch buffer unless ``split_k`` is False."""
+            out_dtype: torch.dtype = BF16, out: torch.Tensor | None = None, split_k: bool = True,
+            residual: torch.Tensor | None = None, alpha: float = 1.0) -> torch.Tensor:
+    """``C[M,N] = alpha * A[M,K] . B[N,K]^T (+ bias) (+ residual)`` on the tcgen05 block-scaled tensor path.
+    ``residual`` is bf16 [M, N] and may be ``out`` itself. Small outputs with a long contraction are split over K
+    through a scratch buffer unless ``split_k`` is False."""
     dev = _lib.require_cuda(a.codes, a.scales, b.codes, b.scales, bias)
     if a.layout != SCALES_TILED or b.layout != SCALES_TILED:
         raise ValueError("mx_gemm needs TILED scales; convert with mx_retile()")
@@ -145,6 +147,10 @@ def mx_gemm(a: MXOperand, b: MXOperand, *, bias: torch.Tensor | None = None,
     if bias is not None and (bias.dtype != BF16 or bias.numel() != b.rows or not bias.is_contiguous()):
         raise ValueError("bias must be contiguous bfloat16 of length N")
     M, N, K = a.rows, b.rows, a.k
+    if residual is not None:
+        _lib.require_cuda(a.codes, residual)
+        if residual.dtype != BF16 or residual.shape != (M, N) or residual.stride(1) != 1:
+            raise ValueError("residual must be bfloat16 [M, N] with unit column stride")
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=dev)
     elif out.shape != (M, N) or out.dtype != out_dtype or out.stride(1) != 1:
@@ -153,9 +159,10 @@ def mx_gemm(a: MXOperand, b: MXOperand, *, bias: torch.Tensor | None = None,
     ws_bytes = check(lib.anima_mx_gemm_workspace_bytes(M, N, K)) if split_k else 0
     ws = _lib.workspace(ws_bytes, dev, "gemm_splitk") if ws_bytes else None
     with torch.cuda.device(dev):
-        check(lib.anima_mx_gemm_ws(
+        check(lib.anima_mx_gemm_ex(
             ptr(a.codes), ptr(a.scales), ptr(b.codes), ptr(b.scales), ptr(out), M, N, K, out.stride(0),
-            ptr(bias), 1 if out_dtype == torch.float32 else 0, ptr(ws), ws.numel() if ws is not None else 0,
+            ptr(bias), ptr(residual), residual.stride(0) if residual is not None else 0, float(alpha),
+            1 if out_dtype == torch.float32 else 0, ptr(ws), ws.numel() if ws is not None else 0,
             ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)))
     return out
 

@@ -229,10 +229,13 @@ def _q(t2d: torch.Tensor, *, col: bool = False):
 
 class _MXStructuredLoKr(torch.autograd.Function):
     """The same delta with every factor GEMM in MXFP8 on the tensor cores (the reference's
-    ``_FP8StructuredLoKr`` uses TE block-FP8 for them); the 8x8 mix stays in bf16."""
+    ``_FP8StructuredLoKr`` uses TE block-FP8 for them); the 8x8 mix stays in bf16.
+
+    With ``base`` given the result is ``base + alpha * delta``, formed in the epilogue of the last GEMM
+    (the reference's separate ``torch.add(base, delta, alpha=)``, ``tlokr.py:757-759``)."""
 
     @staticmethod
-    def forward(ctx, x, w1, w2_a, w2_b, mask):
+    def forward(ctx, x, w1, w2_a, w2_b, mask, base=None, alpha: float = 1.0):
         c = w1.to(BF16)
         aq, aq_col = _q(w2_a.detach(), col=True)      # A [vp, r]: row form for out, column form for dgrad
         bq, bq_col = _q(w2_b.detach(), col=True)      # B [r, vq]
@@ -242,10 +245,16 @@ class _MXStructuredLoKr(torch.autograd.Function):
         hidden = ops.mx_gemm(gq, bq).view(*grouped.shape[:-1], w2_b.shape[0])
         mixed = rank_mix(hidden, c, mask)
         mq, _ = _q(mixed.reshape(-1, mixed.shape[-1]))
-        out = ops.mx_gemm(mq, aq)
         ctx.save_for_backward(x, w1, w2_a, w2_b, *(() if mask is None else (mask,)))
         ctx.has_mask, ctx.ops = mask is not None, (aq_col, bq, bq_col)
-        return out.view(*x.shape[:-1], -1).to(x.dtype)
+        ctx.has_base, ctx.alpha = base is not None, float(alpha) if base is not None else 1.0
+        if base is None:
+            return ops.mx_gemm(mq, aq).view(*x.shape[:-1], -1).to(x.dtype)
+        # base (bf16, contiguous) is updated in place: base += alpha * delta, added by the GEMM's stores
+        res = base.view(-1, w2_a.shape[0])
+        ops.mx_gemm(mq, aq, residual=res, alpha=float(alpha), out=res)
+        ctx.mark_dirty(base)
+        return base
 
     @staticmethod
     def backward(ctx, grad_output):
@@ -264,21 +273,31 @@ class _MXStructuredLoKr(torch.autograd.Function):
         _, mq_col = _q(mixed.reshape(-1, rank), col=True)
         gb2 = grad_output.reshape(-1, vp)
         gbq, gbq_col = _q(gb2, col=True)
-        g_a = ops.mx_gemm(gbq_col, mq_col, out_dtype=torch.float32)          # grad_blocks^T @ mixed   [vp, r]
-        g_mixed = ops.mx_gemm(gbq, aq_col).view(*mixed.shape)                # grad_blocks @ A         [.., r]
+        g_a = ops.mx_gemm(gbq_col, mq_col, out_dtype=torch.float32, alpha=ctx.alpha)   # alpha * grad_blocks^T @ mixed [vp, r]
+        g_mixed = ops.mx_gemm(gbq, aq_col, alpha=ctx.alpha).view(*mixed.shape)         # alpha * grad_blocks @ A       [.., r]
         g_c = rank_mix_wgrad(g_mixed, hidden, mask)
         g_hidden = rank_mix(g_mixed, c, mask, transpose=True)
         ghq, ghq_col = _q(g_hidden.reshape(-1, rank), col=True)
         g_b = ops.mx_gemm(ghq_col, gq_col, out_dtype=torch.float32)          # grad_hidden^T @ grouped [r, vq]
         g_x = ops.mx_gemm(ghq, bq_col).view(x.shape)                         # grad_hidden @ B
-        return g_x.to(x.dtype), g_c.to(w1.dtype), g_a.to(w2_a.dtype), g_b.to(w2_b.dtype), None
+        return (g_x.to(x.dtype), g_c.to(w1.dtype), g_a.to(w2_a.dtype), g_b.to(w2_b.dtype), None,
+                grad_output if ctx.has_base else None, None)
 
 
 _FP8StructuredLoKr = _MXStructuredLoKr  # name used by anima-trainer
 
 
-def _structured_delta(module, x: torch.Tensor, *, fp8: bool) -> torch.Tensor:
-    """``x @ kron(W1, A @ B).T`` for the current timestep context (reference :679-735)."""
+def _structured_delta(module, x: torch.Tensor, *, fp8: bool, base: torch.Tensor | None = None,
+                      alpha: float = 1.0) -> torch.Tensor:
+    """``x @ kron(W1, A @ B).T`` for the current timestep context (reference :679-735); with ``base`` given,
+    ``base + alpha * delta`` (fused into the last GEMM on the quantised path)."""
+    def run(fn, *args):
+        if base is None:
+            return fn.apply(*args)
+        if fn is _MXStructuredLoKr and base.dtype == BF16 and base.is_contiguous() and base.requires_grad:
+            return fn.apply(*args, base, alpha)
+        return torch.add(base, fn.apply(*args), alpha=alpha)
+
     state = _current_state()
     rank, min_rank = module._tlokr_rank, module._tlokr_min_rank
     w1 = module.lokr_w1
@@ -292,18 +311,18 @@ def _structured_delta(module, x: torch.Tensor, *, fp8: bool) -> torch.Tensor:
         active = active_rank_for_timestep(state.uniform_timestep, max_rank=rank, min_rank=min_rank)
         if active % 8 == 0:
             fn = _MXStructuredLoKr if fp8 and active % 32 == 0 else _StructuredLoKr
-            return fn.apply(x, w1, module.lokr_w2_a[:, :active], module.lokr_w2_b[:active], None)
+            return run(fn, x, w1, module.lokr_w2_a[:, :active], module.lokr_w2_b[:active], None)
         key = ("uniform", rank, active, x.dtype, x.device, x.shape[0])
         mask = state.masks.get(key)
         if mask is None:
             mask = (torch.arange(rank, device=x.device) < active).to(x.dtype).expand(x.shape[0], rank).contiguous()
             state.masks[key] = mask
-        return (_MXStructuredLoKr if fp8 else _StructuredLoKr).apply(x, w1, module.lokr_w2_a, module.lokr_w2_b, mask)
+        return run(_MXStructuredLoKr if fp8 else _StructuredLoKr, x, w1, module.lokr_w2_a, module.lokr_w2_b, mask)
     mask = state.mask(max_rank=rank, min_rank=min_rank, dtype=x.dtype, device=x.device)
     if x.shape[0] != mask.shape[0]:
         raise RuntimeError(f"{module.lora_name}: activation batch {x.shape[0]} does not match timestep "
                            f"batch {mask.shape[0]}")
-    return (_MXStructuredLoKr if fp8 else _StructuredLoKr).apply(x, w1, module.lokr_w2_a, module.lokr_w2_b, mask)
+    return run(_MXStructuredLoKr if fp8 else _StructuredLoKr, x, w1, module.lokr_w2_a, module.lokr_w2_b, mask)
 
 
 def forward(module, x: torch.Tensor) -> torch.Tensor:
@@ -317,5 +336,4 @@ def forward(module, x: torch.Tensor) -> torch.Tensor:
         base = fp8_frozen_linear(x, base_q, org.weight, org.bias)
     else:
         base = F.linear(x, org.weight, org.bias)
-    delta = _structured_delta(module, x, fp8=quantised)
-    return torch.add(base, delta, alpha=module._tlokr_alpha)
+    return _structured_delta(module, x, fp8=quantised, base=base, alpha=module._tlokr_alpha)

@@ -112,18 +112,25 @@ int anima_mx_gemm(const uint8_t* a_codes, const uint8_t* a_scales,
                   void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
                   const void* bias_bf16, int out_dtype, int32_t* status, void* stream);
 
-/* The same GEMM with caller scratch for split-K. A small output with a long contraction (the
- * T-LoKr factor gradients, ref: tlokr.py:619-667: [r, vq] and [vp, r] outputs contracted over
- * rows * uq = 262144) has only 1 - 8 output tiles; with a workspace the contraction is split
- * over the SMs into fp32 partial tiles that a second kernel sums in a fixed order (bit-
- * reproducible, no atomics). anima_mx_gemm_workspace_bytes returns the scratch such a shape
- * uses, or 0 when the shape is not split (workspace may then be NULL). */
+/* The same GEMM with a fused epilogue and caller scratch for split-K:
+ *   C = alpha * (A . B^T) + bias + residual
+ * residual (may be NULL) is bf16 [M, N] with row pitch ldr elements and MAY ALIAS C (every element
+ * is read before it is written, by the thread that writes it): T-LoKr's
+ * torch.add(base, delta, alpha=alpha) (ref: tlokr.py:757-759) becomes the epilogue of the last
+ * delta GEMM, written over base.
+ * Split-K: a small output with a long contraction (the T-LoKr factor gradients, ref:
+ * tlokr.py:619-667: [r, vq] and [vp, r] outputs contracted over rows * uq = 262144) has only
+ * 1 - 8 output tiles; with a workspace the contraction is split over the SMs into fp32 partial
+ * tiles that a second kernel sums in a fixed order (bit-reproducible, no atomics).
+ * anima_mx_gemm_workspace_bytes returns the scratch such a shape uses, or 0 when the shape is not
+ * split (workspace may then be NULL). */
 int64_t anima_mx_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
-int anima_mx_gemm_ws(const uint8_t* a_codes, const uint8_t* a_scales,
+int anima_mx_gemm_ex(const uint8_t* a_codes, const uint8_t* a_scales,
                      const uint8_t* b_codes, const uint8_t* b_scales,
                      void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
-                     const void* bias_bf16, int out_dtype, void* workspace,
-                     int64_t workspace_bytes, int32_t* status, void* stream);
+                     const void* bias_bf16, const void* residual_bf16, int64_t ldr, float alpha,
+                     int out_dtype, void* workspace, int64_t workspace_bytes,
+                     int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------- LoKr merged weight
  * ref: lokr_patch.py:76-84 (merged = W + alpha * kron(w1, w2)) followed by the two

@@ -3,10 +3,15 @@ checkout is available; the .npz files it writes are committed, this script docum
 
     TRITON_INTERPRET=1 python tests/golden/make_golden.py /path/to/anima-trainer
 
-* The reference's Triton kernels (quantiser, GEMM, AdaLN, gated add, rank mix) execute
-  under the Triton CPU interpreter, i.e. the reference source itself computes the vectors.
+* The reference's Triton kernels that the Triton CPU interpreter can execute (quantiser, AdaLN
+  forward / dx / dscale+dshift, the gated-add dgate reduction, rank-mix wgrad) run under it, i.e.
+  the reference source itself computes those vectors.
 * Its torch code that runs on CPU (dequantize_rowwise, _StructuredLoKr, the timestep mask and
   schedule, the CPU branches of rank_mix / rank_mix_wgrad) is imported unmodified.
+* What the interpreter cannot run (tl.dot_scaled; kernels doing bf16 arithmetic: rank mix forward,
+  gated-add forward) comes from the reference's own stated equivalents: quantiser +
+  dequantize_rowwise + fp32 matmul for the GEMM, the torch branch of rank_mix, the eager
+  expression x + gate * y.
 bf16 tensors are stored as uint16 bit patterns.
 """
 from __future__ import annotations

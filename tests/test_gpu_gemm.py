@@ -135,6 +135,32 @@ def test_split_k_matches_oracle_and_single_pass(M, N, K, out_dtype):
     torch.testing.assert_close(c.float(), single.float(), rtol=1e-2 if out_dtype == BF16 else 1e-4, atol=1e-3)
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (200, 136, 96), (2048, 256, 128), (128, 256, 8192)])
+def test_alpha_and_residual_epilogue(M, N, K, variant):
+    """C = alpha * A.B^T + bias + residual, also written over the residual buffer itself."""
+    ops, lib = _ops()
+    x = _acts(M, K, M + 1).cuda()
+    w = _acts(N, K, N + 2, std=0.02, outliers=False).cuda()
+    g = torch.Generator().manual_seed(M + N + K)
+    bias = (torch.randn(N, generator=g) * 0.5).to(BF16).cuda()
+    res = torch.randn(M, N, generator=g).to(BF16).cuda()
+    xa, _ = ops.mx_quantize(x, rowwise=True, layout=0)
+    wb, _ = ops.mx_quantize(w, rowwise=True, layout=0)
+    a, b = ops.mx_retile(xa), ops.mx_retile(wb)
+    alpha = 0.375
+    want = alpha * _oracle_product(xa, wb, None, out_bf16=False) + bias.float().cpu().numpy() + res.float().cpu().numpy()
+    c = ops.mx_gemm(a, b, bias=bias, residual=res, alpha=alpha)
+    c32 = ops.mx_gemm(a, b, bias=bias, residual=res, alpha=alpha, out_dtype=torch.float32)
+    inplace = res.clone()
+    ops.mx_gemm(a, b, bias=bias, residual=inplace, alpha=alpha, out=inplace)
+    torch.cuda.synchronize()
+    lib.check_status_word(c.device)
+    np.testing.assert_allclose(c.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(c32.cpu().numpy(), want, rtol=1e-3, atol=2e-3)
+    # in place the CTA-pair kernel lets its stores add the (bf16-rounded) tile to C: one more rounding
+    np.testing.assert_allclose(inplace.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+
+
 def test_split_k_is_not_used_for_large_outputs_or_short_contractions():
     _, lib = _ops()
     f = lib.load().anima_mx_gemm_workspace_bytes
