@@ -90,6 +90,28 @@ __device__ __forceinline__ float warp_sum(float v) {
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
+// Sum of `blocks` partial vectors of 64 floats (partial[b * 64 + e]) by one CTA of kFinalizeThreads threads:
+// group q = thread / 64 adds its contiguous slice of the blocks in ascending order, then thread e < 64 adds
+// the group sums in ascending order. The association is fixed, so the result is reproducible, and no thread
+// walks more than blocks / 16 dependent loads. Returns the total in threads 0..63 (0 elsewhere).
+constexpr int kFinalizeThreads = 1024;
+__device__ __forceinline__ float sum_partials_64(const float* __restrict__ partial, int blocks) {
+  __shared__ float group_sum[kFinalizeThreads / 64][64];
+  const int e = threadIdx.x & 63, q = threadIdx.x >> 6;
+  const int per = (blocks + kFinalizeThreads / 64 - 1) / (kFinalizeThreads / 64);
+  const int b0 = q * per, b1 = min(blocks, b0 + per);
+  float s = 0.f;
+  for (int b = b0; b < b1; ++b) s += partial[b * 64 + e];
+  group_sum[q][e] = s;
+  __syncthreads();
+  float total = 0.f;
+  if (threadIdx.x < 64) {
+#pragma unroll
+    for (int g = 0; g < kFinalizeThreads / 64; ++g) total += group_sum[g][e];
+  }
+  return total;
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

@@ -35,13 +35,18 @@ struct MergeLoader {
   __nv_bfloat16* merged;  // optional [N, K]
   float alpha;
   int64_t K, vp, vq, uq;
-  __device__ __forceinline__ uint4 operator()(int64_t r, int64_t c) const {
+  using Raw = uint4;
+  static constexpr bool kZeroSafe = false;   // finish reads the factors at (row, col)
+  __device__ __forceinline__ Raw fetch(int64_t r, int64_t c) const { return ldg_stream16(w + r * K + c); }
+  __device__ __forceinline__ uint4 operator()(int64_t r, int64_t c) const { return finish(fetch(r, c), r, c); }
+  // W comes from HBM (fetch); the factors are small and cache-resident and are read here.
+  __device__ __forceinline__ uint4 finish(const Raw& raw, int64_t r, int64_t c) const {
     const int ri = static_cast<int>(r), ci = static_cast<int>(c);   // N, K < 2^31 is checked on the host
     const int i = ri / static_cast<int>(vp), p = ri - i * static_cast<int>(vp);
     const int j = ci / static_cast<int>(vq), q = ci - j * static_cast<int>(vq);  // vq % 8 == 0: the 8 columns share j
     const float a = to_f32(w1[i * uq + j]);
     float wv[8], o[8], f2[8];
-    unpack8(ldg_stream16(w + r * K + c), wv);
+    unpack8(raw, wv);
     const F* w2p = w2 + p * vq + q;  // 8 consecutive factors: vq % 8 == 0 keeps them 16/32-byte aligned
     if constexpr (sizeof(F) == 4) {
       const float4 lo = *reinterpret_cast<const float4*>(w2p), hi = *reinterpret_cast<const float4*>(w2p + 4);
@@ -153,11 +158,9 @@ kron_backward_kernel(const G* __restrict__ dw, const F* __restrict__ w1, const F
 
 __global__ void kron_backward_finalize_kernel(const float* __restrict__ partial, int blocks, float alpha,
                                               int up, int uq, float* __restrict__ dw1) {
+  const float s = sum_partials_64(partial, blocks);
   const int i = threadIdx.x / kMaxFactor, j = threadIdx.x % kMaxFactor;
-  if (i >= up || j >= uq) return;
-  float s = 0.f;
-  for (int b = 0; b < blocks; ++b) s += partial[b * (kMaxFactor * kMaxFactor) + threadIdx.x];
-  dw1[i * uq + j] = alpha * s;
+  if (threadIdx.x < kMaxFactor * kMaxFactor && i < up && j < uq) dw1[i * uq + j] = alpha * s;
 }
 
 int check_factors(const char* who, int64_t N, int64_t K, int64_t up, int64_t uq) {
@@ -267,7 +270,7 @@ extern "C" int anima_lokr_kron_backward(const void* dw, int dw_is_fp32, const vo
   }
 #undef ANIMA_KRON
   ANIMA_CHECK_LAUNCH("lokr_kron_backward");
-  kron_backward_finalize_kernel<<<1, kMaxFactor * kMaxFactor, 0, s>>>(ws, blocks, alpha, (int)up, (int)uq, dw1);
+  kron_backward_finalize_kernel<<<1, kFinalizeThreads, 0, s>>>(ws, blocks, alpha, (int)up, (int)uq, dw1);
   ANIMA_CHECK_LAUNCH("lokr_kron_backward finalize");
   return ANIMA_OK;
 }

@@ -22,9 +22,12 @@ namespace {
 using namespace mxq;
 
 struct PlainLoader {
+  using Raw = uint4;
+  static constexpr bool kZeroSafe = true;
   const __nv_bfloat16* x;
   int64_t ld;
-  __device__ __forceinline__ uint4 operator()(int64_t r, int64_t c) const { return ldg_stream16(x + r * ld + c); }
+  __device__ __forceinline__ Raw fetch(int64_t r, int64_t c) const { return ldg_stream16(x + r * ld + c); }
+  __device__ __forceinline__ uint4 finish(const Raw& raw, int64_t, int64_t) const { return raw; }
 };
 
 // erf(t) for t >= 0 as 1 - erfc(t), erfc(t) = 2^(-t q(t)) with q a degree-10 least-squares fit of
@@ -68,11 +71,14 @@ __device__ __forceinline__ float gelu_grad_f(float v, float dy) {
 }
 
 struct GeluLoader {
+  using Raw = uint4;
+  static constexpr bool kZeroSafe = true;   // gelu(0) = 0
   const __nv_bfloat16* h;
   int64_t ld;
-  __device__ __forceinline__ uint4 operator()(int64_t r, int64_t c) const {
+  __device__ __forceinline__ Raw fetch(int64_t r, int64_t c) const { return ldg_stream16(h + r * ld + c); }
+  __device__ __forceinline__ uint4 finish(const Raw& raw, int64_t, int64_t) const {
     float f[8];
-    unpack8(ldg_stream16(h + r * ld + c), f);
+    unpack8(raw, f);
 #pragma unroll
     for (int k = 0; k < 8; ++k) f[k] = gelu_f(f[k]);
     return pack8(f);
@@ -81,12 +87,15 @@ struct GeluLoader {
 
 // d(pre-activation) = grad_act * gelu'(h), rounded to bf16.
 struct GeluBwdLoader {
+  using Raw = uint4;                           // the pre-activation; the incoming gradient is read in finish
+  static constexpr bool kZeroSafe = false;     // (keeping both tiles in registers up front spills)
   const __nv_bfloat16* h;
   const __nv_bfloat16* grad_act;
   int64_t ld;
-  __device__ __forceinline__ uint4 operator()(int64_t r, int64_t c) const {
+  __device__ __forceinline__ Raw fetch(int64_t r, int64_t c) const { return ldg_stream16(h + r * ld + c); }
+  __device__ __forceinline__ uint4 finish(const Raw& raw, int64_t r, int64_t c) const {
     float f[8], g[8];
-    unpack8(ldg_stream16(h + r * ld + c), f);
+    unpack8(raw, f);
     unpack8(ldg_stream16(grad_act + r * ld + c), g);
 #pragma unroll
     for (int k = 0; k < 8; ++k) f[k] = gelu_grad_f(f[k], g[k]);

@@ -47,8 +47,13 @@ __device__ __forceinline__ int tiled_offset(int r, int j) {
   return (r & 31) * 16 + (r >> 5) * 4 + j;
 }
 
-// Loader: __device__ uint4 operator()(int64_t row, int64_t col) const — the 8 bf16
-// values at (row, col .. col+7), both in range.
+// Loader interface (device side), for one chunk of 8 values at (row, col .. col+7), both in range:
+//   using Raw = ...;                                            what the chunk needs from HBM
+//   Raw   fetch(int64_t row, int64_t col) const;                issues the long-latency loads only
+//   uint4 finish(const Raw&, int64_t row, int64_t col) const;   the 8 bf16 values
+//   static constexpr bool kZeroSafe;                            finish(Raw{}) == 0 and reads no memory
+// All eight fetches of a thread are issued before the first finish, so a loader that computes
+// (merge, GELU) does not serialise its chunks on memory latency.
 template <bool ROW, bool COL, class Loader>
 __global__ void __launch_bounds__(kThreads, COL ? 3 : 4) mx_quantize_kernel(const QuantParams p, const Loader load) {
   __shared__ uint4 tile[COL ? kTile * 16 : 1];  // 128 rows x 256 B
@@ -69,22 +74,25 @@ __global__ void __launch_bounds__(kThreads, COL ? 3 : 4) mx_quantize_kernel(cons
   }
   if (COL) reinterpret_cast<uint16_t*>(sc_col)[t] = 0;
 
-  uint4 raw[8];
+  typename Loader::Raw fetched[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int64_t r = tile_r + r0 + 16 * i;
-    raw[i] = make_uint4(0u, 0u, 0u, 0u);
-    if (col_ok && r < p.rows) raw[i] = load(r, col);
+    fetched[i] = typename Loader::Raw{};
+    if (col_ok && r < p.rows) fetched[i] = load.fetch(r, col);
   }
   if (ROW || COL) __syncthreads();  // zero fill of sc_* visible before the byte stores
 
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int r_in = r0 + 16 * i;
-    if (COL) tile[r_in * 16 + c16] = raw[i];
+    // kZeroSafe loaders map an all-zero Raw to zeros without touching memory, so out-of-range chunks need no branch
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (Loader::kZeroSafe || (col_ok && tile_r + r_in < p.rows)) v = load.finish(fetched[i], tile_r + r_in, col);
+    if (COL) tile[r_in * 16 + c16] = v;
     if (ROW) {
       float f[8];
-      unpack8(raw[i], f);
+      unpack8(v, f);
       float amax = 0.f;
 #pragma unroll
       for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(f[k]));

@@ -5,20 +5,16 @@
 // _rank_mix_wgrad_kernel (:85-122). Both are HBM-bound on [batch, n, 8, rank]
 // bf16 tensors:
 //   rank_mix        reads hidden once, writes out once          (4 B/elem)
-//   rank_mix_wgrad  reads grad_mixed and hidden ONCE each       (4 B/elem pair);
-//                   the reference launches one program per (i,j) pair and so
-//                   reads both tensors 8 times.
+//   rank_mix_wgrad  reads grad_mixed and hidden ONCE each       (4 B/elem pair),
+//                   contracting on the tensor cores (mma.sync m16n8k16: the output
+//                   is 8 x 8, far below a tcgen05 tile); the reference launches one
+//                   program per (i,j) pair and so reads both tensors 8 times.
 // The wgrad reduction is two-stage (per-CTA partial 8x8 blocks in caller scratch,
 // then a fixed-order sum) and therefore bit-reproducible.
 #include "common.cuh"
 
 namespace anima {
 namespace {
-
-__device__ __forceinline__ float bf16_lane(const uint4& raw, int e) {
-  const uint32_t w = reinterpret_cast<const uint32_t*>(&raw)[e >> 1];
-  return __uint_as_float((e & 1) ? (w & 0xffff0000u) : (w << 16));
-}
 
 template <bool TRANSPOSE, bool HAS_MASK>
 __global__ void __launch_bounds__(256)
@@ -72,77 +68,85 @@ rank_mix_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16* _
   }
 }
 
-constexpr int kWgradThreads = 128;
+constexpr int kWgradThreads = 256;
+constexpr int kWgradWarps = kWgradThreads / 32;
 
+// D(16x8, fp32) += A(16x16, bf16, row-major) * B(16x8, bf16): rows 8..15 of A are zero here.
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+// dc[i][j] = sum over (b, n, r) of grad[b,n,i,r] * hidden[b,n,j,r] * mask[b,r] is an 8 x 8 output with a
+// contraction of millions: one m16n8k16 tensor-core instruction per 16 contraction elements replaces 1024
+// scalar FMAs, which leaves the kernel bound by its two streaming reads. A warp owns one (b, n) item at a
+// time; lane (g, t) = (lane / 4, lane % 4) loads 8 consecutive r of row g of both tensors. The contraction
+// index may be permuted freely as long as A and B agree, so the lane's four 32-bit words feed the k-slots
+// (2t, 2t+1) and (2t+8, 2t+9) of two instructions directly: no shuffles, 16-byte loads only.
+// The mask multiplies hidden as bf16 pairs: exact for the 0 / 1 masks of the rank schedule.
 template <bool HAS_MASK>
 __global__ void __launch_bounds__(kWgradThreads)
 rank_mix_wgrad_kernel(const __nv_bfloat16* __restrict__ grad, const __nv_bfloat16* __restrict__ hidden,
-                      const __nv_bfloat16* __restrict__ mask, int64_t total, int64_t n_per_batch,
-                      int r8, float* __restrict__ partial) {
-  __shared__ float red[kWgradThreads / 32][64];
-  const int64_t rank = static_cast<int64_t>(r8) * 8;
-  float acc[8][8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
-
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * kWgradThreads;
-  for (int64_t idx = blockIdx.x * static_cast<int64_t>(kWgradThreads) + threadIdx.x; idx < total;
-       idx += stride) {
-    const int64_t row = idx / r8;
-    const int rc = static_cast<int>(idx - row * r8);
-    const int64_t off = row * 8 * rank + rc * 8;
-    uint4 g[8], h[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      g[i] = ldg_stream16(grad + off + i * rank);
-      h[i] = ldg_stream16(hidden + off + i * rank);
-    }
-    uint4 mraw = make_uint4(0u, 0u, 0u, 0u);
-    if (HAS_MASK) mraw = *reinterpret_cast<const uint4*>(mask + (row / n_per_batch) * rank + rc * 8);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      float gv[8], hv[8];
-      const float mv = HAS_MASK ? bf16_lane(mraw, e) : 1.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        gv[i] = bf16_lane(g[i], e);
-        hv[i] = bf16_lane(h[i], e) * mv;
+                      const __nv_bfloat16* __restrict__ mask, int64_t items, int64_t n_per_batch, int rank,
+                      float* __restrict__ partial) {
+  __shared__ float red[kWgradWarps][64];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const int steps = (rank + 31) / 32;
+  const int64_t warps_total = static_cast<int64_t>(gridDim.x) * kWgradWarps;
+  for (int64_t item = static_cast<int64_t>(blockIdx.x) * kWgradWarps + warp; item < items; item += warps_total) {
+    const int64_t off = item * 8 * rank + static_cast<int64_t>(g) * rank + t * 8;
+    const __nv_bfloat16* mp = HAS_MASK ? mask + (item / n_per_batch) * rank + t * 8 : nullptr;
+#pragma unroll 4
+    for (int s = 0; s < steps; ++s) {
+      // rank % 8 == 0: a lane's chunk is all in or all out. Lanes past the tail feed zeros: the two
+      // warp-wide instructions below are reached by all 32 lanes together, never from a divergent branch.
+      uint4 a = make_uint4(0u, 0u, 0u, 0u), b = make_uint4(0u, 0u, 0u, 0u);
+      if (s * 32 + t * 8 < rank) {
+        a = ldg_stream16(grad + off + s * 32);
+        b = ldg_stream16(hidden + off + s * 32);
+        if (HAS_MASK) {
+          const uint4 m = *reinterpret_cast<const uint4*>(mp + s * 32);
+          b.x = bf16x2_mul(b.x, m.x);
+          b.y = bf16x2_mul(b.y, m.y);
+          b.z = bf16x2_mul(b.z, m.z);
+          b.w = bf16x2_mul(b.w, m.w);
+        }
       }
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(gv[i], hv[j], acc[i][j]);
+      __syncwarp();
+      mma_bf16_16816(acc, a.x, a.y, b.x, b.y);
+      mma_bf16_16816(acc, a.z, a.w, b.z, b.w);
     }
   }
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-  for (int i = 0; i < 8; ++i)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float s = warp_sum(acc[i][j]);
-      if (lane == 0) red[warp][i * 8 + j] = s;
-    }
+  // acc[0], acc[1] = dc[g][2t], dc[g][2t+1] of this warp; rows 8..15 (acc[2], acc[3]) are padding
+  red[warp][g * 8 + 2 * t] = acc[0];
+  red[warp][g * 8 + 2 * t + 1] = acc[1];
   __syncthreads();
   if (threadIdx.x < 64) {
     float s = 0.f;
 #pragma unroll
-    for (int w = 0; w < kWgradThreads / 32; ++w) s += red[w][threadIdx.x];
+    for (int w = 0; w < kWgradWarps; ++w) s += red[w][threadIdx.x];
     partial[blockIdx.x * 64 + threadIdx.x] = s;
   }
 }
 
-__global__ void rank_mix_wgrad_finalize_kernel(const float* __restrict__ partial, int blocks,
-                                               float* __restrict__ dc) {
-  float s = 0.f;
-  for (int b = 0; b < blocks; ++b) s += partial[b * 64 + threadIdx.x];
-  dc[threadIdx.x] = s;
+__global__ void __launch_bounds__(kFinalizeThreads)
+rank_mix_wgrad_finalize_kernel(const float* __restrict__ partial, int blocks, float* __restrict__ dc) {
+  const float s = sum_partials_64(partial, blocks);
+  if (threadIdx.x < 64) dc[threadIdx.x] = s;
 }
 
-int wgrad_blocks(int64_t total) {
-  return static_cast<int>(std::max<int64_t>(
-      1, std::min<int64_t>(ceil_div(total, kWgradThreads), 4LL * sm_count())));
+// items = batch * n_per_batch; one warp per item at a time
+int wgrad_blocks(int64_t items) {
+  return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(ceil_div(items, kWgradWarps), 4LL * sm_count())));
 }
 
 }  // namespace
@@ -182,7 +186,7 @@ extern "C" int anima_tlokr_rank_mix(const void* hidden, const void* c, const voi
 extern "C" int64_t anima_tlokr_rank_mix_wgrad_workspace_bytes(int64_t batch, int64_t n_per_batch,
                                                               int64_t rank) {
   if (batch < 0 || n_per_batch < 0 || rank <= 0 || rank % 8) return ANIMA_E_SHAPE;
-  return static_cast<int64_t>(wgrad_blocks(batch * n_per_batch * (rank / 8))) * 64 * sizeof(float);
+  return static_cast<int64_t>(wgrad_blocks(batch * n_per_batch)) * 64 * sizeof(float);
 }
 
 extern "C" int anima_tlokr_rank_mix_wgrad(const void* grad_mixed, const void* hidden, const void* mask,
@@ -195,24 +199,25 @@ extern "C" int anima_tlokr_rank_mix_wgrad(const void* grad_mixed, const void* hi
                 (long long)rank);
   ANIMA_REQUIRE(aligned16(grad_mixed) && aligned16(hidden) && (!mask || aligned16(mask)), ANIMA_E_ALIGN,
                 "tlokr_rank_mix_wgrad: tensors must be 16-byte aligned");
-  const int64_t total = batch * n_per_batch * (rank / 8);
+  ANIMA_REQUIRE(rank < (1 << 30), ANIMA_E_TOO_LARGE, "tlokr_rank_mix_wgrad: rank too large");
+  const int64_t items = batch * n_per_batch;
   const int64_t need = anima_tlokr_rank_mix_wgrad_workspace_bytes(batch, n_per_batch, rank);
   ANIMA_REQUIRE(workspace && workspace_bytes >= need, ANIMA_E_WORKSPACE,
                 "tlokr_rank_mix_wgrad: workspace of %lld bytes required, got %lld", (long long)need,
                 (long long)workspace_bytes);
-  const int blocks = wgrad_blocks(total);
+  const int blocks = wgrad_blocks(items);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* ws = static_cast<float*>(workspace);
   const auto* gp = static_cast<const __nv_bfloat16*>(grad_mixed);
   const auto* hp = static_cast<const __nv_bfloat16*>(hidden);
   const auto* mp = static_cast<const __nv_bfloat16*>(mask);
-  const int r8 = static_cast<int>(rank / 8);
+  const int r = static_cast<int>(rank);
   if (mask)
-    rank_mix_wgrad_kernel<true><<<blocks, kWgradThreads, 0, s>>>(gp, hp, mp, total, n_per_batch, r8, ws);
+    rank_mix_wgrad_kernel<true><<<blocks, kWgradThreads, 0, s>>>(gp, hp, mp, items, n_per_batch, r, ws);
   else
-    rank_mix_wgrad_kernel<false><<<blocks, kWgradThreads, 0, s>>>(gp, hp, mp, total, n_per_batch, r8, ws);
+    rank_mix_wgrad_kernel<false><<<blocks, kWgradThreads, 0, s>>>(gp, hp, mp, items, n_per_batch, r, ws);
   ANIMA_CHECK_LAUNCH("tlokr_rank_mix_wgrad");
-  rank_mix_wgrad_finalize_kernel<<<1, 64, 0, s>>>(ws, blocks, dc);
+  rank_mix_wgrad_finalize_kernel<<<1, kFinalizeThreads, 0, s>>>(ws, blocks, dc);
   ANIMA_CHECK_LAUNCH("tlokr_rank_mix_wgrad finalize");
   return ANIMA_OK;
 }
