@@ -29,6 +29,8 @@ def main() -> None:
     ap.add_argument("--text", type=int, default=512)
     ap.add_argument("--top", type=int, default=30)
     ap.add_argument("--no-checkpoint", action="store_true")
+    ap.add_argument("--gaps", type=int, default=0,
+                    help="also list the N largest idle gaps between consecutive kernels (where the host fell behind)")
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
     tr = Trainer(AnimaConfig(depth=a.depth), StepConfig(precision=a.arm, variant=a.variant,
@@ -49,6 +51,24 @@ def main() -> None:
           f"{total / 1e3:.1f} ms of device time in {sum(v[0] for v in agg.values())} launches")
     for name, (n, us) in sorted(agg.items(), key=lambda kv: -kv[1][1])[:a.top]:
         print(f"{n:6d} {us / 1e3:9.2f} ms {100 * us / total:5.1f}%  {name}")
+    if a.gaps:
+        ev = sorted(((e.time_range.start, e.time_range.end, e.name) for e in prof.events()
+                     if e.device_type == torch.autograd.DeviceType.CUDA), key=lambda t: t[0])
+        span = ev[-1][1] - ev[0][0]
+        gaps, busy_end = [], ev[0][1]
+        for (st, en, name), (_, _, prev) in zip(ev[1:], ev[:-1]):
+            if st > busy_end:
+                gaps.append((st - busy_end, prev[:50], name[:50]))
+            busy_end = max(busy_end, en)
+        idle = sum(g[0] for g in gaps)
+        print(f"span {span / 1e3:.1f} ms, idle {idle / 1e3:.1f} ms in {len(gaps)} gaps "
+              f"({sum(1 for g in gaps if g[0] > 20)} longer than 20 us)")
+        by_pair: dict[tuple, list] = collections.defaultdict(lambda: [0, 0.0])
+        for us, prev, nxt in gaps:
+            by_pair[(prev, nxt)][0] += 1
+            by_pair[(prev, nxt)][1] += us
+        for (prev, nxt), (n, us) in sorted(by_pair.items(), key=lambda kv: -kv[1][1])[:a.gaps]:
+            print(f"{n:6d} {us / 1e3:8.2f} ms  after {prev}  before {nxt}")
 
 
 if __name__ == "__main__":
