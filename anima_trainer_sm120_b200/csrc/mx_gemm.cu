@@ -1,4 +1,4 @@
-// MXFP8 block-scaled GEMM for sm_100a: C[M,N] = A[M,K] . B[N,K]^T (+ bias).
+// MXFP8 block-scaled GEMM for sm_100a: C[M,N] = alpha * A[M,K] . B[N,K]^T (+ bias) (+ residual).
 //
 // Replaces anima-trainer's Triton tl.dot_scaled kernel (mxfp8_gemm.py:254-336) and
 // the Transformer-Engine general_gemm calls of fp8_quant.py (:150, :236 forward;
@@ -24,6 +24,8 @@
 //    BN = 256 the 512 tensor-memory columns cannot hold two full buffers plus the scale columns, so
 //    buffer 1 starts 32 columns before the end of buffer 0 and the epilogue drains those shared
 //    columns first, then releases the MMA warp.
+//    With caller scratch it also splits the contraction of small outputs (work item = tile x K-range,
+//    fp32 partial tiles, fixed-order finalize kernel).
 // Every wait is bounded; on a timeout a kernel raises *status, lets copies in flight land, frees its
 // tensor memory and returns. Tensor-pipe bound: 2*M*N*K flop. No TMA multicast is used anywhere.
 #include <cuda.h>
@@ -449,7 +451,7 @@ __global__ void __launch_bounds__(256) splitk_finalize_kernel(const GemmParams p
 // A cluster of two CTAs (two SMs) owns one 256 x 192 output tile. CTA r stages rows
 // [128 r, 128 r + 128) of the A tile and rows [96 r, 96 r + 96) of the B tile, so every
 // tcgen05.mma (cta_group::2, M256 x N192 x K32) is fed by 7 KB of shared-memory fill per
-// SM (the one-CTA kernel needs 12 KB per M128 x N256 x K32), and 7 stages are in flight.
+// SM (the one-CTA kernel needs 12 KB per M128 x N256 x K32), and 6 stages are in flight.
 // N = 192 leaves room in tensor memory for two DISJOINT accumulator buffers (2 x 192
 // columns) next to the 12 scale columns, so the next tile's MMAs start the moment the
 // previous tile's are issued; with N = 256 the buffers must share columns and the tensor

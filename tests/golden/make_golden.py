@@ -21,7 +21,9 @@ import sys
 from pathlib import Path
 
 os.environ.setdefault("TRITON_INTERPRET", "1")
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py /path/to/anima-trainer")
+REF = Path(sys.argv[1])
 sys.path.insert(0, str(REF / "src"))
 
 import numpy as np  # noqa: E402
