@@ -80,7 +80,17 @@ def _acts(rows, cols, std=1.0):
     return (torch.randn(rows, cols, device="cuda") * std).to(BF16)
 
 
-def run(iters: int, only: str | None, small: bool, pick: str | None = None, direct: bool = False) -> list[dict]:
+def cublaslt_mxfp8(a, b):
+    """A callable running ``torch._scaled_mm`` (cuBLASLt block-scaled MXFP8) on two TILED MXFP8 operands."""
+    a8 = a.codes.view(torch.float8_e4m3fn)
+    b8 = b.codes.view(torch.float8_e4m3fn).t()
+    sa = a.scales.view(torch.float8_e8m0fnu)
+    sb = b.scales.view(torch.float8_e8m0fnu)
+    return lambda: torch._scaled_mm(a8, b8, scale_a=sa, scale_b=sb, out_dtype=BF16)
+
+
+def run(iters: int, only: str | None, small: bool, pick: str | None = None, direct: bool = False,
+        yardstick: bool = False) -> list[dict]:
     _lib.load()
     torch.manual_seed(0)
     peaks = _peaks()
@@ -174,6 +184,15 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
             tensor("mx_gemm fwd", [M, N, K], fl, lambda: ops.mx_gemm(xr, wr, out=y))
             tensor("mx_gemm dgrad", [M, K, N], fl, lambda: ops.mx_gemm(gr, wc, out=dx))
             tensor("mx_gemm wgrad (fp32 out)", [N, K, M], fl, lambda: ops.mx_gemm(gc, xc, out_dtype=torch.float32, out=dw))
+            if yardstick:
+                # the vendor library's MXFP8 GEMM on the SAME operands (its swizzled scale layout is the
+                # 128 x 4 tiled layout): a measured ceiling to read the kernel against, not a code path
+                try:
+                    fn = cublaslt_mxfp8(xr, wr)
+                    fn()
+                    tensor("yardstick: cuBLASLt MXFP8 via torch._scaled_mm, fwd", [M, N, K], fl, fn)
+                except Exception as e:  # noqa: BLE001 - the yardstick is optional
+                    print(json.dumps({"kernel": "yardstick: cuBLASLt MXFP8", "unavailable": str(e)[:200]}), flush=True)
             del x, w, gy, xr, xc, wr, wc, gr, gc, y, dx, dw
         _lib.check_status_word(torch.device("cuda", torch.cuda.current_device()))
     return out
@@ -186,5 +205,7 @@ if __name__ == "__main__":
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--pick", default=None, help="run only entries whose 'name [shape]' contains this text")
     ap.add_argument("--direct", action="store_true", help="plain launches instead of CUDA-graph replays")
+    ap.add_argument("--yardstick", action="store_true",
+                    help="also time the vendor library's MXFP8 GEMM (torch._scaled_mm) on the same operands")
     a = ap.parse_args()
-    run(a.iters, a.only, a.small, a.pick, a.direct)
+    run(a.iters, a.only, a.small, a.pick, a.direct, a.yardstick)

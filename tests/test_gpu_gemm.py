@@ -286,3 +286,25 @@ def test_full_size_config2_properties():
     lib.check_status_word(c.device)
     torch.testing.assert_close(dw, dw_t.t(), rtol=1e-5, atol=1e-4)
     assert _rel_max(gy.float().t() @ x.float(), dw) < 0.10
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 768, 1024), (4096, 2048, 2048)])
+def test_agrees_with_the_vendor_library_mxfp8_gemm(M, N, K):
+    """Independent check on the GPU: cuBLASLt's block-scaled MXFP8 GEMM (torch._scaled_mm) consumes the very
+    same code and TILED scale buffers (its swizzled layout is the 128 x 4 tiled layout) and must give the same
+    product up to fp32 accumulation order. Skipped where the installed torch / cuBLASLt rejects the call."""
+    ops, lib = _ops()
+    from anima_trainer_sm120_b200.kernel_bench import cublaslt_mxfp8
+    x = _acts(M, K, 21).cuda()
+    w = _acts(N, K, 22, std=0.02, outliers=False).cuda()
+    a, _ = ops.mx_quantize(x, rowwise=True)
+    b, _ = ops.mx_quantize(w, rowwise=True)
+    try:
+        want = cublaslt_mxfp8(a, b)()
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"torch._scaled_mm MXFP8 unavailable: {str(e)[:120]}")
+    got = ops.mx_gemm(a, b)
+    torch.cuda.synchronize()
+    lib.check_status_word(got.device)
+    torch.testing.assert_close(got.float(), want.float(), rtol=RTOL, atol=ATOL)
+    assert float((got.float() - want.float()).abs().max()) <= 0.0625 * float(want.float().abs().max()) / 8
