@@ -41,6 +41,7 @@ PROTOTYPES: dict[str, tuple[object, list[object]]] = {
     "anima_mx_scales_bytes": (I64, [I64, I64, c_int]),
     "anima_mx_dequantize": (c_int, [P, P, I64, I64, c_int, P, P]),
     "anima_mx_scales_retile": (c_int, [P, I64, I64, P, P]),
+    "anima_mx_scales_regroup": (c_int, [P, I64, I64, P, I64, I64, P]),
     "anima_mx_gemm": (c_int, [P, P, P, P, P, I64, I64, I64, I64, P, c_int, P, P]),
     "anima_mx_gemm_workspace_bytes": (I64, [I64, I64, I64]),
     "anima_mx_gemm_ex": (c_int, [P, P, P, P, P, I64, I64, I64, I64, P, P, I64, c_float, c_int, P, I64, P, P]),

@@ -148,6 +148,29 @@ __global__ void mx_scales_retile_kernel(const uint8_t* __restrict__ plain, int64
   }
 }
 
+// TILED scales of a code matrix [rows_in, k_in] -> TILED scales of the SAME codes viewed as
+// [rows_out, k_out] (rows_in * k_in == rows_out * k_out): the 32-element blocks keep their row-major
+// order, only their (row, block) coordinates and therefore their place in the 128 x 4 tiling change.
+__global__ void mx_scales_regroup_kernel(const uint8_t* __restrict__ in, int64_t kb_in, int64_t rows_out,
+                                         int64_t kb_out, uint8_t* __restrict__ out) {
+  const int64_t kb4_out = ceil_div(kb_out, 4), kb4_in = ceil_div(kb_in, 4);
+  const int64_t total = ceil_div(rows_out, 128) * kb4_out * 512;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t chunk = i / 512;
+    const int off = static_cast<int>(i % 512);
+    const int j = off & 3, r_in = ((off >> 2) & 3) * 32 + (off >> 4);
+    const int64_t r = (chunk / kb4_out) * 128 + r_in, b = (chunk % kb4_out) * 4 + j;
+    uint8_t v = 0;
+    if (r < rows_out && b < kb_out) {
+      const int64_t flat = r * kb_out + b;
+      const int64_t ri = flat / kb_in, bi = flat - ri * kb_in;
+      v = in[((ri / 128) * kb4_in + bi / 4) * 512 + tiled_offset(static_cast<int>(ri % 128), static_cast<int>(bi % 4))];
+    }
+    out[i] = v;
+  }
+}
+
 }  // namespace
 }  // namespace anima
 
@@ -265,5 +288,22 @@ extern "C" int anima_mx_scales_retile(const uint8_t* plain, int64_t rows, int64_
   mx_scales_retile_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(plain, rows, k / 32,
                                                                                  tiled);
   ANIMA_CHECK_LAUNCH("mx_scales_retile");
+  return ANIMA_OK;
+}
+
+extern "C" int anima_mx_scales_regroup(const uint8_t* tiled_in, int64_t rows_in, int64_t k_in, uint8_t* tiled_out,
+                                       int64_t rows_out, int64_t k_out, void* stream) {
+  ANIMA_REQUIRE(tiled_in && tiled_out, ANIMA_E_ARG, "mx_scales_regroup: null pointer");
+  ANIMA_REQUIRE(rows_in >= 0 && rows_out >= 0 && k_in > 0 && k_out > 0 && k_in % 32 == 0 && k_out % 32 == 0,
+                ANIMA_E_SHAPE, "mx_scales_regroup: k must be a positive multiple of 32");
+  ANIMA_REQUIRE(rows_in * k_in == rows_out * k_out, ANIMA_E_SHAPE,
+                "mx_scales_regroup: [%lld, %lld] and [%lld, %lld] hold different numbers of elements",
+                (long long)rows_in, (long long)k_in, (long long)rows_out, (long long)k_out);
+  if (rows_out == 0) return ANIMA_OK;
+  const int64_t total = anima_mx_scales_bytes(rows_out, k_out, ANIMA_SCALES_TILED);
+  const int blocks = static_cast<int>(std::min<int64_t>(ceil_div(total, 256), sm_count() * 16));
+  mx_scales_regroup_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(tiled_in, k_in / 32, rows_out,
+                                                                                  k_out / 32, tiled_out);
+  ANIMA_CHECK_LAUNCH("mx_scales_regroup");
   return ANIMA_OK;
 }

@@ -129,6 +129,22 @@ def mx_retile(op: MXOperand) -> MXOperand:
     return MXOperand(op.codes, tiled, SCALES_TILED)
 
 
+def mx_regroup(op: MXOperand, rows: int, k: int) -> MXOperand:
+    """The same row-wise codes viewed as ``[rows, k]`` (``rows * k`` unchanged, ``k % 32 == 0``), with TILED scales
+    re-tiled for that shape. The code buffer is shared, not copied."""
+    if op.layout != SCALES_TILED:
+        raise ValueError("mx_regroup needs TILED scales")
+    if rows * k != op.rows * op.k or k % 32:
+        raise ValueError(f"cannot view [{op.rows}, {op.k}] as [{rows}, {k}]")
+    dev = _lib.require_cuda(op.codes, op.scales)
+    scales = _alloc_scales(rows, k, SCALES_TILED, dev)
+    if rows:
+        with torch.cuda.device(dev):
+            check(_lib.load().anima_mx_scales_regroup(ptr(op.scales), op.rows, op.k, ptr(scales), rows, k,
+                                                      _lib.stream_ptr(dev)))
+    return MXOperand(op.codes.view(rows, k), scales, SCALES_TILED)
+
+
 def mx_gemm(a: MXOperand, b: MXOperand, *, bias: torch.Tensor | None = None,
             out_dtype: torch.dtype = BF16, out: torch.Tensor | None = None, split_k: bool = True,
             residual: torch.Tensor | None = None, alpha: float = 1.0) -> torch.Tensor:

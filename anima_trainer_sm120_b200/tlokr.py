@@ -287,17 +287,9 @@ class _MXStructuredLoKr(torch.autograd.Function):
 _FP8StructuredLoKr = _MXStructuredLoKr  # name used by anima-trainer
 
 
-def _structured_delta(module, x: torch.Tensor, *, fp8: bool, base: torch.Tensor | None = None,
-                      alpha: float = 1.0) -> torch.Tensor:
-    """``x @ kron(W1, A @ B).T`` for the current timestep context (reference :679-735); with ``base`` given,
-    ``base + alpha * delta`` (fused into the last GEMM on the quantised path)."""
-    def run(fn, *args):
-        if base is None:
-            return fn.apply(*args)
-        if fn is _MXStructuredLoKr and base.dtype == BF16 and base.is_contiguous() and base.requires_grad:
-            return fn.apply(*args, base, alpha)
-        return torch.add(base, fn.apply(*args), alpha=alpha)
-
+def _delta_plan(module, x: torch.Tensor, *, fp8: bool):
+    """(autograd function, A, B, mask) of the structured delta for the current timestep context
+    (the dispatch of reference :679-735)."""
     state = _current_state()
     rank, min_rank = module._tlokr_rank, module._tlokr_min_rank
     w1 = module.lokr_w1
@@ -311,18 +303,104 @@ def _structured_delta(module, x: torch.Tensor, *, fp8: bool, base: torch.Tensor 
         active = active_rank_for_timestep(state.uniform_timestep, max_rank=rank, min_rank=min_rank)
         if active % 8 == 0:
             fn = _MXStructuredLoKr if fp8 and active % 32 == 0 else _StructuredLoKr
-            return run(fn, x, w1, module.lokr_w2_a[:, :active], module.lokr_w2_b[:active], None)
+            return fn, module.lokr_w2_a[:, :active], module.lokr_w2_b[:active], None
         key = ("uniform", rank, active, x.dtype, x.device, x.shape[0])
         mask = state.masks.get(key)
         if mask is None:
             mask = (torch.arange(rank, device=x.device) < active).to(x.dtype).expand(x.shape[0], rank).contiguous()
             state.masks[key] = mask
-        return run(_MXStructuredLoKr if fp8 else _StructuredLoKr, x, w1, module.lokr_w2_a, module.lokr_w2_b, mask)
+        return (_MXStructuredLoKr if fp8 else _StructuredLoKr), module.lokr_w2_a, module.lokr_w2_b, mask
     mask = state.mask(max_rank=rank, min_rank=min_rank, dtype=x.dtype, device=x.device)
     if x.shape[0] != mask.shape[0]:
         raise RuntimeError(f"{module.lora_name}: activation batch {x.shape[0]} does not match timestep "
                            f"batch {mask.shape[0]}")
-    return run(_MXStructuredLoKr if fp8 else _StructuredLoKr, x, w1, module.lokr_w2_a, module.lokr_w2_b, mask)
+    return (_MXStructuredLoKr if fp8 else _StructuredLoKr), module.lokr_w2_a, module.lokr_w2_b, mask
+
+
+def _structured_delta(module, x: torch.Tensor, *, fp8: bool, base: torch.Tensor | None = None,
+                      alpha: float = 1.0) -> torch.Tensor:
+    """``x @ kron(W1, A @ B).T`` for the current timestep context; with ``base`` given,
+    ``base + alpha * delta`` (fused into the last GEMM on the quantised path)."""
+    fn, w2_a, w2_b, mask = _delta_plan(module, x, fp8=fp8)
+    args = (x, module.lokr_w1, w2_a, w2_b, mask)
+    if base is None:
+        return fn.apply(*args)
+    if fn is _MXStructuredLoKr and base.dtype == BF16 and base.is_contiguous() and base.requires_grad:
+        return fn.apply(*args, base, alpha)
+    return torch.add(base, fn.apply(*args), alpha=alpha)
+
+
+class _MXTLoKrLinear(torch.autograd.Function):
+    """The whole quantised T-LoKr linear, ``x W^T + bias + alpha * delta(x)``, as ONE autograd node.
+
+    The reference runs a frozen FP8 base projection (``fp8_frozen_linear``, ``tlokr.py:743``), the
+    structured delta (``_FP8StructuredLoKr``, :543-676) and ``torch.add(base, delta, alpha=)`` (:757-759) as
+    three nodes, each quantising its own inputs. As one node:
+
+    * x is quantised row-wise ONCE: the base GEMM contracts it as [rows, K], the delta as the grouped view
+      [rows * uq, K / uq]; the code bytes are the same, only the scales are re-tiled (``ops.mx_regroup``);
+      likewise the incoming gradient serves the base dgrad and the delta chain from one quantisation;
+    * ``+ alpha * delta`` and, in backward, ``+ grad_x(delta)`` are added by the stores of the last GEMM of
+      each chain into the buffer the base GEMM wrote: no separate add kernels, no autograd sum.
+
+    Only x and the small factors are saved; the rank-space intermediates are recomputed in backward, as in
+    the reference."""
+
+    @staticmethod
+    def forward(ctx, x, W_mx, bias, w1, w2_a, w2_b, mask, alpha: float):
+        from .fp8_quant import _bias_bf16, quantize_activation
+        c = w1.to(BF16)
+        uq = c.shape[1]
+        vp, rank = w2_a.shape
+        K = x.shape[-1]
+        rows = x.numel() // K
+        n_out = W_mx.row.rows
+        aq, aq_col = _q(w2_a.detach(), col=True)      # A [vp, r]: row form for out, column form for dgrad
+        bq, bq_col = _q(w2_b.detach(), col=True)      # B [r, vq]
+        x_row, _ = quantize_activation(x, colwise=False)
+        gq = ops.mx_regroup(x_row, rows * uq, K // uq)
+        y = torch.empty(*x.shape[:-1], n_out, dtype=BF16, device=x.device)
+        ops.mx_gemm(x_row, W_mx.row, bias=_bias_bf16(bias), out=y.view(-1, n_out))
+        hidden = ops.mx_gemm(gq, bq).view(x.shape[0], -1, uq, rank)
+        mixed = rank_mix(hidden, c, mask)
+        mq, _ = _q(mixed.reshape(-1, rank))
+        res = y.view(-1, vp)
+        ops.mx_gemm(mq, aq, residual=res, alpha=float(alpha), out=res)       # y += alpha * delta
+        ctx.save_for_backward(x, w1, w2_a, w2_b, *(() if mask is None else (mask,)))
+        ctx.has_mask, ctx.ops, ctx.W_mx = mask is not None, (aq_col, bq, bq_col), W_mx
+        ctx.alpha, ctx.bias_grad = float(alpha), bias is not None and bias.requires_grad
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        saved = ctx.saved_tensors        # read once: activation checkpointing unpacks on access
+        x, w1, w2_a, w2_b = saved[:4]
+        mask = saved[4] if ctx.has_mask else None
+        aq_col, bq, bq_col = ctx.ops
+        c = w1.to(BF16)
+        up, uq = c.shape
+        vp, rank = w2_a.shape
+        K = x.shape[-1]
+        rows = x.numel() // K
+        gy = grad_output.contiguous() if grad_output.dtype == BF16 else grad_output.to(BF16).contiguous()
+        gbq, gbq_col = _q(gy.view(-1, vp), col=True)                                   # grad as [rows * up, vp]
+        g_x = torch.empty_like(x)
+        ops.mx_gemm(ops.mx_regroup(gbq, rows, up * vp), ctx.W_mx.col, out=g_x.view(rows, K))   # base dgrad
+        grouped = _grouped(x, uq)
+        gq, gq_col = _q(grouped.reshape(-1, grouped.shape[-1]), col=True)
+        hidden = ops.mx_gemm(gq, bq).view(*grouped.shape[:-1], rank)
+        mixed = rank_mix(hidden, c, mask)
+        _, mq_col = ops.mx_quantize(mixed.reshape(-1, rank), rowwise=False, colwise=True)
+        g_a = ops.mx_gemm(gbq_col, mq_col, out_dtype=torch.float32, alpha=ctx.alpha)   # alpha * grad^T @ mixed  [vp, r]
+        g_mixed = ops.mx_gemm(gbq, aq_col, alpha=ctx.alpha).view(*mixed.shape)         # alpha * grad @ A        [.., r]
+        g_c = rank_mix_wgrad(g_mixed, hidden, mask)
+        g_hidden = rank_mix(g_mixed, c, mask, transpose=True)
+        ghq, ghq_col = _q(g_hidden.reshape(-1, rank), col=True)
+        g_b = ops.mx_gemm(ghq_col, gq_col, out_dtype=torch.float32)                    # grad_hidden^T @ grouped [r, vq]
+        res = g_x.view(-1, grouped.shape[-1])
+        ops.mx_gemm(ghq, bq_col, residual=res, out=res)                                # g_x += grad_hidden @ B
+        g_bias = gy.view(rows, -1).sum(dim=0) if ctx.bias_grad else None
+        return g_x, None, g_bias, g_c.to(w1.dtype), g_a.to(w2_a.dtype), g_b.to(w2_b.dtype), None, None
 
 
 def forward(module, x: torch.Tensor) -> torch.Tensor:
@@ -331,6 +409,11 @@ def forward(module, x: torch.Tensor) -> torch.Tensor:
     org = module.org_module[0]
     base_q = getattr(module, "_tlokr_fp8_base_weight", None)
     quantised = base_q is not None and x.is_cuda and (x.numel() // x.shape[-1]) % 32 == 0
+    if quantised and x.dtype == BF16 and base_q.col is not None and tuple(module.lokr_w1.shape) == (8, 8):
+        fn, w2_a, w2_b, mask = _delta_plan(module, x, fp8=True)
+        if fn is _MXStructuredLoKr:
+            return _MXTLoKrLinear.apply(x.contiguous(), base_q, org.bias, module.lokr_w1, w2_a, w2_b, mask,
+                                        module._tlokr_alpha)
     if quantised:
         from .fp8_quant import fp8_frozen_linear
         base = fp8_frozen_linear(x, base_q, org.weight, org.bias)

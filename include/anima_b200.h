@@ -94,6 +94,14 @@ int anima_mx_dequantize(const uint8_t* codes, const uint8_t* scales, int64_t row
 int anima_mx_scales_retile(const uint8_t* plain, int64_t rows, int64_t k, uint8_t* tiled,
                            void* stream);
 
+/* TILED scales of a code matrix [rows_in, k_in] -> TILED scales of the same code buffer viewed as
+ * [rows_out, k_out] (equal element counts, both k multiples of 32). T-LoKr contracts the grouped
+ * view x.reshape(rows * uq, K / uq) of the tensor its base projection contracts as [rows, K]
+ * (ref: tlokr.py:472-476, :743): the row-wise codes are the same bytes, so one quantisation serves
+ * both GEMMs once its scales are re-tiled for the second shape. */
+int anima_mx_scales_regroup(const uint8_t* tiled_in, int64_t rows_in, int64_t k_in,
+                            uint8_t* tiled_out, int64_t rows_out, int64_t k_out, void* stream);
+
 /* ---------------------------------------------------------------- MXFP8 GEMM
  * ref: mxfp8_gemm.py:254-336 (_mxfp8_gemm_kernel, mxfp8_matmul);
  *      fp8_quant.py:146-150 (general_gemm 'TN'), :503-507 ('NN' dgrad, 'NT' wgrad).

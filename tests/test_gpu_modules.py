@@ -198,3 +198,53 @@ def test_training_arms_track_each_other(variant):
         assert any(not torch.equal(a, b) for a, b in zip(before, tr.params))
     for a, b in zip(curves["bf16"], curves["mxfp8"]):
         assert abs(a - b) / a < 0.02, curves
+
+
+def test_scale_regroup_equals_quantising_the_reshaped_tensor():
+    from anima_trainer_sm120_b200 import ops
+    torch.manual_seed(4)
+    for rows, K, u in ((96, 512, 8), (1024, 2048, 8), (33, 256, 4)):
+        x = (torch.randn(rows, K, device=DEV) * 3).to(BF16)
+        row, _ = ops.mx_quantize(x, rowwise=True)
+        want, _ = ops.mx_quantize(x.view(rows * u, K // u), rowwise=True)
+        got = ops.mx_regroup(row, rows * u, K // u)
+        assert torch.equal(got.codes, want.codes) and torch.equal(got.scales, want.scales)
+        back = ops.mx_regroup(got, rows, K)
+        assert torch.equal(back.scales, row.scales)
+    with pytest.raises(ValueError):
+        ops.mx_regroup(row, 7, 11)
+
+
+def test_tlokr_single_node_linear_matches_three_node_composition():
+    """``_MXTLoKrLinear`` (one quantisation of x and of the gradient, adds done by GEMM stores) against the
+    base projection + ``_MXStructuredLoKr`` + ``torch.add`` composition it replaces."""
+    from anima_trainer_sm120_b200 import fp8_quant, tlokr
+    _, mod, lin = _tlokr_module(in_f=1024, out_f=2048, rank=64)
+    with torch.no_grad():
+        mod.lokr_w2_b.normal_(std=0.05)
+        lin.weight.normal_(std=0.03)
+    Wq = fp8_quant.quantize_weight(lin.weight)
+    t = torch.rand(4, device=DEV)
+    mask = tlokr._TimestepState(timesteps=t).mask(max_rank=64, min_rank=32, dtype=BF16, device=torch.device(DEV))
+    x = torch.randn(4, 128, 1024, device=DEV, dtype=BF16)
+    probe = torch.randn(4, 128, 2048, device=DEV, dtype=BF16)
+    alpha = 0.6
+    res = []
+    for single in (False, True):
+        xi = x.clone().requires_grad_(True)
+        for p in (mod.lokr_w1, mod.lokr_w2_a, mod.lokr_w2_b):
+            p.grad = None
+        if single:
+            y = tlokr._MXTLoKrLinear.apply(xi, Wq, lin.bias, mod.lokr_w1, mod.lokr_w2_a, mod.lokr_w2_b, mask, alpha)
+        else:
+            base = fp8_quant.fp8_frozen_linear(xi, Wq, lin.weight, lin.bias)
+            y = torch.add(base, tlokr._MXStructuredLoKr.apply(xi, mod.lokr_w1, mod.lokr_w2_a, mod.lokr_w2_b, mask),
+                          alpha=alpha)
+        y.backward(probe)
+        res.append([y.detach(), xi.grad, mod.lokr_w1.grad.clone(), mod.lokr_w2_a.grad.clone(), mod.lokr_w2_b.grad.clone()])
+    names = ("y", "grad_x", "grad_w1", "grad_A", "grad_B")
+    rels = {name: _rel(ref, got) for name, ref, got in zip(names, *res)}
+    # the factor gradients are signed sums over every token of products of two quantised tensors; the two
+    # forms quantise alpha * grad and grad respectively, so those sums move by a few percent of their maximum
+    # (quantisation noise, not accumulation order). The reference's acceptance for quantised paths is 0.10.
+    assert all(v < (2e-2 if name in ("y", "grad_x") else 0.10) for name, v in rels.items()), rels
