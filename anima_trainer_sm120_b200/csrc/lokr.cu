@@ -37,6 +37,8 @@ struct MergeLoader {
   int64_t K, vp, vq, uq;
   using Raw = uint4;
   static constexpr bool kZeroSafe = false;   // finish reads the factors at (row, col)
+  static constexpr int kSmemBytes = 0;
+  __device__ __forceinline__ void prepare(void*) {}
   __device__ __forceinline__ Raw fetch(int64_t r, int64_t c) const { return ldg_stream16(w + r * K + c); }
   __device__ __forceinline__ uint4 operator()(int64_t r, int64_t c) const { return finish(fetch(r, c), r, c); }
   // W comes from HBM (fetch); the factors are small and cache-resident and are read here.

@@ -14,6 +14,8 @@
 // arithmetic, e = E - 8 + (m > 1.75). The kernel uses that integer form: it does
 // not depend on the accuracy of a hardware log2 near m == 1.75, the only mantissa
 // a bf16 input can take that lands on the rounding boundary.
+#include <mutex>
+
 #include "mx_quantize_tile.cuh"
 
 namespace anima {
@@ -24,64 +26,82 @@ using namespace mxq;
 struct PlainLoader {
   using Raw = uint4;
   static constexpr bool kZeroSafe = true;
+  static constexpr int kSmemBytes = 0;
+  __device__ __forceinline__ void prepare(void*) {}
   const __nv_bfloat16* x;
   int64_t ld;
   __device__ __forceinline__ Raw fetch(int64_t r, int64_t c) const { return ldg_stream16(x + r * ld + c); }
   __device__ __forceinline__ uint4 finish(const Raw& raw, int64_t, int64_t) const { return raw; }
 };
 
-// erf(t) for t >= 0 as 1 - erfc(t), erfc(t) = 2^(-t q(t)) with q a degree-10 least-squares fit of
-// -log2(erfc(t)) / t on [0, 4] (beyond 4, erf rounds to 1 in fp32). Absolute error about 1e-7, i.e.
-// one or two fp32 steps of erf: branch-free and a quarter of the instructions of the libm erff,
-// which otherwise makes this loader compute-bound.
-__device__ __forceinline__ float erf_nonneg(float t) {
-  t = fminf(t, 4.0f);
-  float q = -1.434943897e-07f;
-  q = fmaf(q, t, 3.633767847e-06f);
-  q = fmaf(q, t, -4.095852273e-05f);
-  q = fmaf(q, t, 2.688576060e-04f);
-  q = fmaf(q, t, -1.106124022e-03f);
-  q = fmaf(q, t, 2.616207348e-03f);
-  q = fmaf(q, t, -3.566088853e-04f);
-  q = fmaf(q, t, -2.759680524e-02f);
-  q = fmaf(q, t, 1.482741833e-01f);
-  q = fmaf(q, t, 9.184474349e-01f);
-  q = fmaf(q, t, 1.627907038e+00f);
-  float e;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-t * q));
-  return 1.f - e;
+// ---- GELU inside the quantiser ----------------------------------------------------------------
+// A bf16 GELU is a function of 16 input bits, and so is the factor gelu'(x) that multiplies the incoming
+// gradient. Both are tabulated for |x| in [2^-11, 8) (14 binades x 128 mantissas x 2 signs = 3584 entries):
+// the table is filled once per device by evaluating, with the CUDA math library, exactly the expressions an
+// eager bf16 GELU kernel evaluates in fp32,
+//     forward   x * 0.5 * (1 + erf(x / sqrt 2))                         stored rounded to bf16
+//     backward  0.5 * (1 + erf(x / sqrt 2)) + x * exp(-x^2 / 2) / sqrt(2 pi)   stored as fp32, then dy * factor
+// so the quantised codes equal those of quantising the materialised activation / gradient bit for bit,
+// while a lookup costs a fraction of the ~25 instructions of an erf evaluation (which made this loader
+// compute-bound). Inputs outside the table (|x| < 2^-11 or >= 8, NaN, inf: about 1 in 2500 for N(0,1) data)
+// take the same expressions directly. Each CTA copies the table it needs (7 or 14 KB) into shared memory.
+constexpr int kGeluLutMinExp = 127 - 11;   // biased exponent of 2^-11
+constexpr int kGeluLutMaxExp = 127 + 3;    // first binade NOT in the table: [8, 16)
+constexpr int kGeluLutHalf = (kGeluLutMaxExp - kGeluLutMinExp) * 128;
+constexpr int kGeluLutSize = 2 * kGeluLutHalf;
+__device__ __align__(16) uint16_t g_gelu_lut[kGeluLutSize];
+__device__ __align__(16) float g_gelu_grad_lut[kGeluLutSize];
+
+__device__ __noinline__ float gelu_eager_f(float x) {   // rare path: kept out of line so the lookup loop stays small
+  return x * 0.5f * (1.f + erff(x * 0.70710678118654752440f));
+}
+__device__ __noinline__ float gelu_grad_factor_eager_f(float x) {
+  const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752440f));
+  const float pdf = expf(-0.5f * x * x) * 0.39894228040143267794f;   // M_2_SQRTPI * M_SQRT1_2 * 0.5
+  return cdf + x * pdf;
+}
+// index of a bf16 bit pattern in the tables, or -1
+__device__ __forceinline__ int gelu_lut_index(uint32_t bits16) {
+  const int mag = static_cast<int>(bits16 & 0x7fffu) - (kGeluLutMinExp << 7);
+  if (static_cast<unsigned>(mag) >= static_cast<unsigned>(kGeluLutHalf)) return -1;
+  return mag + ((bits16 & 0x8000u) ? kGeluLutHalf : 0);
 }
 
-// Exact-form (erf) GELU of a pre-activation, evaluated in fp32 in the order an eager bf16 GELU uses,
-// x * 0.5 * (1 + erf(x / sqrt 2)), and rounded to bf16 where that kernel would store it. Over all
-// finite bf16 inputs the rounded result equals the libm-erff form for x > -3.1; in the negative tail,
-// where 1 + erf cancels in fp32 and either form carries only a few significant bits, a tenth of the
-// inputs differ by a few bf16 steps of values below 3e-3.
-__device__ __forceinline__ float gelu_f(float v) {
-  const float erf = copysignf(erf_nonneg(fabsf(v) * 0.70710678118654752440f), v);
-  return v * 0.5f * (1.f + erf);
-}
-__device__ __forceinline__ float gelu_grad_f(float v, float dy) {
-  const float erf = copysignf(erf_nonneg(fabsf(v) * 0.70710678118654752440f), v);
-  const float cdf = 0.5f * (1.f + erf);
-  float pdf;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pdf) : "f"(v * v * -0.72134752044448170368f));   // exp(-v^2 / 2)
-  pdf *= 0.39894228040143267794f;                                                           // 1 / sqrt(2 pi)
-  return dy * (cdf + v * pdf);
+__global__ void gelu_lut_init_kernel() {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= kGeluLutSize) return;
+  const uint32_t bits = static_cast<uint32_t>((i % kGeluLutHalf) + (kGeluLutMinExp << 7)) | (i >= kGeluLutHalf ? 0x8000u : 0u);
+  const float x = __uint_as_float(bits << 16);
+  g_gelu_lut[i] = __bfloat16_as_ushort(__float2bfloat16_rn(gelu_eager_f(x)));
+  g_gelu_grad_lut[i] = gelu_grad_factor_eager_f(x);
 }
 
 struct GeluLoader {
   using Raw = uint4;
   static constexpr bool kZeroSafe = true;   // gelu(0) = 0
+  static constexpr int kSmemBytes = kGeluLutSize * 2;
   const __nv_bfloat16* h;
   int64_t ld;
+  const uint16_t* lut;                       // shared-memory copy, set by prepare()
+  __device__ __forceinline__ void prepare(void* smem) {
+    uint4* dst = static_cast<uint4*>(smem);
+    const uint4* src = reinterpret_cast<const uint4*>(g_gelu_lut);
+    for (int i = threadIdx.x; i < kGeluLutSize / 8; i += blockDim.x) dst[i] = src[i];
+    lut = static_cast<const uint16_t*>(smem);
+  }
   __device__ __forceinline__ Raw fetch(int64_t r, int64_t c) const { return ldg_stream16(h + r * ld + c); }
+  __device__ __forceinline__ uint32_t one(uint32_t bits16) const {
+    const int idx = gelu_lut_index(bits16);
+    if (idx >= 0) return lut[idx];
+    return __bfloat16_as_ushort(__float2bfloat16_rn(gelu_eager_f(__uint_as_float(bits16 << 16))));
+  }
   __device__ __forceinline__ uint4 finish(const Raw& raw, int64_t, int64_t) const {
-    float f[8];
-    unpack8(raw, f);
+    uint4 out;
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
+    uint32_t* o = reinterpret_cast<uint32_t*>(&out);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) f[k] = gelu_f(f[k]);
-    return pack8(f);
+    for (int k = 0; k < 4; ++k) o[k] = one(w[k] & 0xffffu) | (one(w[k] >> 16) << 16);
+    return out;
   }
 };
 
@@ -89,17 +109,33 @@ struct GeluLoader {
 struct GeluBwdLoader {
   using Raw = uint4;                           // the pre-activation; the incoming gradient is read in finish
   static constexpr bool kZeroSafe = false;     // (keeping both tiles in registers up front spills)
+  static constexpr int kSmemBytes = kGeluLutSize * 4;
   const __nv_bfloat16* h;
   const __nv_bfloat16* grad_act;
   int64_t ld;
+  const float* lut;
+  __device__ __forceinline__ void prepare(void* smem) {
+    uint4* dst = static_cast<uint4*>(smem);
+    const uint4* src = reinterpret_cast<const uint4*>(g_gelu_grad_lut);
+    for (int i = threadIdx.x; i < kGeluLutSize / 4; i += blockDim.x) dst[i] = src[i];
+    lut = static_cast<const float*>(smem);
+  }
   __device__ __forceinline__ Raw fetch(int64_t r, int64_t c) const { return ldg_stream16(h + r * ld + c); }
+  __device__ __forceinline__ float factor(uint32_t bits16) const {
+    const int idx = gelu_lut_index(bits16);
+    if (idx >= 0) return lut[idx];
+    return gelu_grad_factor_eager_f(__uint_as_float(bits16 << 16));
+  }
   __device__ __forceinline__ uint4 finish(const Raw& raw, int64_t r, int64_t c) const {
-    float f[8], g[8];
-    unpack8(raw, f);
+    float g[8], o[8];
     unpack8(ldg_stream16(grad_act + r * ld + c), g);
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) f[k] = gelu_grad_f(f[k], g[k]);
-    return pack8(f);
+    for (int k = 0; k < 4; ++k) {
+      o[2 * k] = g[2 * k] * factor(w[k] & 0xffffu);
+      o[2 * k + 1] = g[2 * k + 1] * factor(w[k] >> 16);
+    }
+    return pack8(o);
   }
 };
 
@@ -244,6 +280,40 @@ extern "C" int anima_mx_quantize(const void* x, int64_t rows, int64_t cols, int6
                          scale_layout, stream);
 }
 
+namespace {
+
+// Fills the GELU tables of the current device on first use. The fill runs on the caller's stream; until it
+// has completed, calls on any stream are ordered after it with an event wait (no host synchronisation).
+int ensure_gelu_tables(cudaStream_t s) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static int state[kMaxDevices];            // 0 not started, 1 fill launched, 2 fill known complete
+  static cudaEvent_t filled[kMaxDevices];
+  int dev = 0;
+  ANIMA_REQUIRE(cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices, ANIMA_E_CUDA,
+                "mx_quantize_gelu: cannot identify the current device");
+  std::lock_guard<std::mutex> lock(mu);
+  if (state[dev] == 2) return ANIMA_OK;
+  if (state[dev] == 0) {
+    ANIMA_REQUIRE(cudaEventCreateWithFlags(&filled[dev], cudaEventDisableTiming) == cudaSuccess, ANIMA_E_CUDA,
+                  "mx_quantize_gelu: cannot create an event");
+    gelu_lut_init_kernel<<<ceil_div(kGeluLutSize, 256), 256, 0, s>>>();
+    ANIMA_CHECK_LAUNCH("mx_quantize_gelu table fill");
+    ANIMA_REQUIRE(cudaEventRecord(filled[dev], s) == cudaSuccess, ANIMA_E_CUDA, "mx_quantize_gelu: cannot record an event");
+    state[dev] = 1;
+    return ANIMA_OK;
+  }
+  if (cudaEventQuery(filled[dev]) == cudaSuccess) {
+    state[dev] = 2;
+    return ANIMA_OK;
+  }
+  ANIMA_REQUIRE(cudaStreamWaitEvent(s, filled[dev], 0) == cudaSuccess, ANIMA_E_CUDA,
+                "mx_quantize_gelu: cannot order the stream after the table fill");
+  return ANIMA_OK;
+}
+
+}  // namespace
+
 extern "C" int anima_mx_quantize_gelu(const void* h, const void* grad_act, int64_t rows, int64_t cols,
                                       int64_t ld, uint8_t* codes_row, uint8_t* scales_row,
                                       uint8_t* codes_colT, uint8_t* scales_col, int scale_layout,
@@ -253,12 +323,13 @@ extern "C" int anima_mx_quantize_gelu(const void* h, const void* grad_act, int64
     return rc;
   ANIMA_REQUIRE(!grad_act || aligned16(grad_act), ANIMA_E_ALIGN, "mx_quantize_gelu: grad_act must be 16-byte aligned");
   if (rows == 0 || cols == 0) return ANIMA_OK;
+  if (int rc = ensure_gelu_tables(static_cast<cudaStream_t>(stream))) return rc;
   if (grad_act) {
-    const GeluBwdLoader load{static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(grad_act), ld};
+    const GeluBwdLoader load{static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(grad_act), ld, nullptr};
     return launch_quantize("mx_quantize_gelu", load, rows, cols, codes_row, scales_row, codes_colT, scales_col,
                            scale_layout, stream);
   }
-  const GeluLoader load{static_cast<const __nv_bfloat16*>(h), ld};
+  const GeluLoader load{static_cast<const __nv_bfloat16*>(h), ld, nullptr};
   return launch_quantize("mx_quantize_gelu", load, rows, cols, codes_row, scales_row, codes_colT, scales_col,
                          scale_layout, stream);
 }

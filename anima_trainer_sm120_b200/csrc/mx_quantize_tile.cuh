@@ -52,11 +52,14 @@ __device__ __forceinline__ int tiled_offset(int r, int j) {
 //   Raw   fetch(int64_t row, int64_t col) const;                issues the long-latency loads only
 //   uint4 finish(const Raw&, int64_t row, int64_t col) const;   the 8 bf16 values
 //   static constexpr bool kZeroSafe;                            finish(Raw{}) == 0 and reads no memory
+//   static constexpr int kSmemBytes; void prepare(void* smem);  per-CTA shared-memory state (a lookup table)
 // All eight fetches of a thread are issued before the first finish, so a loader that computes
 // (merge, GELU) does not serialise its chunks on memory latency.
 template <bool ROW, bool COL, class Loader>
-__global__ void __launch_bounds__(kThreads, COL ? 3 : 4) mx_quantize_kernel(const QuantParams p, const Loader load) {
+__global__ void __launch_bounds__(kThreads, COL ? 3 : 4) mx_quantize_kernel(const QuantParams p, const Loader load_arg) {
   __shared__ uint4 tile[COL ? kTile * 16 : 1];  // 128 rows x 256 B
+  __shared__ __align__(16) uint8_t loader_smem[Loader::kSmemBytes > 0 ? Loader::kSmemBytes : 16];
+  Loader load = load_arg;
   __shared__ __align__(16) uint8_t sc_row[ROW ? 512 : 16];
   __shared__ __align__(16) uint8_t sc_col[COL ? 512 : 16];
 
@@ -81,7 +84,8 @@ __global__ void __launch_bounds__(kThreads, COL ? 3 : 4) mx_quantize_kernel(cons
     fetched[i] = typename Loader::Raw{};
     if (col_ok && r < p.rows) fetched[i] = load.fetch(r, col);
   }
-  if (ROW || COL) __syncthreads();  // zero fill of sc_* visible before the byte stores
+  load.prepare(loader_smem);   // after the tile's loads are in flight; visible to all threads after the barrier
+  __syncthreads();             // also: zero fill of sc_* visible before the byte stores
 
 #pragma unroll
   for (int i = 0; i < 8; ++i) {

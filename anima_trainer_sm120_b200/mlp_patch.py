@@ -15,9 +15,9 @@ backward  quantise grad_y; grad_act = grad_y W2 (bf16); dW2 = grad_y^T gelu(h) (
           dW1 = grad_h^T x (fp32) -> dw1, dw2.
 
 The arithmetic of each step is that of the unfused chain (the activation and its gradient are rounded
-to bf16 before quantisation exactly where the eager kernels would round them); the only difference
-from ``lokr_linear_fused -> F.gelu -> lokr_linear_fused`` is the erf evaluation inside the GELU, which
-agrees with the eager kernel's to about one fp32 step.
+to bf16 before quantisation exactly where the eager kernels would round them, and the GELU values come
+from a table of the eager kernel's own fp32 expressions), so the result equals
+``lokr_linear_fused -> F.gelu -> lokr_linear_fused`` bit for bit.
 
 ``install`` patches ``GPT2FeedForward.forward``; a call falls through to the original forward unless
 both layers carry an eligible LoKr adapter on the quantised path and the activation is the exact GELU.
@@ -96,10 +96,29 @@ def _adapter(linear: nn.Module):
     return mod
 
 
+def _tlokr_adapter(linear: nn.Module):
+    mod = getattr(getattr(linear, "forward", None), "__self__", None)
+    if mod is None or not getattr(mod, "_tlokr_enabled", False):
+        return None
+    if mod.module_dropout and mod.training:
+        return None
+    return mod
+
+
 def _patched_forward(self, x: torch.Tensor) -> torch.Tensor:
-    m1, m2 = _adapter(self.layer1), _adapter(self.layer2)
     act = self.activation
     exact_gelu = isinstance(act, nn.GELU) and getattr(act, "approximate", "none") == "none"
+    t1, t2 = _tlokr_adapter(self.layer1), _tlokr_adapter(self.layer2)
+    if t1 is not None and t2 is not None and exact_gelu:
+        from . import tlokr
+        p1 = tlokr.single_node_plan(t1, x)
+        if p1 is not None:
+            # layer 2 sees a tensor of layer 1's output shape; only shape, dtype and device enter its plan
+            hidden = tlokr._ActSpec((*x.shape[:-1], t1.org_module[0].out_features), x.dtype, x.device)
+            p2 = tlokr.single_node_plan(t2, hidden)
+            if p2 is not None:
+                return tlokr._MXTLoKrMLP.apply(x.contiguous(), *p1, *p2)
+    m1, m2 = _adapter(self.layer1), _adapter(self.layer2)
     if (m1 is None or m2 is None or not exact_gelu or not x.is_cuda
             or (x.numel() // x.shape[-1]) % lokr_patch.MX_ALIGN):
         return _PATCHED[type(self)](self, x)

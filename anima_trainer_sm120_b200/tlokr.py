@@ -24,6 +24,8 @@ from contextvars import ContextVar
 from dataclasses import dataclass, field
 from types import MethodType
 
+from typing import NamedTuple
+
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
@@ -330,6 +332,63 @@ def _structured_delta(module, x: torch.Tensor, *, fp8: bool, base: torch.Tensor 
     return torch.add(base, fn.apply(*args), alpha=alpha)
 
 
+def _mx_linear_fwd(x_row, lead_shape, W_mx, bias, w1, w2_a, w2_b, mask, alpha):
+    """``y = x W^T + bias + alpha * delta(x)`` from the row-wise MXFP8 operand of x ``[rows, K]``.
+    Returns (y, small factor operands kept for backward)."""
+    from .fp8_quant import _bias_bf16
+    c = w1.to(BF16)
+    uq = c.shape[1]
+    vp, rank = w2_a.shape
+    rows, K = x_row.rows, x_row.k
+    n_out = W_mx.row.rows
+    aq, aq_col = _q(w2_a.detach(), col=True)      # A [vp, r]: row form for out, column form for dgrad
+    bq, bq_col = _q(w2_b.detach(), col=True)      # B [r, vq]
+    gq = ops.mx_regroup(x_row, rows * uq, K // uq)            # same codes, scales re-tiled for the grouped view
+    y = torch.empty(*lead_shape, n_out, dtype=BF16, device=x_row.codes.device)
+    ops.mx_gemm(x_row, W_mx.row, bias=_bias_bf16(bias), out=y.view(-1, n_out))
+    hidden = ops.mx_gemm(gq, bq).view(lead_shape[0], -1, uq, rank)
+    mixed = rank_mix(hidden, c, mask)
+    mq, _ = _q(mixed.reshape(-1, rank))
+    res = y.view(-1, vp)
+    ops.mx_gemm(mq, aq, residual=res, alpha=float(alpha), out=res)       # y += alpha * delta
+    return y, (aq_col, bq, bq_col)
+
+
+def _mx_linear_bwd(quant_grad, quant_grouped, lead_shape, K, W_mx, w1, w2_a, w2_b, mask, alpha, factor_ops):
+    """Backward of :func:`_mx_linear_fwd`. ``quant_grad(rows, k)`` / ``quant_grouped(rows, k)`` return the
+    (row, column) MXFP8 operands of the incoming gradient / of the layer input viewed as ``[rows, k]``, so a
+    caller can fold an elementwise op (the MLP activation and its derivative) into those quantisations.
+    Returns (grad_x bf16 [*lead, K], grad_w1, grad_A, grad_B)."""
+    aq_col, bq, bq_col = factor_ops
+    c = w1.to(BF16)
+    up, uq = c.shape
+    vp, rank = w2_a.shape
+    vq = K // uq
+    rows = 1
+    for d in lead_shape:
+        rows *= d
+    gbq, gbq_col = quant_grad(rows * up, vp)                                        # grad as [rows * up, vp]
+    g_x = torch.empty(*lead_shape, K, dtype=BF16, device=gbq.codes.device)
+    ops.mx_gemm(ops.mx_regroup(gbq, rows, up * vp), W_mx.col, out=g_x.view(rows, K))   # base dgrad
+    gq, gq_col = quant_grouped(rows * uq, vq)
+    hidden = ops.mx_gemm(gq, bq).view(lead_shape[0], -1, uq, rank)
+    mixed = rank_mix(hidden, c, mask)
+    _, mq_col = ops.mx_quantize(mixed.reshape(-1, rank), rowwise=False, colwise=True)
+    g_a = ops.mx_gemm(gbq_col, mq_col, out_dtype=torch.float32, alpha=alpha)        # alpha * grad^T @ mixed  [vp, r]
+    g_mixed = ops.mx_gemm(gbq, aq_col, alpha=alpha).view(*mixed.shape)              # alpha * grad @ A        [.., r]
+    g_c = rank_mix_wgrad(g_mixed, hidden, mask)
+    g_hidden = rank_mix(g_mixed, c, mask, transpose=True)
+    ghq, ghq_col = _q(g_hidden.reshape(-1, rank), col=True)
+    g_b = ops.mx_gemm(ghq_col, gq_col, out_dtype=torch.float32)                     # grad_hidden^T @ grouped [r, vq]
+    res = g_x.view(-1, vq)
+    ops.mx_gemm(ghq, bq_col, residual=res, out=res)                                 # g_x += grad_hidden @ B
+    return g_x, g_c.to(w1.dtype), g_a.to(w2_a.dtype), g_b.to(w2_b.dtype)
+
+
+def _bf16c(t: torch.Tensor) -> torch.Tensor:
+    return t.contiguous() if t.dtype == BF16 else t.to(BF16).contiguous()
+
+
 class _MXTLoKrLinear(torch.autograd.Function):
     """The whole quantised T-LoKr linear, ``x W^T + bias + alpha * delta(x)``, as ONE autograd node.
 
@@ -348,26 +407,11 @@ class _MXTLoKrLinear(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, W_mx, bias, w1, w2_a, w2_b, mask, alpha: float):
-        from .fp8_quant import _bias_bf16, quantize_activation
-        c = w1.to(BF16)
-        uq = c.shape[1]
-        vp, rank = w2_a.shape
-        K = x.shape[-1]
-        rows = x.numel() // K
-        n_out = W_mx.row.rows
-        aq, aq_col = _q(w2_a.detach(), col=True)      # A [vp, r]: row form for out, column form for dgrad
-        bq, bq_col = _q(w2_b.detach(), col=True)      # B [r, vq]
+        from .fp8_quant import quantize_activation
         x_row, _ = quantize_activation(x, colwise=False)
-        gq = ops.mx_regroup(x_row, rows * uq, K // uq)
-        y = torch.empty(*x.shape[:-1], n_out, dtype=BF16, device=x.device)
-        ops.mx_gemm(x_row, W_mx.row, bias=_bias_bf16(bias), out=y.view(-1, n_out))
-        hidden = ops.mx_gemm(gq, bq).view(x.shape[0], -1, uq, rank)
-        mixed = rank_mix(hidden, c, mask)
-        mq, _ = _q(mixed.reshape(-1, rank))
-        res = y.view(-1, vp)
-        ops.mx_gemm(mq, aq, residual=res, alpha=float(alpha), out=res)       # y += alpha * delta
+        y, factor_ops = _mx_linear_fwd(x_row, x.shape[:-1], W_mx, bias, w1, w2_a, w2_b, mask, alpha)
         ctx.save_for_backward(x, w1, w2_a, w2_b, *(() if mask is None else (mask,)))
-        ctx.has_mask, ctx.ops, ctx.W_mx = mask is not None, (aq_col, bq, bq_col), W_mx
+        ctx.has_mask, ctx.ops, ctx.W_mx = mask is not None, factor_ops, W_mx
         ctx.alpha, ctx.bias_grad = float(alpha), bias is not None and bias.requires_grad
         return y
 
@@ -376,31 +420,79 @@ class _MXTLoKrLinear(torch.autograd.Function):
         saved = ctx.saved_tensors        # read once: activation checkpointing unpacks on access
         x, w1, w2_a, w2_b = saved[:4]
         mask = saved[4] if ctx.has_mask else None
-        aq_col, bq, bq_col = ctx.ops
-        c = w1.to(BF16)
-        up, uq = c.shape
-        vp, rank = w2_a.shape
-        K = x.shape[-1]
-        rows = x.numel() // K
-        gy = grad_output.contiguous() if grad_output.dtype == BF16 else grad_output.to(BF16).contiguous()
-        gbq, gbq_col = _q(gy.view(-1, vp), col=True)                                   # grad as [rows * up, vp]
-        g_x = torch.empty_like(x)
-        ops.mx_gemm(ops.mx_regroup(gbq, rows, up * vp), ctx.W_mx.col, out=g_x.view(rows, K))   # base dgrad
-        grouped = _grouped(x, uq)
-        gq, gq_col = _q(grouped.reshape(-1, grouped.shape[-1]), col=True)
-        hidden = ops.mx_gemm(gq, bq).view(*grouped.shape[:-1], rank)
-        mixed = rank_mix(hidden, c, mask)
-        _, mq_col = ops.mx_quantize(mixed.reshape(-1, rank), rowwise=False, colwise=True)
-        g_a = ops.mx_gemm(gbq_col, mq_col, out_dtype=torch.float32, alpha=ctx.alpha)   # alpha * grad^T @ mixed  [vp, r]
-        g_mixed = ops.mx_gemm(gbq, aq_col, alpha=ctx.alpha).view(*mixed.shape)         # alpha * grad @ A        [.., r]
-        g_c = rank_mix_wgrad(g_mixed, hidden, mask)
-        g_hidden = rank_mix(g_mixed, c, mask, transpose=True)
-        ghq, ghq_col = _q(g_hidden.reshape(-1, rank), col=True)
-        g_b = ops.mx_gemm(ghq_col, gq_col, out_dtype=torch.float32)                    # grad_hidden^T @ grouped [r, vq]
-        res = g_x.view(-1, grouped.shape[-1])
-        ops.mx_gemm(ghq, bq_col, residual=res, out=res)                                # g_x += grad_hidden @ B
-        g_bias = gy.view(rows, -1).sum(dim=0) if ctx.bias_grad else None
-        return g_x, None, g_bias, g_c.to(w1.dtype), g_a.to(w2_a.dtype), g_b.to(w2_b.dtype), None, None
+        gy = _bf16c(grad_output)
+        g_x, g_c, g_a, g_b = _mx_linear_bwd(
+            lambda r, k: _q(gy.view(r, k), col=True), lambda r, k: _q(x.reshape(r, k), col=True),
+            x.shape[:-1], x.shape[-1], ctx.W_mx, w1, w2_a, w2_b, mask, ctx.alpha, ctx.ops)
+        g_bias = gy.reshape(-1, gy.shape[-1]).sum(dim=0) if ctx.bias_grad else None
+        return g_x, None, g_bias, g_c, g_a, g_b, None, None
+
+
+class _MXTLoKrMLP(torch.autograd.Function):
+    """``layer2(gelu(layer1(x)))`` with both layers quantised T-LoKr linears, as one node: the activation and
+    its derivative are evaluated inside the quantiser (``ops.mx_quantize_gelu``), so neither ``gelu(h)`` nor
+    ``grad * gelu'(h)`` is ever written as a bf16 tensor. Saves x, the pre-activation h and the factors."""
+
+    @staticmethod
+    def forward(ctx, x, W1, b1, w1_1, a_1, b_1, mask1, alpha1: float, W2, b2, w1_2, a_2, b_2, mask2, alpha2: float):
+        from .fp8_quant import quantize_activation
+        x_row, _ = quantize_activation(x, colwise=False)
+        h, ops1 = _mx_linear_fwd(x_row, x.shape[:-1], W1, b1, w1_1, a_1, b_1, mask1, alpha1)
+        act_row, _ = ops.mx_quantize_gelu(h.view(-1, h.shape[-1]), rowwise=True)
+        y, ops2 = _mx_linear_fwd(act_row, x.shape[:-1], W2, b2, w1_2, a_2, b_2, mask2, alpha2)
+        masks = tuple(m for m in (mask1, mask2) if m is not None)
+        ctx.save_for_backward(x, h, w1_1, a_1, b_1, w1_2, a_2, b_2, *masks)
+        ctx.has_masks = (mask1 is not None, mask2 is not None)
+        ctx.ops, ctx.W = (ops1, ops2), (W1, W2)
+        ctx.alphas = (float(alpha1), float(alpha2))
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        saved = ctx.saved_tensors
+        x, h, w1_1, a_1, b_1, w1_2, a_2, b_2 = saved[:8]
+        rest = list(saved[8:])
+        mask1 = rest.pop(0) if ctx.has_masks[0] else None
+        mask2 = rest.pop(0) if ctx.has_masks[1] else None
+        gy = _bf16c(grad_output)
+        lead = x.shape[:-1]
+        # layer 2: its input is gelu(h), quantised straight from h
+        g_act, g_c2, g_a2, g_b2 = _mx_linear_bwd(
+            lambda r, k: _q(gy.view(r, k), col=True),
+            lambda r, k: ops.mx_quantize_gelu(h.view(r, k), rowwise=True, colwise=True),
+            lead, h.shape[-1], ctx.W[1], w1_2, a_2, b_2, mask2, ctx.alphas[1], ctx.ops[1])
+        # layer 1: its incoming gradient is g_act * gelu'(h), formed inside the quantiser
+        g_x, g_c1, g_a1, g_b1 = _mx_linear_bwd(
+            lambda r, k: ops.mx_quantize_gelu(h.view(r, k), g_act.view(r, k), rowwise=True, colwise=True),
+            lambda r, k: _q(x.reshape(r, k), col=True),
+            lead, x.shape[-1], ctx.W[0], w1_1, a_1, b_1, mask1, ctx.alphas[0], ctx.ops[0])
+        return (g_x, None, None, g_c1, g_a1, g_b1, None, None,
+                None, None, g_c2, g_a2, g_b2, None, None)
+
+
+class _ActSpec(NamedTuple):
+    """Shape, dtype and device of an activation: all the dispatch looks at."""
+    shape: tuple
+    dtype: torch.dtype
+    device: torch.device
+
+
+def single_node_plan(module, x):
+    """Arguments ``(W_mx, bias, w1, A, B, mask, alpha)`` of the one-node quantised T-LoKr linear for an input
+    ``x`` (a tensor or an :class:`_ActSpec`), or None when the call has to take the general path (no
+    pre-quantised base, rows not a multiple of 32, input not bf16 on CUDA, a factor other than 8 x 8, or an active
+    rank the MXFP8 GEMMs cannot contract)."""
+    base_q = getattr(module, "_tlokr_fp8_base_weight", None)
+    rows = 1
+    for d in x.shape[:-1]:
+        rows *= d
+    if (base_q is None or base_q.col is None or x.device.type != "cuda" or x.dtype != BF16
+            or rows % 32 or tuple(module.lokr_w1.shape) != (8, 8)):
+        return None
+    fn, w2_a, w2_b, mask = _delta_plan(module, x, fp8=True)
+    if fn is not _MXStructuredLoKr:
+        return None
+    return base_q, module.org_module[0].bias, module.lokr_w1, w2_a, w2_b, mask, module._tlokr_alpha
 
 
 def forward(module, x: torch.Tensor) -> torch.Tensor:
@@ -409,11 +501,9 @@ def forward(module, x: torch.Tensor) -> torch.Tensor:
     org = module.org_module[0]
     base_q = getattr(module, "_tlokr_fp8_base_weight", None)
     quantised = base_q is not None and x.is_cuda and (x.numel() // x.shape[-1]) % 32 == 0
-    if quantised and x.dtype == BF16 and base_q.col is not None and tuple(module.lokr_w1.shape) == (8, 8):
-        fn, w2_a, w2_b, mask = _delta_plan(module, x, fp8=True)
-        if fn is _MXStructuredLoKr:
-            return _MXTLoKrLinear.apply(x.contiguous(), base_q, org.bias, module.lokr_w1, w2_a, w2_b, mask,
-                                        module._tlokr_alpha)
+    plan = single_node_plan(module, x)
+    if plan is not None:
+        return _MXTLoKrLinear.apply(x.contiguous(), *plan)
     if quantised:
         from .fp8_quant import fp8_frozen_linear
         base = fp8_frozen_linear(x, base_q, org.weight, org.bias)

@@ -74,7 +74,7 @@ int anima_mx_quantize(const void* x_bf16, int64_t rows, int64_t cols, int64_t ld
 /* Quantise an MLP activation without materialising it (no reference counterpart: the reference
  * runs GELU as a separate eager kernel between mlp.layer1 and mlp.layer2 and quantises its output).
  * h bf16 [rows, cols] is the pre-activation.
- *   grad_act == NULL : quantises bf16(gelu(h)), exact erf form.
+ *   grad_act == NULL : quantises bf16(gelu(h)), exact erf form, bit-identical to an eager fp32-math bf16 GELU.
  *   grad_act != NULL : quantises bf16(grad_act * gelu'(h)), the gradient w.r.t. h; grad_act has h's
  *                      shape and leading dimension.
  * Outputs, scale layout and size rules are those of anima_mx_quantize. */

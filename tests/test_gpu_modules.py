@@ -248,3 +248,34 @@ def test_tlokr_single_node_linear_matches_three_node_composition():
     # forms quantise alpha * grad and grad respectively, so those sums move by a few percent of their maximum
     # (quantisation noise, not accumulation order). The reference's acceptance for quantised paths is 0.10.
     assert all(v < (2e-2 if name in ("y", "grad_x") else 0.10) for name, v in rels.items()), rels
+
+
+def test_tlokr_mlp_node_matches_two_linears_with_eager_gelu():
+    from anima_trainer_sm120_b200 import fp8_quant, tlokr
+    _, m1, l1 = _tlokr_module(in_f=512, out_f=2048, rank=64)
+    _, m2, l2 = _tlokr_module(in_f=2048, out_f=512, rank=64)
+    with torch.no_grad():
+        for m, l in ((m1, l1), (m2, l2)):
+            m.lokr_w2_b.normal_(std=0.05)
+            l.weight.normal_(std=0.03)
+    W1, W2 = fp8_quant.quantize_weight(l1.weight), fp8_quant.quantize_weight(l2.weight)
+    t = torch.rand(4, device=DEV)
+    mask = tlokr._TimestepState(timesteps=t).mask(max_rank=64, min_rank=32, dtype=BF16, device=torch.device(DEV))
+    x = torch.randn(4, 128, 512, device=DEV, dtype=BF16)
+    probe = torch.randn(4, 128, 512, device=DEV, dtype=BF16)
+    params = (m1.lokr_w1, m1.lokr_w2_a, m1.lokr_w2_b, m2.lokr_w1, m2.lokr_w2_a, m2.lokr_w2_b)
+    res = []
+    for fused in (False, True):
+        xi = x.clone().requires_grad_(True)
+        for p in params:
+            p.grad = None
+        a1 = (W1, l1.bias, m1.lokr_w1, m1.lokr_w2_a, m1.lokr_w2_b, mask, 0.8)
+        a2 = (W2, l2.bias, m2.lokr_w1, m2.lokr_w2_a, m2.lokr_w2_b, mask, 1.2)
+        if fused:
+            y = tlokr._MXTLoKrMLP.apply(xi, *a1, *a2)
+        else:
+            y = tlokr._MXTLoKrLinear.apply(F.gelu(tlokr._MXTLoKrLinear.apply(xi, *a1)), *a2)
+        y.backward(probe)
+        res.append([y.detach(), xi.grad] + [p.grad.clone() for p in params])
+    rels = [_rel(ref, got) for ref, got in zip(*res)]
+    assert all(v < (2e-2 if i < 2 else 0.10) for i, v in enumerate(rels)), rels
