@@ -81,3 +81,43 @@ class FusedGatedAdd(torch.autograd.Function):
 
 def fused_gated_add(x: torch.Tensor, gate: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
     return FusedGatedAdd.apply(x, gate, y)
+
+
+class FusedGatedAddAdaLN(torch.autograd.Function):
+    """``x_new = x + gate * sub`` followed by ``y = AdaLN(x_new; scale, shift)``: the residual update of one
+    sublayer and the modulation of the next, from one read of x and sub. Returns ``(x_new, y)``, each
+    bit-identical to ``FusedGatedAdd`` then ``FusedAdaLN``; backward runs their two backward kernels."""
+
+    @staticmethod
+    def forward(ctx, x, gate, sub, scale, shift, eps):
+        assert x.is_cuda, "FusedGatedAddAdaLN requires CUDA tensors"
+        assert x.shape == sub.shape, f"x {x.shape} != sub {sub.shape}"
+        B, T, H, W, D = x.shape
+        x_flat, sub_flat = _flat(x, D), _flat(sub, D)
+        gate_flat, scale_flat, shift_flat = _flat(gate, D), _flat(scale, D), _flat(shift, D)
+        HW = H * W
+        assert x_flat.shape[0] == gate_flat.shape[0] * HW == scale_flat.shape[0] * HW, "modulation shape mismatch"
+        x_new, y, mean, rstd = ops.gated_add_adaln_fwd(x_flat, gate_flat, sub_flat, scale_flat, shift_flat, eps, HW)
+        ctx.save_for_backward(sub_flat, gate_flat, x_new, scale_flat, mean, rstd)
+        ctx.shape, ctx.mod_shape, ctx.HW = (B, T, H, W, D), gate.shape, HW
+        ctx.dtypes = (x.dtype, gate.dtype, sub.dtype, scale.dtype, shift.dtype)
+        return x_new.view(B, T, H, W, D).to(x.dtype), y.view(B, T, H, W, D).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, d_xnew, d_y):
+        sub_flat, gate_flat, x_new, scale_flat, mean, rstd = ctx.saved_tensors
+        B, T, H, W, D = ctx.shape
+        xd, gd, ud, sd, bd = ctx.dtypes
+        dout = None if d_xnew is None else _flat(d_xnew, D)
+        dscale = dshift = None
+        if d_y is not None:
+            dx_ln, dscale, dshift = ops.adaln_bwd(_flat(d_y, D), x_new, scale_flat, mean, rstd, ctx.HW)
+            dout = dx_ln if dout is None else dout + dx_ln
+            dscale, dshift = dscale.view(ctx.mod_shape).to(sd), dshift.view(ctx.mod_shape).to(bd)
+        dsub, dgate = ops.gated_add_bwd(dout, sub_flat, gate_flat, ctx.HW)
+        return (dout.view(B, T, H, W, D).to(xd), dgate.view(ctx.mod_shape).to(gd), dsub.view(B, T, H, W, D).to(ud),
+                dscale, dshift, None)
+
+
+def fused_gated_add_adaln(x, gate, sub, scale, shift, eps):
+    return FusedGatedAddAdaLN.apply(x, gate, sub, scale, shift, eps)

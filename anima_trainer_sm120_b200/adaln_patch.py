@@ -1,8 +1,8 @@
 """Replace a DiT ``Block._forward`` with one that runs the AdaLN modulation
 ``LayerNorm(x) * (1 + scale) + shift`` and the gated residual ``x + gate * sublayer(...)`` on the
 fused sm_100a kernels — the call surface of anima-trainer's ``adaln_patch.py`` (``_patched_forward``
-:42-153, ``install`` :156-166, ``uninstall`` :169-177). Three FusedAdaLN and three FusedGatedAdd
-calls per block; control flow and argument list are those of the patched upstream method.
+:42-153, ``install`` :156-166, ``uninstall`` :169-177). One FusedAdaLN, two FusedGatedAddAdaLN (the reference's FusedGatedAdd + FusedAdaLN pair) and one
+FusedGatedAdd call per block; control flow and argument list are those of the patched upstream method.
 """
 from __future__ import annotations
 
@@ -11,7 +11,7 @@ from typing import Optional
 
 import torch
 
-from .adaln_kernel import FusedAdaLN, FusedGatedAdd
+from .adaln_kernel import FusedAdaLN, FusedGatedAdd, FusedGatedAddAdaLN
 from .adaln_merge import apply_merged_adaln
 
 _PATCHED: dict[type, object] = {}
@@ -41,15 +41,17 @@ def _patched_forward(self, x_B_T_H_W_D: torch.Tensor, emb_B_T_D: torch.Tensor, c
     (sh_s, sc_s, g_s), (sh_c, sc_c, g_c), (sh_m, sc_m, g_m) = mods
     B, T, H, W, D = x.shape
 
+    # The residual update of a sublayer and the modulation of the next one are one kernel (one read of x and of
+    # the sublayer output); the values are those of FusedGatedAdd followed by FusedAdaLN.
     n = FusedAdaLN.apply(x, _five(sc_s), _five(sh_s), self.layer_norm_self_attn.eps)
     r = self.self_attn(n.reshape(B, T * H * W, D), attn_params, None, rope_emb=rope_emb_L_1_1_D)
-    x = FusedGatedAdd.apply(x, _five(g_s), r.view(B, T, H, W, D))
+    x, n = FusedGatedAddAdaLN.apply(x, _five(g_s), r.view(B, T, H, W, D), _five(sc_c), _five(sh_c),
+                                    self.layer_norm_cross_attn.eps)
 
-    n = FusedAdaLN.apply(x, _five(sc_c), _five(sh_c), self.layer_norm_cross_attn.eps)
     r = self.cross_attn(n.reshape(B, T * H * W, D), attn_params, crossattn_emb, rope_emb=rope_emb_L_1_1_D)
-    x = FusedGatedAdd.apply(x, _five(g_c), r.view(B, T, H, W, D))
+    x, n = FusedGatedAddAdaLN.apply(x, _five(g_c), r.view(B, T, H, W, D), _five(sc_m), _five(sh_m),
+                                    self.layer_norm_mlp.eps)
 
-    n = FusedAdaLN.apply(x, _five(sc_m), _five(sh_m), self.layer_norm_mlp.eps)
     return FusedGatedAdd.apply(x, _five(g_m), self.mlp(n))
 
 

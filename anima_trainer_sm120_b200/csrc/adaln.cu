@@ -28,12 +28,18 @@ constexpr int kRowsPerIter = 4;
 // One warp per row; lane l owns the 16-byte chunks l, l+32, ... of the row. The row stays packed (bf16)
 // in registers and is unpacked in each of the three passes (sum, centred squares, output): that keeps the
 // kernel at ~50 registers, so 4 CTAs (32 warps, 128 KB of loads in flight) fit on an SM.
-template <int NCH>
+//
+// GATED: the row normalised is x_new = x + gate * sub (the gated residual of the PREVIOUS sublayer, same
+// arithmetic as gated_add_fwd_kernel: one fp32 fma, rounded once to bf16), which is also written out; the
+// two kernels of "residual update, then modulation of the next sublayer" become one pass that reads x and sub
+// and writes x_new and y (8 B/elem instead of 6 + 4).
+template <int NCH, bool GATED>
 __global__ void __launch_bounds__(kThreads, NCH <= 8 ? 4 : 2)
-adaln_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ scale,
+adaln_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate,
+                 const __nv_bfloat16* __restrict__ sub, const __nv_bfloat16* __restrict__ scale,
                  const __nv_bfloat16* __restrict__ shift, float eps, int64_t rows, int64_t hw,
-                 int d, __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out,
-                 float* __restrict__ rstd_out) {
+                 int d, __nv_bfloat16* __restrict__ x_new, __nv_bfloat16* __restrict__ y,
+                 float* __restrict__ mean_out, float* __restrict__ rstd_out) {
   const int lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -46,6 +52,22 @@ adaln_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
     const int col = (i * 32 + lane) * 8;
     raw[i] = make_uint4(0u, 0u, 0u, 0u);
     if (col < d) raw[i] = ldg_stream16(xr + col);
+  }
+  if (GATED) {
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const int col = (i * 32 + lane) * 8;
+      if (col < d) {
+        float xf[8], yf[8], gf[8], o[8];
+        unpack8(raw[i], xf);
+        unpack8(ldg_stream16(sub + row * d + col), yf);
+        unpack8(*reinterpret_cast<const uint4*>(gate + bt * d + col), gf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = xf[e] + gf[e] * yf[e];
+        raw[i] = pack8(o);
+        stg_stream16(x_new + row * d + col, raw[i]);   // the normalisation below sees the rounded values
+      }
+    }
   }
   float sum = 0.f;
 #pragma unroll
@@ -377,7 +399,7 @@ extern "C" int anima_adaln_fwd(const void* x, const void* scale, const void* shi
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int di = static_cast<int>(d);
 #define ANIMA_LAUNCH_FWD(N) \
-  adaln_fwd_kernel<N><<<grid, kThreads, 0, s>>>(xp, sp, bp, eps, rows, hw, di, yp, mean, rstd)
+  adaln_fwd_kernel<N, false><<<grid, kThreads, 0, s>>>(xp, nullptr, nullptr, sp, bp, eps, rows, hw, di, nullptr, yp, mean, rstd)
   if (d <= 256) ANIMA_LAUNCH_FWD(1);
   else if (d <= 512) ANIMA_LAUNCH_FWD(2);
   else if (d <= 1024) ANIMA_LAUNCH_FWD(4);
@@ -385,6 +407,38 @@ extern "C" int anima_adaln_fwd(const void* x, const void* scale, const void* shi
   else ANIMA_LAUNCH_FWD(16);
 #undef ANIMA_LAUNCH_FWD
   ANIMA_CHECK_LAUNCH("adaln_fwd");
+  return ANIMA_OK;
+}
+
+extern "C" int anima_gated_add_adaln_fwd(const void* x, const void* gate, const void* sub, const void* scale,
+                                         const void* shift, float eps, int64_t rows, int64_t hw, int64_t d,
+                                         void* x_new, void* y, float* mean, float* rstd, void* stream) {
+  ANIMA_REQUIRE(x && gate && sub && scale && shift && x_new && y && mean && rstd, ANIMA_E_ARG,
+                "gated_add_adaln_fwd: null pointer");
+  if (int rc = check_rows("gated_add_adaln_fwd", rows, hw, d, 4096)) return rc;
+  ANIMA_REQUIRE(aligned16(x) && aligned16(gate) && aligned16(sub) && aligned16(scale) && aligned16(shift) &&
+                    aligned16(x_new) && aligned16(y),
+                ANIMA_E_ALIGN, "gated_add_adaln_fwd: tensors must be 16-byte aligned");
+  if (rows == 0) return ANIMA_OK;
+  const auto* xp = static_cast<const __nv_bfloat16*>(x);
+  const auto* gp = static_cast<const __nv_bfloat16*>(gate);
+  const auto* up = static_cast<const __nv_bfloat16*>(sub);
+  const auto* sp = static_cast<const __nv_bfloat16*>(scale);
+  const auto* bp = static_cast<const __nv_bfloat16*>(shift);
+  auto* xn = static_cast<__nv_bfloat16*>(x_new);
+  auto* yp = static_cast<__nv_bfloat16*>(y);
+  const unsigned grid = static_cast<unsigned>(ceil_div(rows, kThreads / 32));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int di = static_cast<int>(d);
+#define ANIMA_LAUNCH_GFWD(N) \
+  adaln_fwd_kernel<N, true><<<grid, kThreads, 0, s>>>(xp, gp, up, sp, bp, eps, rows, hw, di, xn, yp, mean, rstd)
+  if (d <= 256) ANIMA_LAUNCH_GFWD(1);
+  else if (d <= 512) ANIMA_LAUNCH_GFWD(2);
+  else if (d <= 1024) ANIMA_LAUNCH_GFWD(4);
+  else if (d <= 2048) ANIMA_LAUNCH_GFWD(8);
+  else ANIMA_LAUNCH_GFWD(16);
+#undef ANIMA_LAUNCH_GFWD
+  ANIMA_CHECK_LAUNCH("gated_add_adaln_fwd");
   return ANIMA_OK;
 }
 

@@ -253,6 +253,22 @@ def adaln_fwd(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, eps: fl
     return y, mean, rstd
 
 
+def gated_add_adaln_fwd(x: torch.Tensor, gate: torch.Tensor, sub: torch.Tensor, scale: torch.Tensor,
+                        shift: torch.Tensor, eps: float, hw: int
+                        ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``x_new = x + gate * sub`` and ``y = AdaLN(x_new)`` in one pass -> (x_new, y, mean, rstd)."""
+    dev = _lib.require_cuda(x, gate, sub, scale, shift)
+    rows, d = x.shape
+    x_new, y = torch.empty_like(x), torch.empty_like(x)
+    mean = torch.empty(rows, dtype=torch.float32, device=dev)
+    rstd = torch.empty(rows, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(_lib.load().anima_gated_add_adaln_fwd(ptr(x), ptr(gate), ptr(sub), ptr(scale), ptr(shift), float(eps),
+                                                    rows, hw, d, ptr(x_new), ptr(y), ptr(mean), ptr(rstd),
+                                                    _lib.stream_ptr(dev)))
+    return x_new, y, mean, rstd
+
+
 def adaln_bwd(dy: torch.Tensor, x: torch.Tensor, scale: torch.Tensor, mean: torch.Tensor,
               rstd: torch.Tensor, hw: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     dev = _lib.require_cuda(dy, x, scale, mean, rstd)

@@ -223,6 +223,15 @@ int anima_gated_add_bwd(const void* dout, const void* y, const void* gate, int64
                         int64_t hw, int64_t d, void* dy, void* dgate, void* workspace,
                         int64_t workspace_bytes, void* stream);
 
+/* The gated residual of one sublayer and the AdaLN modulation of the next in one pass (no single
+ * reference counterpart: adaln_patch.py:42-153 calls FusedGatedAdd, then FusedAdaLN, on the same tensor):
+ *   x_new = x + gate * sub                      (as anima_gated_add_fwd)
+ *   y     = LayerNorm(x_new) * (1 + scale) + shift, mean / rstd of x_new   (as anima_adaln_fwd)
+ * Both outputs are bit-identical to the two separate calls. gate, scale, shift bf16 [rows/hw, d]. */
+int anima_gated_add_adaln_fwd(const void* x, const void* gate, const void* sub, const void* scale,
+                              const void* shift, float eps, int64_t rows, int64_t hw, int64_t d,
+                              void* x_new, void* y, float* mean, float* rstd, void* stream);
+
 /* ---------------------------------------------------------------- T-LoKr rank mix
  * ref: tlokr_kernels.py:15-82, :125-166 (rank_mix).
  * hidden, out bf16 [batch, n, 8, rank]; c bf16 [8,8]; mask bf16 [batch, rank] or NULL.

@@ -170,3 +170,28 @@ def test_full_size_config3_properties():
     out0 = ops.gated_add_fwd(x, torch.zeros_like(gate), y, HW)
     assert torch.equal(out0, x)
     _close(out1, x.float() + gate.float().repeat_interleave(HW, dim=0) * y.float())
+
+
+@pytest.mark.parametrize("B,H,W,D", [(2, 8, 8, 256), (1, 5, 7, 2048), (3, 4, 4, 4096)])
+def test_gated_add_adaln_one_pass_equals_the_two_ops(B, H, W, D):
+    """x_new and y of the one-pass op are bit-identical to FusedGatedAdd followed by FusedAdaLN, and so are
+    all five gradients (backward runs the same two backward kernels on the same operands)."""
+    from anima_trainer_sm120_b200.adaln_kernel import FusedAdaLN, FusedGatedAdd, FusedGatedAddAdaLN
+    g = torch.Generator().manual_seed(B * 100 + D)
+    mk = lambda *s, std=1.0: (torch.randn(*s, generator=g) * std).to(torch.bfloat16).cuda()
+    x, sub = mk(B, 1, H, W, D), mk(B, 1, H, W, D)
+    gate, scale, shift = mk(B, 1, 1, 1, D, std=0.3), mk(B, 1, 1, 1, D, std=0.3), mk(B, 1, 1, 1, D, std=0.3)
+    p1, p2 = mk(B, 1, H, W, D), mk(B, 1, H, W, D)
+    results = []
+    for fused in (False, True):
+        leaves = [t.clone().requires_grad_(True) for t in (x, gate, sub, scale, shift)]
+        xi, gi, ui, si, bi = leaves
+        if fused:
+            x_new, y = FusedGatedAddAdaLN.apply(xi, gi, ui, si, bi, 1e-6)
+        else:
+            x_new = FusedGatedAdd.apply(xi, gi, ui)
+            y = FusedAdaLN.apply(x_new, si, bi, 1e-6)
+        torch.autograd.backward([x_new, y], [p1, p2])
+        results.append([x_new.detach(), y.detach()] + [t.grad for t in leaves])
+    for ref, got in zip(*results):
+        assert torch.equal(ref, got)
