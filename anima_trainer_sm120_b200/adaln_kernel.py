@@ -86,7 +86,9 @@ def fused_gated_add(x: torch.Tensor, gate: torch.Tensor, y: torch.Tensor) -> tor
 class FusedGatedAddAdaLN(torch.autograd.Function):
     """``x_new = x + gate * sub`` followed by ``y = AdaLN(x_new; scale, shift)``: the residual update of one
     sublayer and the modulation of the next, from one read of x and sub. Returns ``(x_new, y)``, each
-    bit-identical to ``FusedGatedAdd`` then ``FusedAdaLN``; backward runs their two backward kernels."""
+    bit-identical to ``FusedGatedAdd`` then ``FusedAdaLN``; backward is one kernel too (the AdaLN input
+    gradient, its sum with the residual-stream gradient, and the gated-residual backward), again bit-identical
+    to the separate kernels."""
 
     @staticmethod
     def forward(ctx, x, gate, sub, scale, shift, eps):
@@ -108,13 +110,17 @@ class FusedGatedAddAdaLN(torch.autograd.Function):
         sub_flat, gate_flat, x_new, scale_flat, mean, rstd = ctx.saved_tensors
         B, T, H, W, D = ctx.shape
         xd, gd, ud, sd, bd = ctx.dtypes
-        dout = None if d_xnew is None else _flat(d_xnew, D)
-        dscale = dshift = None
-        if d_y is not None:
-            dx_ln, dscale, dshift = ops.adaln_bwd(_flat(d_y, D), x_new, scale_flat, mean, rstd, ctx.HW)
-            dout = dx_ln if dout is None else dout + dx_ln
+        if d_xnew is not None and d_y is not None:      # the usual case: one kernel for both backward ops
+            dout, dsub, dscale, dshift, dgate = ops.gated_add_adaln_bwd(
+                _flat(d_y, D), _flat(d_xnew, D), x_new, scale_flat, mean, rstd, sub_flat, gate_flat, ctx.HW)
+        else:
+            dout = None if d_xnew is None else _flat(d_xnew, D)
+            dscale = dshift = None
+            if d_y is not None:
+                dout, dscale, dshift = ops.adaln_bwd(_flat(d_y, D), x_new, scale_flat, mean, rstd, ctx.HW)
+            dsub, dgate = ops.gated_add_bwd(dout, sub_flat, gate_flat, ctx.HW)
+        if dscale is not None:
             dscale, dshift = dscale.view(ctx.mod_shape).to(sd), dshift.view(ctx.mod_shape).to(bd)
-        dsub, dgate = ops.gated_add_bwd(dout, sub_flat, gate_flat, ctx.HW)
         return (dout.view(B, T, H, W, D).to(xd), dgate.view(ctx.mod_shape).to(gd), dsub.view(B, T, H, W, D).to(ud),
                 dscale, dshift, None)
 

@@ -129,13 +129,22 @@ RowSplit make_split(int64_t bt, int64_t hw) {
   return {static_cast<int>(chunks), static_cast<int>(rpc)};
 }
 
-template <int NCH>
-__global__ void __launch_bounds__(kThreads)
+// GATED: x is the x_new = x_prev + gate * sub written by the one-pass forward. The gradient that reaches
+// x_new is d_res (through the residual stream) plus the LayerNorm gradient computed here; instead of writing
+// the latter, adding the two with a separate kernel and reading the sum back for the gated-residual backward,
+// the same thread forms dout = d_res + bf16(dx_ln), writes it (it is also the gradient of x_prev), and
+// continues with dsub = gate * dout and the dgate partial sums. Every rounding point is that of the three
+// separate kernels, so all outputs are bit-identical to them.
+template <int NCH, bool GATED>
+__global__ void __launch_bounds__(kThreads, NCH == 1 ? 2 : 1)
 adaln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                  const __nv_bfloat16* __restrict__ scale, const float* __restrict__ mean,
-                 const float* __restrict__ rstd, int64_t hw, int d, int rows_per_chunk,
-                 __nv_bfloat16* __restrict__ dx, float* __restrict__ partial) {
+                 const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ d_res,
+                 const __nv_bfloat16* __restrict__ sub, const __nv_bfloat16* __restrict__ gate, int64_t hw, int d,
+                 int rows_per_chunk, __nv_bfloat16* __restrict__ dx, __nv_bfloat16* __restrict__ dsub,
+                 float* __restrict__ partial) {
   constexpr int R = kRowsPerIter;
+  constexpr int NOUT = GATED ? 3 : 2;
   __shared__ float red[2][kThreads / 32][2 * R];
 
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -157,10 +166,25 @@ adaln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __re
       db[j][k] = 0.f;
     }
   }
+  float gt[GATED ? NCH : 1][8], dg[GATED ? NCH : 1][8];
+  if (GATED) {
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int col = (j * kThreads + t) * 8;
+      float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (col < d) unpack8(*reinterpret_cast<const uint4*>(gate + bt * d + col), s);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        gt[j][k] = s[k];
+        dg[j][k] = 0.f;
+      }
+    }
+  }
 
   int buf = 0;
   for (int64_t r0 = row_begin; r0 < row_end; r0 += R) {
     float g[R][NCH][8], xh[R][NCH][8];  // dy then dxhat; x then xhat
+    uint4 res_raw[GATED ? R : 1][NCH];
     float mu[R], rs[R];
 #pragma unroll
     for (int k = 0; k < R; ++k) {
@@ -175,6 +199,10 @@ adaln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __re
         if (row_ok && col < d) {
           a = ldg_stream16(dy + row * d + col);
           b = ldg_stream16(x + row * d + col);
+        }
+        if (GATED) {
+          res_raw[k][j] = make_uint4(0u, 0u, 0u, 0u);
+          if (row_ok && col < d) res_raw[k][j] = ldg_stream16(d_res + row * d + col);
         }
         unpack8(a, g[k][j]);
         unpack8(b, xh[k][j]);
@@ -227,7 +255,26 @@ adaln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __re
             float o[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) o[e] = rs[k] * (g[k][j][e] - c1 - xh[k][j][e] * c2);
-            stg_stream16(dx + row * d + col, pack8(o));
+            if (!GATED) {
+              stg_stream16(dx + row * d + col, pack8(o));
+            } else {
+              float ln[8], rf[8], df[8], yf[8];
+              const uint4 sub_raw = ldg_stream16(sub + row * d + col);   // read late: registers are scarce here
+              unpack8(pack8(o), ln);                     // the LayerNorm gradient as its own kernel would store it
+              unpack8(res_raw[k][j], rf);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) df[e] = rf[e] + ln[e];
+              const uint4 dout = pack8(df);              // bf16 sum, as the separate add would store it
+              stg_stream16(dx + row * d + col, dout);
+              unpack8(dout, df);
+              unpack8(sub_raw, yf);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                dg[j][e] += df[e] * yf[e];
+                o[e] = gt[j][e] * df[e];
+              }
+              stg_stream16(dsub + row * d + col, pack8(o));
+            }
           }
         }
       }
@@ -235,8 +282,8 @@ adaln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __re
     buf ^= 1;
   }
 
-  // partial[bt][chunk][0] = dscale sums, [1] = dshift sums; fp32 [d] each.
-  float* out = partial + ((bt * gridDim.x + blockIdx.x) * 2) * static_cast<int64_t>(d);
+  // partial[bt][chunk][0] = dscale sums, [1] = dshift sums, ([2] = dgate sums); fp32 [d] each.
+  float* out = partial + ((bt * gridDim.x + blockIdx.x) * NOUT) * static_cast<int64_t>(d);
 #pragma unroll
   for (int j = 0; j < NCH; ++j) {
     const int col = (j * kThreads + t) * 8;
@@ -245,6 +292,10 @@ adaln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __re
       *reinterpret_cast<float4*>(out + col + 4) = make_float4(ds[j][4], ds[j][5], ds[j][6], ds[j][7]);
       *reinterpret_cast<float4*>(out + d + col) = make_float4(db[j][0], db[j][1], db[j][2], db[j][3]);
       *reinterpret_cast<float4*>(out + d + col + 4) = make_float4(db[j][4], db[j][5], db[j][6], db[j][7]);
+      if (GATED) {
+        *reinterpret_cast<float4*>(out + 2 * d + col) = make_float4(dg[j][0], dg[j][1], dg[j][2], dg[j][3]);
+        *reinterpret_cast<float4*>(out + 2 * d + col + 4) = make_float4(dg[j][4], dg[j][5], dg[j][6], dg[j][7]);
+      }
     }
   }
 }
@@ -252,7 +303,7 @@ adaln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __re
 // out_k[bt][c] = bf16( sum over chunks (ascending) of partial[bt][chunk][k][c] ), k < nout.
 __global__ void finalize_partials_kernel(const float* __restrict__ partial, int64_t bt_count, int chunks,
                                          int nout, int d, __nv_bfloat16* __restrict__ out0,
-                                         __nv_bfloat16* __restrict__ out1) {
+                                         __nv_bfloat16* __restrict__ out1, __nv_bfloat16* __restrict__ out2 = nullptr) {
   const int64_t total = bt_count * nout * d;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -262,7 +313,7 @@ __global__ void finalize_partials_kernel(const float* __restrict__ partial, int6
     float acc = 0.f;
     for (int ch = 0; ch < chunks; ++ch)
       acc += partial[((bt * chunks + ch) * nout + k) * static_cast<int64_t>(d) + c];
-    (k == 0 ? out0 : out1)[bt * d + c] = __float2bfloat16_rn(acc);
+    (k == 0 ? out0 : k == 1 ? out1 : out2)[bt * d + c] = __float2bfloat16_rn(acc);
   }
 }
 
@@ -473,17 +524,69 @@ extern "C" int anima_adaln_bwd(const void* dy, const void* x, const void* scale,
   const auto* scp = static_cast<const __nv_bfloat16*>(scale);
   auto* dxp = static_cast<__nv_bfloat16*>(dx);
   if (d <= 2048)
-    adaln_bwd_kernel<1><<<grid, kThreads, 0, s>>>(dyp, xp, scp, mean, rstd, hw, (int)d,
-                                                  sp.rows_per_chunk, dxp, ws);
+    adaln_bwd_kernel<1, false><<<grid, kThreads, 0, s>>>(dyp, xp, scp, mean, rstd, nullptr, nullptr, nullptr, hw,
+                                                         (int)d, sp.rows_per_chunk, dxp, nullptr, ws);
   else
-    adaln_bwd_kernel<2><<<grid, kThreads, 0, s>>>(dyp, xp, scp, mean, rstd, hw, (int)d,
-                                                  sp.rows_per_chunk, dxp, ws);
+    adaln_bwd_kernel<2, false><<<grid, kThreads, 0, s>>>(dyp, xp, scp, mean, rstd, nullptr, nullptr, nullptr, hw,
+                                                         (int)d, sp.rows_per_chunk, dxp, nullptr, ws);
   ANIMA_CHECK_LAUNCH("adaln_bwd");
   const int64_t total = bt * 2 * d;
   finalize_partials_kernel<<<static_cast<unsigned>(std::min<int64_t>(ceil_div(total, 256), 1024)), 256, 0, s>>>(
       ws, bt, sp.chunks, 2, (int)d, static_cast<__nv_bfloat16*>(dscale),
       static_cast<__nv_bfloat16*>(dshift));
   ANIMA_CHECK_LAUNCH("adaln_bwd finalize");
+  return ANIMA_OK;
+}
+
+extern "C" int64_t anima_gated_add_adaln_bwd_workspace_bytes(int64_t rows, int64_t hw, int64_t d) {
+  if (rows < 0 || hw <= 0 || d <= 0 || rows % hw) return ANIMA_E_SHAPE;
+  const RowSplit sp = make_split(rows / hw, hw);
+  return (rows / hw) * sp.chunks * 3 * d * static_cast<int64_t>(sizeof(float));
+}
+
+extern "C" int anima_gated_add_adaln_bwd(const void* d_y, const void* d_xnew, const void* x_new, const void* scale,
+                                         const float* mean, const float* rstd, const void* sub, const void* gate,
+                                         int64_t rows, int64_t hw, int64_t d, void* dx, void* dsub, void* dscale,
+                                         void* dshift, void* dgate, void* workspace, int64_t workspace_bytes,
+                                         void* stream) {
+  ANIMA_REQUIRE(d_y && d_xnew && x_new && scale && mean && rstd && sub && gate && dx && dsub && dscale && dshift &&
+                    dgate,
+                ANIMA_E_ARG, "gated_add_adaln_bwd: null pointer");
+  if (int rc = check_rows("gated_add_adaln_bwd", rows, hw, d, 4096)) return rc;
+  ANIMA_REQUIRE(aligned16(d_y) && aligned16(d_xnew) && aligned16(x_new) && aligned16(scale) && aligned16(sub) &&
+                    aligned16(gate) && aligned16(dx) && aligned16(dsub),
+                ANIMA_E_ALIGN, "gated_add_adaln_bwd: tensors must be 16-byte aligned");
+  if (rows == 0) return ANIMA_OK;
+  const int64_t need = anima_gated_add_adaln_bwd_workspace_bytes(rows, hw, d);
+  ANIMA_REQUIRE(workspace && aligned16(workspace) && workspace_bytes >= need, ANIMA_E_WORKSPACE,
+                "gated_add_adaln_bwd: workspace of %lld bytes (16-byte aligned) required, got %lld", (long long)need,
+                (long long)workspace_bytes);
+  const int64_t bt = rows / hw;
+  ANIMA_REQUIRE(bt <= 65535, ANIMA_E_TOO_LARGE, "gated_add_adaln_bwd: rows/hw=%lld exceeds 65535", (long long)bt);
+  const RowSplit sp = make_split(bt, hw);
+  const dim3 grid(sp.chunks, static_cast<unsigned>(bt));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* ws = static_cast<float*>(workspace);
+  const auto* dyp = static_cast<const __nv_bfloat16*>(d_y);
+  const auto* drp = static_cast<const __nv_bfloat16*>(d_xnew);
+  const auto* xp = static_cast<const __nv_bfloat16*>(x_new);
+  const auto* scp = static_cast<const __nv_bfloat16*>(scale);
+  const auto* sbp = static_cast<const __nv_bfloat16*>(sub);
+  const auto* gp = static_cast<const __nv_bfloat16*>(gate);
+  auto* dxp = static_cast<__nv_bfloat16*>(dx);
+  auto* dsp = static_cast<__nv_bfloat16*>(dsub);
+  if (d <= 2048)
+    adaln_bwd_kernel<1, true><<<grid, kThreads, 0, s>>>(dyp, xp, scp, mean, rstd, drp, sbp, gp, hw, (int)d,
+                                                        sp.rows_per_chunk, dxp, dsp, ws);
+  else
+    adaln_bwd_kernel<2, true><<<grid, kThreads, 0, s>>>(dyp, xp, scp, mean, rstd, drp, sbp, gp, hw, (int)d,
+                                                        sp.rows_per_chunk, dxp, dsp, ws);
+  ANIMA_CHECK_LAUNCH("gated_add_adaln_bwd");
+  const int64_t total = bt * 3 * d;
+  finalize_partials_kernel<<<static_cast<unsigned>(std::min<int64_t>(ceil_div(total, 256), 1024)), 256, 0, s>>>(
+      ws, bt, sp.chunks, 3, (int)d, static_cast<__nv_bfloat16*>(dscale), static_cast<__nv_bfloat16*>(dshift),
+      static_cast<__nv_bfloat16*>(dgate));
+  ANIMA_CHECK_LAUNCH("gated_add_adaln_bwd finalize");
   return ANIMA_OK;
 }
 

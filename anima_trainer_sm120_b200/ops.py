@@ -269,6 +269,26 @@ def gated_add_adaln_fwd(x: torch.Tensor, gate: torch.Tensor, sub: torch.Tensor, 
     return x_new, y, mean, rstd
 
 
+def gated_add_adaln_bwd(d_y: torch.Tensor, d_xnew: torch.Tensor, x_new: torch.Tensor, scale: torch.Tensor,
+                        mean: torch.Tensor, rstd: torch.Tensor, sub: torch.Tensor, gate: torch.Tensor, hw: int):
+    """Backward of :func:`gated_add_adaln_fwd` in one pass -> (dx, dsub, dscale, dshift, dgate)."""
+    dev = _lib.require_cuda(d_y, d_xnew, x_new, scale, mean, rstd, sub, gate)
+    rows, d = x_new.shape
+    bt = rows // hw if hw else 0
+    dx, dsub = torch.empty_like(x_new), torch.empty_like(x_new)
+    dscale, dshift, dgate = (torch.empty((bt, d), dtype=BF16, device=dev) for _ in range(3))
+    if rows == 0:
+        return dx, dsub, dscale, dshift, dgate
+    lib = _lib.load()
+    nbytes = check(lib.anima_gated_add_adaln_bwd_workspace_bytes(rows, hw, d))
+    ws = _lib.workspace(nbytes, dev, "gated_adaln_bwd")
+    with torch.cuda.device(dev):
+        check(lib.anima_gated_add_adaln_bwd(ptr(d_y), ptr(d_xnew), ptr(x_new), ptr(scale), ptr(mean), ptr(rstd),
+                                            ptr(sub), ptr(gate), rows, hw, d, ptr(dx), ptr(dsub), ptr(dscale),
+                                            ptr(dshift), ptr(dgate), ptr(ws), ws.numel(), _lib.stream_ptr(dev)))
+    return dx, dsub, dscale, dshift, dgate
+
+
 def adaln_bwd(dy: torch.Tensor, x: torch.Tensor, scale: torch.Tensor, mean: torch.Tensor,
               rstd: torch.Tensor, hw: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     dev = _lib.require_cuda(dy, x, scale, mean, rstd)

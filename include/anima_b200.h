@@ -232,6 +232,18 @@ int anima_gated_add_adaln_fwd(const void* x, const void* gate, const void* sub, 
                               const void* shift, float eps, int64_t rows, int64_t hw, int64_t d,
                               void* x_new, void* y, float* mean, float* rstd, void* stream);
 
+/* Backward of the pair in one pass. d_y is the gradient of y, d_xnew the gradient reaching x_new through
+ * the residual stream. With dx_ln the AdaLN input gradient (as anima_adaln_bwd):
+ *   dx   = d_xnew + dx_ln        (gradient of x, bf16)        dsub  = gate * dx
+ *   dscale, dshift as anima_adaln_bwd;                        dgate as anima_gated_add_bwd (of dx and sub)
+ * All five outputs are bit-identical to anima_adaln_bwd, a bf16 add and anima_gated_add_bwd run in turn. */
+int64_t anima_gated_add_adaln_bwd_workspace_bytes(int64_t rows, int64_t hw, int64_t d);
+int anima_gated_add_adaln_bwd(const void* d_y, const void* d_xnew, const void* x_new, const void* scale,
+                              const float* mean, const float* rstd, const void* sub, const void* gate,
+                              int64_t rows, int64_t hw, int64_t d, void* dx, void* dsub, void* dscale,
+                              void* dshift, void* dgate, void* workspace, int64_t workspace_bytes,
+                              void* stream);
+
 /* ---------------------------------------------------------------- T-LoKr rank mix
  * ref: tlokr_kernels.py:15-82, :125-166 (rank_mix).
  * hidden, out bf16 [batch, n, 8, rank]; c bf16 [8,8]; mask bf16 [batch, rank] or NULL.
