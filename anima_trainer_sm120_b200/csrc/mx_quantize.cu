@@ -282,33 +282,27 @@ extern "C" int anima_mx_quantize(const void* x, int64_t rows, int64_t cols, int6
 
 namespace {
 
-// Fills the GELU tables of the current device on first use. The fill runs on the caller's stream; until it
-// has completed, calls on any stream are ordered after it with an event wait (no host synchronisation).
+// Fills the GELU tables of the current device on first use and waits for the fill (the one host
+// synchronisation this entry point ever makes, once per device): every later call, on any stream and inside
+// stream capture, then finds the tables complete without any event bookkeeping. The first call on a device
+// must therefore be made outside stream capture.
 int ensure_gelu_tables(cudaStream_t s) {
   constexpr int kMaxDevices = 64;
   static std::mutex mu;
-  static int state[kMaxDevices];            // 0 not started, 1 fill launched, 2 fill known complete
-  static cudaEvent_t filled[kMaxDevices];
+  static bool ready[kMaxDevices];
   int dev = 0;
   ANIMA_REQUIRE(cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices, ANIMA_E_CUDA,
                 "mx_quantize_gelu: cannot identify the current device");
   std::lock_guard<std::mutex> lock(mu);
-  if (state[dev] == 2) return ANIMA_OK;
-  if (state[dev] == 0) {
-    ANIMA_REQUIRE(cudaEventCreateWithFlags(&filled[dev], cudaEventDisableTiming) == cudaSuccess, ANIMA_E_CUDA,
-                  "mx_quantize_gelu: cannot create an event");
-    gelu_lut_init_kernel<<<ceil_div(kGeluLutSize, 256), 256, 0, s>>>();
-    ANIMA_CHECK_LAUNCH("mx_quantize_gelu table fill");
-    ANIMA_REQUIRE(cudaEventRecord(filled[dev], s) == cudaSuccess, ANIMA_E_CUDA, "mx_quantize_gelu: cannot record an event");
-    state[dev] = 1;
-    return ANIMA_OK;
-  }
-  if (cudaEventQuery(filled[dev]) == cudaSuccess) {
-    state[dev] = 2;
-    return ANIMA_OK;
-  }
-  ANIMA_REQUIRE(cudaStreamWaitEvent(s, filled[dev], 0) == cudaSuccess, ANIMA_E_CUDA,
-                "mx_quantize_gelu: cannot order the stream after the table fill");
+  if (ready[dev]) return ANIMA_OK;
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  ANIMA_REQUIRE(cudaStreamIsCapturing(s, &capturing) == cudaSuccess && capturing == cudaStreamCaptureStatusNone,
+                ANIMA_E_UNSUPPORTED, "mx_quantize_gelu: the first call on a device must be made outside stream capture");
+  gelu_lut_init_kernel<<<ceil_div(kGeluLutSize, 256), 256, 0, s>>>();
+  ANIMA_CHECK_LAUNCH("mx_quantize_gelu table fill");
+  const cudaError_t rc = cudaStreamSynchronize(s);
+  ANIMA_REQUIRE(rc == cudaSuccess, ANIMA_E_CUDA, "mx_quantize_gelu: table fill failed: %s", cudaGetErrorString(rc));
+  ready[dev] = true;
   return ANIMA_OK;
 }
 

@@ -173,6 +173,36 @@ class Shape:
         self.w2 = (torch.randn(n // FACTOR, k // FACTOR, generator=g) * 0.02).to(dev).requires_grad_(True)
 
 
+def train_steps_per_s(dev, world: int, steps: int = 6, warmup: int = 2) -> dict:
+    """Optimizer steps per second of the config-5 training step (CUDA events, max over ranks)."""
+    import torch.distributed as dist
+
+    from anima_trainer_sm120_b200.anima_dit import AnimaConfig
+    from anima_trainer_sm120_b200.train_step import StepConfig, Trainer
+
+    tr = Trainer(AnimaConfig(), StepConfig(precision="mxfp8", variant="lokr"), dev)
+    times = []
+    for i in range(warmup + steps):
+        lat, ctx, seed = tr.synthetic_batch(8, 128, 512, i)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        tr.step(lat, ctx, seed)
+        e1.record()
+        e1.synchronize()
+        if i >= warmup:
+            times.append(e0.elapsed_time(e1))
+    ms = torch.tensor([sum(times) / len(times)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    per_rank = 1000.0 / float(ms)
+    return {"metric": "anima_lokr_train_steps_per_s", "value": per_rank, "unit": "steps/s (batch 8 per GPU)",
+            "samples_per_s": per_rank * 8 * world, "n_gpus": world, "steps": steps, "warmup": warmup,
+            "config": {"model": "Anima-shaped stand-in DiT, 28 blocks, d=2048, 16x128 heads, MLP 8192 (random init)",
+                       "batch_per_gpu": 8, "latent_tokens": 4096, "text_tokens": 512, "adapters": "LoKr factor 8 dim 128",
+                       "gradient_checkpointing": True, "optimizer": "AdamW (stand-in)", "data": "synthetic"},
+            "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 2 ** 30}
+
+
 def run_gpu_arm(args) -> None:
     import torch.distributed as dist
 
@@ -315,6 +345,18 @@ def run_gpu_arm(args) -> None:
     ms_e2e = timed(True, args.steps, 1)
     _lib.check_status_word(dev)
 
+    # Second headline of the reference ("Anima LoKr train steps/s @1024^2 b8"): a few optimizer steps of the
+    # Anima-shaped stand-in (28 blocks, batch 8 per GPU, 4096 latent tokens, checkpointing on) through the same
+    # kernels, all ranks taking part. Reported as an extra object; the contract's value / e2e stay the GEMM metric.
+    h2d = sum(s.x_host.numel() * 2 + s.dy_host.numel() * 2 for s in shapes)
+    train = None
+    if not args.no_train_step:
+        ops.mx_gemm = real_gemm                      # no per-launch events inside the training step
+        for s in shapes:
+            s.__dict__.clear()
+        torch.cuda.empty_cache()
+        train = train_steps_per_s(dev, world)
+
     if rank == 0:
         peaks = {}
         pk = ROOT / "MEASURED_PEAKS.json"
@@ -325,7 +367,6 @@ def run_gpu_arm(args) -> None:
         achieved = gemm_fl / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
         ms_step = ms_total / args.steps
         fl = gemm_flops_per_step() * world
-        h2d = sum(s.x_host.numel() * 2 + s.dy_host.numel() * 2 for s in shapes)
         d2h = n_grad * 4 + len(shapes) * 4
         cpu = cpu_lokr_linear(seconds_budget=15.0, max_iters=20) if world == 1 else None
         line = {
@@ -349,6 +390,8 @@ def run_gpu_arm(args) -> None:
         }
         if cpu is not None:
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        if train is not None:
+            line["train_step"] = train
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -360,6 +403,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-train-step", action="store_true",
+                    help="skip the extra measurement of the full training step (the train_step object of the line)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
