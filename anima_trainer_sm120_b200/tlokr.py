@@ -332,18 +332,17 @@ def _structured_delta(module, x: torch.Tensor, *, fp8: bool, base: torch.Tensor 
     return torch.add(base, fn.apply(*args), alpha=alpha)
 
 
-def _mx_linear_fwd(x_row, lead_shape, W_mx, bias, w1, w2_a, w2_b, mask, alpha):
-    """``y = x W^T + bias + alpha * delta(x)`` from the row-wise MXFP8 operand of x ``[rows, K]``.
+def _mx_linear_fwd(x_row, gq, lead_shape, W_mx, bias, w1, w2_a, w2_b, mask, alpha):
+    """``y = x W^T + bias + alpha * delta(x)`` from the row-wise MXFP8 operand of x viewed as ``[rows, K]``
+    (``x_row``) and as the grouped ``[rows * uq, K / uq]`` (``gq``): the same code bytes under two scale tilings.
     Returns (y, small factor operands kept for backward)."""
     from .fp8_quant import _bias_bf16
     c = w1.to(BF16)
     uq = c.shape[1]
     vp, rank = w2_a.shape
-    rows, K = x_row.rows, x_row.k
     n_out = W_mx.row.rows
     aq, aq_col = _q(w2_a.detach(), col=True)      # A [vp, r]: row form for out, column form for dgrad
     bq, bq_col = _q(w2_b.detach(), col=True)      # B [r, vq]
-    gq = ops.mx_regroup(x_row, rows * uq, K // uq)            # same codes, scales re-tiled for the grouped view
     y = torch.empty(*lead_shape, n_out, dtype=BF16, device=x_row.codes.device)
     ops.mx_gemm(x_row, W_mx.row, bias=_bias_bf16(bias), out=y.view(-1, n_out))
     hidden = ops.mx_gemm(gq, bq).view(lead_shape[0], -1, uq, rank)
@@ -354,11 +353,25 @@ def _mx_linear_fwd(x_row, lead_shape, W_mx, bias, w1, w2_a, w2_b, mask, alpha):
     return y, (aq_col, bq, bq_col)
 
 
+def _input_operands(quantise, rows: int, K: int, uq: int, keep: bool, device):
+    """MXFP8 operands of a layer input for forward and backward. ``quantise(r, k, col)`` quantises the input viewed
+    as ``[r, k]``. With ``keep`` (a pass whose saved tensors backward will read) the grouped view is quantised in both
+    forms once, so that backward needs neither the bf16 input nor another pass over it; otherwise only the row form
+    is made and uninitialised buffers of the same shapes stand in for what a checkpoint drops anyway.
+    Returns (x_row [rows, K], gq [rows * uq, K / uq], gq_col [K / uq, rows * uq])."""
+    from .fp8_quant import _placeholder
+    if keep:
+        gq, gq_col = quantise(rows * uq, K // uq, True)
+        return ops.mx_regroup(gq, rows, K), gq, gq_col
+    x_row, _ = quantise(rows, K, False)
+    return x_row, ops.mx_regroup(x_row, rows * uq, K // uq), _placeholder(K // uq, rows * uq, device)
+
+
 def _mx_linear_bwd(quant_grad, quant_grouped, lead_shape, K, W_mx, w1, w2_a, w2_b, mask, alpha, factor_ops):
-    """Backward of :func:`_mx_linear_fwd`. ``quant_grad(rows, k)`` / ``quant_grouped(rows, k)`` return the
-    (row, column) MXFP8 operands of the incoming gradient / of the layer input viewed as ``[rows, k]``, so a
-    caller can fold an elementwise op (the MLP activation and its derivative) into those quantisations.
-    Returns (grad_x bf16 [*lead, K], grad_w1, grad_A, grad_B)."""
+    """Backward of :func:`_mx_linear_fwd`. ``quant_grad(rows, k)`` returns the (row, column) MXFP8 operands of the
+    incoming gradient viewed as ``[rows, k]``, so a caller can fold an elementwise op (the derivative of the MLP
+    activation) into that quantisation; ``quant_grouped(rows, k)`` returns the operands of the layer input in its
+    grouped view (saved by the forward pass). Returns (grad_x bf16 [*lead, K], grad_w1, grad_A, grad_B)."""
     aq_col, bq, bq_col = factor_ops
     c = w1.to(BF16)
     up, uq = c.shape
@@ -402,28 +415,41 @@ class _MXTLoKrLinear(torch.autograd.Function):
     * ``+ alpha * delta`` and, in backward, ``+ grad_x(delta)`` are added by the stores of the last GEMM of
       each chain into the buffer the base GEMM wrote: no separate add kernels, no autograd sum.
 
-    Only x and the small factors are saved; the rank-space intermediates are recomputed in backward, as in
-    the reference."""
+    What is saved for backward are the MXFP8 operands of x in its grouped view (both forms, made by one pass
+    over x in the forward that backward will use) and the small factors; the rank-space intermediates are
+    recomputed in backward, as in the reference."""
 
     @staticmethod
     def forward(ctx, x, W_mx, bias, w1, w2_a, w2_b, mask, alpha: float):
-        from .fp8_quant import quantize_activation
-        x_row, _ = quantize_activation(x, colwise=False)
-        y, factor_ops = _mx_linear_fwd(x_row, x.shape[:-1], W_mx, bias, w1, w2_a, w2_b, mask, alpha)
-        ctx.save_for_backward(x, w1, w2_a, w2_b, *(() if mask is None else (mask,)))
+        from .fp8_quant import _pack, in_first_pass, quantize_activation
+        K, uq = x.shape[-1], w1.shape[1]
+        rows = x.numel() // K
+        train = any(ctx.needs_input_grad[i] for i in (0, 3, 4, 5))
+        keep = train and not in_first_pass()
+
+        def quantise(r, k, col):
+            if not col and (r, k) == (rows, K):
+                return quantize_activation(x, colwise=False)        # shared with other consumers of x
+            return _q(x.reshape(r, k), col=col)
+
+        x_row, gq, gq_col = _input_operands(quantise, rows, K, uq, keep, x.device)
+        y, factor_ops = _mx_linear_fwd(x_row, gq, x.shape[:-1], W_mx, bias, w1, w2_a, w2_b, mask, alpha)
+        ctx.save_for_backward(w1, w2_a, w2_b, *_pack(gq), *_pack(gq_col), *(() if mask is None else (mask,)))
         ctx.has_mask, ctx.ops, ctx.W_mx = mask is not None, factor_ops, W_mx
-        ctx.alpha, ctx.bias_grad = float(alpha), bias is not None and bias.requires_grad
+        ctx.alpha, ctx.bias_grad, ctx.x_shape = float(alpha), bias is not None and bias.requires_grad, x.shape
         return y
 
     @staticmethod
     def backward(ctx, grad_output):
+        from .fp8_quant import _unpack
         saved = ctx.saved_tensors        # read once: activation checkpointing unpacks on access
-        x, w1, w2_a, w2_b = saved[:4]
-        mask = saved[4] if ctx.has_mask else None
+        w1, w2_a, w2_b = saved[:3]
+        gq, gq_col = _unpack(*saved[3:5]), _unpack(*saved[5:7])
+        mask = saved[7] if ctx.has_mask else None
         gy = _bf16c(grad_output)
         g_x, g_c, g_a, g_b = _mx_linear_bwd(
-            lambda r, k: _q(gy.view(r, k), col=True), lambda r, k: _q(x.reshape(r, k), col=True),
-            x.shape[:-1], x.shape[-1], ctx.W_mx, w1, w2_a, w2_b, mask, ctx.alpha, ctx.ops)
+            lambda r, k: _q(gy.view(r, k), col=True), lambda r, k: (gq, gq_col),
+            ctx.x_shape[:-1], ctx.x_shape[-1], ctx.W_mx, w1, w2_a, w2_b, mask, ctx.alpha, ctx.ops)
         g_bias = gy.reshape(-1, gy.shape[-1]).sum(dim=0) if ctx.bias_grad else None
         return g_x, None, g_bias, g_c, g_a, g_b, None, None
 
@@ -431,41 +457,57 @@ class _MXTLoKrLinear(torch.autograd.Function):
 class _MXTLoKrMLP(torch.autograd.Function):
     """``layer2(gelu(layer1(x)))`` with both layers quantised T-LoKr linears, as one node: the activation and
     its derivative are evaluated inside the quantiser (``ops.mx_quantize_gelu``), so neither ``gelu(h)`` nor
-    ``grad * gelu'(h)`` is ever written as a bf16 tensor. Saves x, the pre-activation h and the factors."""
+    ``grad * gelu'(h)`` is ever written as a bf16 tensor. Saves the pre-activation h, the grouped MXFP8 operands of
+    both layer inputs and the factors."""
 
     @staticmethod
     def forward(ctx, x, W1, b1, w1_1, a_1, b_1, mask1, alpha1: float, W2, b2, w1_2, a_2, b_2, mask2, alpha2: float):
-        from .fp8_quant import quantize_activation
-        x_row, _ = quantize_activation(x, colwise=False)
-        h, ops1 = _mx_linear_fwd(x_row, x.shape[:-1], W1, b1, w1_1, a_1, b_1, mask1, alpha1)
-        act_row, _ = ops.mx_quantize_gelu(h.view(-1, h.shape[-1]), rowwise=True)
-        y, ops2 = _mx_linear_fwd(act_row, x.shape[:-1], W2, b2, w1_2, a_2, b_2, mask2, alpha2)
+        from .fp8_quant import _pack, in_first_pass, quantize_activation
+        K, lead = x.shape[-1], x.shape[:-1]
+        rows = x.numel() // K
+        train = any(ctx.needs_input_grad[i] for i in (0, 3, 4, 5, 10, 11, 12))
+        keep = train and not in_first_pass()
+
+        def quantise_x(r, k, col):
+            if not col and (r, k) == (rows, K):
+                return quantize_activation(x, colwise=False)
+            return _q(x.reshape(r, k), col=col)
+
+        x_row, gq1, gq1_col = _input_operands(quantise_x, rows, K, w1_1.shape[1], keep, x.device)
+        h, ops1 = _mx_linear_fwd(x_row, gq1, lead, W1, b1, w1_1, a_1, b_1, mask1, alpha1)
+        hid = h.shape[-1]
+        act_row, gq2, gq2_col = _input_operands(
+            lambda r, k, col: ops.mx_quantize_gelu(h.view(r, k), rowwise=True, colwise=col),
+            rows, hid, w1_2.shape[1], keep, x.device)
+        y, ops2 = _mx_linear_fwd(act_row, gq2, lead, W2, b2, w1_2, a_2, b_2, mask2, alpha2)
         masks = tuple(m for m in (mask1, mask2) if m is not None)
-        ctx.save_for_backward(x, h, w1_1, a_1, b_1, w1_2, a_2, b_2, *masks)
+        ctx.save_for_backward(h, w1_1, a_1, b_1, w1_2, a_2, b_2, *_pack(gq1), *_pack(gq1_col), *_pack(gq2),
+                              *_pack(gq2_col), *masks)
         ctx.has_masks = (mask1 is not None, mask2 is not None)
         ctx.ops, ctx.W = (ops1, ops2), (W1, W2)
-        ctx.alphas = (float(alpha1), float(alpha2))
+        ctx.alphas, ctx.x_shape = (float(alpha1), float(alpha2)), x.shape
         return y
 
     @staticmethod
     def backward(ctx, grad_output):
+        from .fp8_quant import _unpack
         saved = ctx.saved_tensors
-        x, h, w1_1, a_1, b_1, w1_2, a_2, b_2 = saved[:8]
-        rest = list(saved[8:])
+        h, w1_1, a_1, b_1, w1_2, a_2, b_2 = saved[:7]
+        gq1, gq1_col, gq2, gq2_col = (_unpack(*saved[i:i + 2]) for i in (7, 9, 11, 13))
+        rest = list(saved[15:])
         mask1 = rest.pop(0) if ctx.has_masks[0] else None
         mask2 = rest.pop(0) if ctx.has_masks[1] else None
         gy = _bf16c(grad_output)
-        lead = x.shape[:-1]
-        # layer 2: its input is gelu(h), quantised straight from h
+        lead = ctx.x_shape[:-1]
+        # layer 2: its input gelu(h) was quantised straight from h by the forward pass
         g_act, g_c2, g_a2, g_b2 = _mx_linear_bwd(
-            lambda r, k: _q(gy.view(r, k), col=True),
-            lambda r, k: ops.mx_quantize_gelu(h.view(r, k), rowwise=True, colwise=True),
+            lambda r, k: _q(gy.view(r, k), col=True), lambda r, k: (gq2, gq2_col),
             lead, h.shape[-1], ctx.W[1], w1_2, a_2, b_2, mask2, ctx.alphas[1], ctx.ops[1])
         # layer 1: its incoming gradient is g_act * gelu'(h), formed inside the quantiser
         g_x, g_c1, g_a1, g_b1 = _mx_linear_bwd(
             lambda r, k: ops.mx_quantize_gelu(h.view(r, k), g_act.view(r, k), rowwise=True, colwise=True),
-            lambda r, k: _q(x.reshape(r, k), col=True),
-            lead, x.shape[-1], ctx.W[0], w1_1, a_1, b_1, mask1, ctx.alphas[0], ctx.ops[0])
+            lambda r, k: (gq1, gq1_col),
+            lead, ctx.x_shape[-1], ctx.W[0], w1_1, a_1, b_1, mask1, ctx.alphas[0], ctx.ops[0])
         return (g_x, None, None, g_c1, g_a1, g_b1, None, None,
                 None, None, g_c2, g_a2, g_b2, None, None)
 
