@@ -78,10 +78,12 @@ __global__ void gelu_lut_init_kernel() {
 
 struct GeluLoader {
   using Raw = uint4;
-  static constexpr bool kZeroSafe = true;   // gelu(0) = 0
+  static constexpr bool kZeroSafe = false;  // finish may store the activation at (row, col)
   static constexpr int kSmemBytes = kGeluLutSize * 2;
   const __nv_bfloat16* h;
   int64_t ld;
+  __nv_bfloat16* act_out;                    // optional: the bf16 activation itself, [rows, cols] contiguous
+  int64_t cols;
   const uint16_t* lut;                       // shared-memory copy, set by prepare()
   __device__ __forceinline__ void prepare(void* smem) {
     uint4* dst = static_cast<uint4*>(smem);
@@ -95,12 +97,13 @@ struct GeluLoader {
     if (idx >= 0) return lut[idx];
     return __bfloat16_as_ushort(__float2bfloat16_rn(gelu_eager_f(__uint_as_float(bits16 << 16))));
   }
-  __device__ __forceinline__ uint4 finish(const Raw& raw, int64_t, int64_t) const {
+  __device__ __forceinline__ uint4 finish(const Raw& raw, int64_t r, int64_t c) const {
     uint4 out;
     const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
     uint32_t* o = reinterpret_cast<uint32_t*>(&out);
 #pragma unroll
     for (int k = 0; k < 4; ++k) o[k] = one(w[k] & 0xffffu) | (one(w[k] >> 16) << 16);
+    if (act_out) stg_stream16(act_out + r * cols + c, out);
     return out;
   }
 };
@@ -113,6 +116,8 @@ struct GeluBwdLoader {
   const __nv_bfloat16* h;
   const __nv_bfloat16* grad_act;
   int64_t ld;
+  __nv_bfloat16* act_out;                    // optional: the bf16 gradient itself, [rows, cols] contiguous
+  int64_t cols;
   const float* lut;
   __device__ __forceinline__ void prepare(void* smem) {
     uint4* dst = static_cast<uint4*>(smem);
@@ -135,7 +140,9 @@ struct GeluBwdLoader {
       o[2 * k] = g[2 * k] * factor(w[k] & 0xffffu);
       o[2 * k + 1] = g[2 * k + 1] * factor(w[k] >> 16);
     }
-    return pack8(o);
+    const uint4 out = pack8(o);
+    if (act_out) stg_stream16(act_out + r * cols + c, out);
+    return out;
   }
 };
 
@@ -309,21 +316,23 @@ int ensure_gelu_tables(cudaStream_t s) {
 }  // namespace
 
 extern "C" int anima_mx_quantize_gelu(const void* h, const void* grad_act, int64_t rows, int64_t cols,
-                                      int64_t ld, uint8_t* codes_row, uint8_t* scales_row,
+                                      int64_t ld, void* act_bf16, uint8_t* codes_row, uint8_t* scales_row,
                                       uint8_t* codes_colT, uint8_t* scales_col, int scale_layout,
                                       void* stream) {
   if (int rc = check_quantize_args("mx_quantize_gelu", h, rows, cols, ld, codes_row, scales_row, codes_colT,
                                    scales_col, scale_layout))
     return rc;
-  ANIMA_REQUIRE(!grad_act || aligned16(grad_act), ANIMA_E_ALIGN, "mx_quantize_gelu: grad_act must be 16-byte aligned");
+  ANIMA_REQUIRE((!grad_act || aligned16(grad_act)) && (!act_bf16 || aligned16(act_bf16)), ANIMA_E_ALIGN,
+                "mx_quantize_gelu: grad_act and act_bf16 must be 16-byte aligned");
   if (rows == 0 || cols == 0) return ANIMA_OK;
   if (int rc = ensure_gelu_tables(static_cast<cudaStream_t>(stream))) return rc;
   if (grad_act) {
-    const GeluBwdLoader load{static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(grad_act), ld, nullptr};
+    const GeluBwdLoader load{static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(grad_act), ld,
+                             static_cast<__nv_bfloat16*>(act_bf16), cols, nullptr};
     return launch_quantize("mx_quantize_gelu", load, rows, cols, codes_row, scales_row, codes_colT, scales_col,
                            scale_layout, stream);
   }
-  const GeluLoader load{static_cast<const __nv_bfloat16*>(h), ld, nullptr};
+  const GeluLoader load{static_cast<const __nv_bfloat16*>(h), ld, static_cast<__nv_bfloat16*>(act_bf16), cols, nullptr};
   return launch_quantize("mx_quantize_gelu", load, rows, cols, codes_row, scales_row, codes_colT, scales_col,
                          scale_layout, stream);
 }

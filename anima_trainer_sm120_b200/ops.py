@@ -50,8 +50,8 @@ def _alloc_scales(rows: int, k: int, layout: int, device) -> torch.Tensor:
     return torch.empty(scales_bytes(rows, k, layout), dtype=torch.uint8, device=device)
 
 
-def _quantize_call(entry: str, x: torch.Tensor, extra: tuple, rowwise: bool, colwise: bool, layout: int
-                   ) -> tuple[MXOperand | None, MXOperand | None]:
+def _quantize_call(entry: str, x: torch.Tensor, extra: tuple, rowwise: bool, colwise: bool, layout: int,
+                   after_ld: tuple = ()) -> tuple[MXOperand | None, MXOperand | None]:
     dev = _lib.require_cuda(x)
     rows, cols = x.shape
     if rowwise and cols % 32:
@@ -69,7 +69,7 @@ def _quantize_call(entry: str, x: torch.Tensor, extra: tuple, rowwise: bool, col
         return row_op, col_op
     with torch.cuda.device(dev):
         check(getattr(_lib.load(), entry)(
-            ptr(x), *extra, rows, cols, x.stride(0) if rows > 1 else cols,
+            ptr(x), *extra, rows, cols, x.stride(0) if rows > 1 else cols, *after_ld,
             ptr(row_op.codes) if row_op else None, ptr(row_op.scales) if row_op else None,
             ptr(col_op.codes) if col_op else None, ptr(col_op.scales) if col_op else None,
             layout, _lib.stream_ptr(dev)))
@@ -93,10 +93,11 @@ def mx_quantize(
 
 def mx_quantize_gelu(
     h: torch.Tensor, grad_act: torch.Tensor | None = None, *, rowwise: bool = True, colwise: bool = False,
-    layout: int = SCALES_TILED,
+    layout: int = SCALES_TILED, act_out: torch.Tensor | None = None,
 ) -> tuple[MXOperand | None, MXOperand | None]:
     """MXFP8 forms of ``gelu(h)`` (``grad_act`` None) or of ``grad_act * gelu'(h)``, from one read of the bf16
-    pre-activation ``h [rows, cols]``; the activation / its gradient is never written as a bf16 tensor."""
+    pre-activation ``h [rows, cols]``; the activation / its gradient is not written as a bf16 tensor unless
+    ``act_out`` (bf16, contiguous, h's shape) is given to receive it."""
     _bf16_2d(h, "h")
     h = h.contiguous()
     if grad_act is not None:
@@ -105,7 +106,12 @@ def mx_quantize_gelu(
             raise ValueError(f"grad_act {tuple(grad_act.shape)} does not match h {tuple(h.shape)}")
         grad_act = grad_act.contiguous()
         _lib.require_cuda(h, grad_act)
-    return _quantize_call("anima_mx_quantize_gelu", h, (ptr(grad_act),), rowwise, colwise, layout)
+    if act_out is not None:
+        _lib.require_cuda(h, act_out)
+        if act_out.dtype != BF16 or act_out.shape != h.shape or not act_out.is_contiguous():
+            raise ValueError("act_out must be contiguous bfloat16 of h's shape")
+    return _quantize_call("anima_mx_quantize_gelu", h, (ptr(grad_act),), rowwise, colwise, layout,
+                          after_ld=(ptr(act_out),))
 
 
 def mx_dequantize(op: MXOperand) -> torch.Tensor:

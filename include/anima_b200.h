@@ -77,11 +77,12 @@ int anima_mx_quantize(const void* x_bf16, int64_t rows, int64_t cols, int64_t ld
  *   grad_act == NULL : quantises bf16(gelu(h)), exact erf form, bit-identical to an eager fp32-math bf16 GELU.
  *   grad_act != NULL : quantises bf16(grad_act * gelu'(h)), the gradient w.r.t. h; grad_act has h's
  *                      shape and leading dimension.
+ * act_bf16 (optional, [rows, cols] contiguous) also receives the bf16 tensor that is being quantised.
  * Outputs, scale layout and size rules are those of anima_mx_quantize. The first call on each device
  * fills two small lookup tables and waits for that fill (one host synchronisation, once per device);
  * make it outside stream capture. */
 int anima_mx_quantize_gelu(const void* h, const void* grad_act, int64_t rows, int64_t cols,
-                           int64_t ld, uint8_t* codes_row, uint8_t* scales_row,
+                           int64_t ld, void* act_bf16, uint8_t* codes_row, uint8_t* scales_row,
                            uint8_t* codes_colT, uint8_t* scales_col, int scale_layout,
                            void* stream);
 

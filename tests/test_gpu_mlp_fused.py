@@ -24,15 +24,21 @@ def test_quantize_gelu_is_bit_exact_for_every_finite_bf16_input():
     finite = bits[(bits & 0x7F80) != 0x7F80]                                  # 65280 patterns
     g = torch.Generator().manual_seed(0)
     h = finite[torch.randperm(finite.numel(), generator=g)].to(torch.int16).view(BF16).view(2040, 32).to(DEV)
-    row, _ = ops.mx_quantize_gelu(h, rowwise=True)
-    want, _ = ops.mx_quantize(F.gelu(h), rowwise=True)
+    act = torch.empty_like(h)
+    row, _ = ops.mx_quantize_gelu(h, rowwise=True, act_out=act)
+    eager = F.gelu(h)
+    assert torch.equal(act.view(torch.int16), eager.view(torch.int16))           # the bf16 activation itself
+    want, _ = ops.mx_quantize(eager, rowwise=True)
     _same(row, want)
-    dy = torch.randn(2040, 32, generator=g).to(BF16).to(DEV)
-    hr = h.clone().requires_grad_(True)
-    F.gelu(hr).backward(dy)
-    row, _ = ops.mx_quantize_gelu(h, dy, rowwise=True)
-    want, _ = ops.mx_quantize(hr.grad, rowwise=True)
-    _same(row, want)
+    for seed in (1, 2):                                                           # the gradient depends on dy too
+        dy = torch.randn(2040, 32, generator=torch.Generator().manual_seed(seed)).to(BF16).to(DEV)
+        hr = h.clone().requires_grad_(True)
+        F.gelu(hr).backward(dy)
+        grad = torch.empty_like(h)
+        row, _ = ops.mx_quantize_gelu(h, dy, rowwise=True, act_out=grad)
+        assert torch.equal(grad.view(torch.int16), hr.grad.view(torch.int16))
+        want, _ = ops.mx_quantize(hr.grad, rowwise=True)
+        _same(row, want)
 
 
 @pytest.mark.parametrize("rows,cols", [(256, 512), (96, 160), (1024, 8192)])
