@@ -73,6 +73,9 @@ def main() -> None:
         out.setdefault("peak_mem_gb", {})[arm] = torch.cuda.max_memory_allocated(dev) / 2 ** 30
         del tr
         torch.cuda.empty_cache()
+    if "bf16_fused" in out["losses"] and "mxfp8" in out["losses"]:
+        rel = [abs(b - m) / b for b, m in zip(out["losses"]["bf16_fused"], out["losses"]["mxfp8"])]
+        out["max_rel_diff_vs_bf16_fused"] = max(rel)
     if "bf16" in out["losses"] and "mxfp8" in out["losses"]:
         rel = [abs(b - m) / b for b, m in zip(out["losses"]["bf16"], out["losses"]["mxfp8"])]
         out["max_rel_diff"] = max(rel)

@@ -10,6 +10,8 @@ gradients are summed with ONE all-reduce of a flat fp32 buffer between backward 
 Two precision arms share everything but the kernels:
   ``bf16``   the reference's bf16 mode restated — eager LayerNorm / modulation / gated add, merged
              weight ``F.linear`` for the adapters (``lokr_patch`` bf16 path). Runs on CPU too.
+  ``bf16_fused``  bf16 linears with this package's AdaLN / gated-add / RMSNorm+RoPE kernels (the reference's bf16
+             mode keeps its fused glue kernels too): isolates the gain of the MXFP8 linears.
   ``mxfp8``  this package's kernels behind the same module patches: fused AdaLN + gated residual,
              fused q / k RMSNorm + RoPE, merged modulation MLPs, the LoKr MLP as one node
              with GELU quantised in its producer, MXFP8 frozen linears, fused MXFP8 LoKr linears (or T-LoKr).
@@ -40,7 +42,7 @@ def noisy_input_and_target(latents: torch.Tensor, gen: torch.Generator | None = 
 
 @dataclass
 class StepConfig:
-    precision: str = "mxfp8"          # "bf16" | "mxfp8"
+    precision: str = "mxfp8"          # "bf16" | "bf16_fused" | "mxfp8"
     variant: str = "lokr"             # "lokr" | "tlokr"
     preset: str = "anima-cross-mlp"
     lokr_dim: int = 128
@@ -56,8 +58,8 @@ class Trainer:
     """Builds model + adapters for one rank and runs optimizer steps on synthetic batches."""
 
     def __init__(self, model_cfg: AnimaConfig, cfg: StepConfig, device: torch.device):
-        if cfg.precision not in ("bf16", "mxfp8"):
-            raise ValueError(f"precision must be 'bf16' or 'mxfp8', got {cfg.precision!r}")
+        if cfg.precision not in ("bf16", "bf16_fused", "mxfp8"):
+            raise ValueError(f"precision must be 'bf16', 'bf16_fused' or 'mxfp8', got {cfg.precision!r}")
         self.cfg, self.model_cfg, self.device = cfg, model_cfg, device
         self.world = dist.get_world_size() if dist.is_initialized() else 1
         self.rank = dist.get_rank() if dist.is_initialized() else 0
@@ -88,6 +90,17 @@ class Trainer:
                 fp8_quant.quantize_tlokr_base_weights(self.network)
             else:
                 lokr_patch.enable_fp8(self.network)
+        elif cfg.precision == "bf16_fused":
+            # bf16 linears (cuBLAS, merged-weight F.linear for the adapters) with this package's AdaLN / gated-add
+            # and q/k RMSNorm+RoPE kernels: the reference's bf16 mode also runs its fused glue kernels, so this arm
+            # separates what the MXFP8 linears gain from what the glue kernels gain.
+            if device.type != "cuda":
+                raise RuntimeError("precision='bf16_fused' needs a CUDA device: the kernels have no CPU path")
+            adaln_merge.merge_adaln_modulation(self.dit)
+            adaln_patch.install(Block)
+            qk_norm_rope.install(Attention)
+            mlp_patch.uninstall(GPT2FeedForward)
+            lokr_patch.disable_fp8()
         else:
             adaln_patch.uninstall(Block)
             qk_norm_rope.uninstall(Attention)
