@@ -111,7 +111,7 @@ def _patched_forward(self, x: torch.Tensor) -> torch.Tensor:
     t1, t2 = _tlokr_adapter(self.layer1), _tlokr_adapter(self.layer2)
     if t1 is not None and t2 is not None and exact_gelu:
         from . import tlokr
-        p1 = tlokr.single_node_plan(t1, x)
+        p1 = tlokr.single_node_plan(t1, x) if tlokr.DELTA_PRECISION == "mxfp8" else None
         if p1 is not None:
             # layer 2 sees a tensor of layer 1's output shape; only shape, dtype and device enter its plan
             hidden = tlokr._ActSpec((*x.shape[:-1], t1.org_module[0].out_features), x.dtype, x.device)

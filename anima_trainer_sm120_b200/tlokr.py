@@ -537,13 +537,19 @@ def single_node_plan(module, x):
     return base_q, module.org_module[0].bias, module.lokr_w1, w2_a, w2_b, mask, module._tlokr_alpha
 
 
+# Precision of the structured delta when the base projection is quantised: "mxfp8" (every factor GEMM on the
+# MXFP8 tensor path, the reference's FP8 mode) or "bf16" (the HBM-bound factor chain stays in bf16 and skips its
+# quantisation passes; the base projection stays MXFP8).
+DELTA_PRECISION = "mxfp8"
+
+
 def forward(module, x: torch.Tensor) -> torch.Tensor:
     """T-LoKr forward called by ``lokr_patch``: frozen base projection (quantised once when
     ``fp8_quant.quantize_tlokr_base_weights`` ran) plus ``alpha`` times the structured delta."""
     org = module.org_module[0]
     base_q = getattr(module, "_tlokr_fp8_base_weight", None)
     quantised = base_q is not None and x.is_cuda and (x.numel() // x.shape[-1]) % 32 == 0
-    plan = single_node_plan(module, x)
+    plan = single_node_plan(module, x) if DELTA_PRECISION == "mxfp8" else None
     if plan is not None:
         return _MXTLoKrLinear.apply(x.contiguous(), *plan)
     if quantised:
@@ -551,4 +557,5 @@ def forward(module, x: torch.Tensor) -> torch.Tensor:
         base = fp8_frozen_linear(x, base_q, org.weight, org.bias)
     else:
         base = F.linear(x, org.weight, org.bias)
-    return _structured_delta(module, x, fp8=quantised, base=base, alpha=module._tlokr_alpha)
+    return _structured_delta(module, x, fp8=quantised and DELTA_PRECISION == "mxfp8", base=base,
+                             alpha=module._tlokr_alpha)
