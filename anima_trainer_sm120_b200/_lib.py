@@ -8,7 +8,7 @@ usable GPU, the call raises.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
 from pathlib import Path
 
 import torch

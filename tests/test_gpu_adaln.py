@@ -5,7 +5,6 @@ Cases follow tests/sanity_adaln_kernel.py:105-112 of the reference (shapes, seed
 scale / shift ~ 0.1 N(0,1))."""
 from __future__ import annotations
 
-import numpy as np
 import pytest
 import torch
 

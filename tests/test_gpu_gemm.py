@@ -12,7 +12,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import bf16_from_bits
+
 from oracle import mxfp8 as OQ
 
 pytestmark = pytest.mark.gpu
