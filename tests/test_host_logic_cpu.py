@@ -1,0 +1,137 @@
+"""Host-side logic that needs no GPU: the activation-quantisation memo, the checkpoint first-pass flag, the
+T-LoKr dispatch plan, and the fall-through of the MLP / q-k patches on CPU tensors."""
+from __future__ import annotations
+
+import gc
+
+import pytest
+import torch
+
+from anima_trainer_sm120_b200 import fp8_quant, mlp_patch, ops, qk_norm_rope, tlokr
+from anima_trainer_sm120_b200.anima_dit import Attention, GPT2FeedForward, tiny_config
+
+
+@pytest.fixture
+def fake_quantiser(monkeypatch):
+    """Replace the CUDA quantiser by a counter that returns distinguishable operands."""
+    calls = []
+
+    def fake(x2d, *, rowwise=True, colwise=False, layout=1):
+        calls.append((tuple(x2d.shape), rowwise, colwise))
+        row = ops.MXOperand(torch.zeros(1, dtype=torch.uint8), torch.tensor([len(calls)], dtype=torch.uint8), layout)
+        col = ops.MXOperand(torch.ones(1, dtype=torch.uint8), torch.tensor([len(calls)], dtype=torch.uint8), layout)
+        return row, (col if colwise else None)
+
+    monkeypatch.setattr(ops, "mx_quantize", fake)
+    fp8_quant.clear_activation_memo()
+    fp8_quant.act_memo_stats.update(hits=0, misses=0)
+    yield calls
+    fp8_quant.clear_activation_memo()
+
+
+def test_memo_hits_on_the_same_tensor_object_only(fake_quantiser):
+    x = torch.zeros(64, 32, dtype=torch.bfloat16)
+    r1, c1 = fp8_quant.quantize_activation(x, colwise=False)
+    r2, _ = fp8_quant.quantize_activation(x, colwise=False)
+    assert r2 is r1 and c1 is None and len(fake_quantiser) == 1
+    same_storage_other_object = x.view(64, 32)
+    fp8_quant.quantize_activation(same_storage_other_object, colwise=False)
+    assert len(fake_quantiser) == 2                                   # identity, not storage, is the key
+    assert fp8_quant.act_memo_stats == {"hits": 1, "misses": 2}
+
+
+def test_memo_misses_after_in_place_change_and_when_a_form_is_missing(fake_quantiser):
+    x = torch.zeros(64, 32, dtype=torch.bfloat16)
+    fp8_quant.quantize_activation(x, colwise=False)
+    _, col = fp8_quant.quantize_activation(x, colwise=True)             # entry has no column form: quantise again
+    assert col is not None and len(fake_quantiser) == 2
+    row, col2 = fp8_quant.quantize_activation(x, colwise=True)          # now both forms are there
+    assert col2 is col and len(fake_quantiser) == 2
+    row_only, none = fp8_quant.quantize_activation(x, colwise=False)    # a richer entry serves a poorer request
+    assert row_only is row and none is None and len(fake_quantiser) == 2
+    x.add_(1)
+    fp8_quant.quantize_activation(x, colwise=False)
+    assert len(fake_quantiser) == 3
+
+
+def test_memo_keeps_two_tensors_and_forgets_dead_ones(fake_quantiser):
+    a, b, c = (torch.zeros(32, 32, dtype=torch.bfloat16) for _ in range(3))
+    for t in (a, b):
+        fp8_quant.quantize_activation(t, colwise=False)
+    fp8_quant.quantize_activation(a, colwise=False)                     # a and b both still held
+    fp8_quant.quantize_activation(b, colwise=False)
+    assert len(fake_quantiser) == 2
+    fp8_quant.quantize_activation(c, colwise=False)                     # evicts the least recently used (a)
+    fp8_quant.quantize_activation(a, colwise=False)
+    assert len(fake_quantiser) == 4
+    del c
+    gc.collect()
+    fresh = torch.zeros(32, 32, dtype=torch.bfloat16)                   # may reuse c's address: must not hit
+    fp8_quant.quantize_activation(fresh, colwise=False)
+    assert len(fake_quantiser) == 5
+
+
+def test_first_pass_flag_nests_and_resets():
+    assert not fp8_quant.in_first_pass()
+    with fp8_quant.first_pass():
+        assert fp8_quant.in_first_pass()
+        with fp8_quant.first_pass():
+            assert fp8_quant.in_first_pass()
+        assert fp8_quant.in_first_pass()
+    assert not fp8_quant.in_first_pass()
+    with pytest.raises(RuntimeError):
+        with fp8_quant.first_pass():
+            raise RuntimeError("boom")
+    assert not fp8_quant.in_first_pass()
+
+
+def _tlokr_module(in_f=256, out_f=256, rank=16):
+    from anima_trainer_sm120_b200 import lokr_patch
+    from anima_trainer_sm120_b200.lokr import LokrModule, LokrNetwork
+    lin = torch.nn.Linear(in_f, out_f, bias=False).requires_grad_(False)
+    mod = LokrModule("t", lin, lora_dim=rank, alpha=rank, factor=8)
+    net = LokrNetwork([mod])
+    lokr_patch.install()
+    tlokr.convert_network(net, rank=rank, min_rank_ratio=0.5)
+    return mod
+
+
+def test_delta_plan_follows_the_timestep_context():
+    mod = _tlokr_module()
+    x = torch.zeros(2, 8, 256, dtype=torch.bfloat16)
+    try:
+        tlokr.set_timestep(torch.tensor([0.1, 0.9]))
+        fn, a, b, mask = tlokr._delta_plan(mod, x, fp8=False)
+        assert fn is tlokr._StructuredLoKr and a is mod.lokr_w2_a and tuple(mask.shape) == (2, 16)
+        spec = tlokr._ActSpec((2, 8, 256), torch.bfloat16, torch.device("cpu"))      # a shape stands in for a tensor
+        fn2, _, _, mask2 = tlokr._delta_plan(mod, spec, fp8=False)
+        assert fn2 is fn and torch.equal(mask2, mask)
+        tlokr.set_timestep(torch.tensor([1.0, 1.0]), uniform_timestep=1.0)           # 8 active ranks: sliced factors
+        fn, a, b, mask = tlokr._delta_plan(mod, x, fp8=True)
+        assert mask is None and a.shape[1] == 8 and b.shape[0] == 8
+        assert fn is tlokr._StructuredLoKr                                             # 8 % 32 != 0: no MXFP8 GEMM
+        with pytest.raises(RuntimeError):                                              # width not divisible by 8
+            tlokr._delta_plan(mod, torch.zeros(2, 8, 252, dtype=torch.bfloat16), fp8=False)
+    finally:
+        tlokr.clear_timestep()
+    assert tlokr.single_node_plan(mod, x) is None                                      # CPU tensor, no quantised base
+
+
+def test_patches_fall_through_on_cpu():
+    cfg = tiny_config(dim=256, heads=2, mlp_dim=512)
+    mlp = GPT2FeedForward(cfg)
+    x = torch.randn(2, 8, 256)
+    ref = mlp(x)
+    mlp_patch.install(GPT2FeedForward)
+    try:
+        assert torch.equal(mlp(x), ref)
+    finally:
+        mlp_patch.uninstall(GPT2FeedForward)
+    attn = Attention(cfg, None)
+    rope = torch.rand(8, 1, 1, 128)
+    ref = attn(x, None, None, rope_emb=rope)
+    qk_norm_rope.install(Attention)
+    try:
+        assert torch.equal(attn(x, None, None, rope_emb=rope), ref)
+    finally:
+        qk_norm_rope.uninstall(Attention)
