@@ -71,6 +71,10 @@ int anima_mx_quantize(const void* x_bf16, int64_t rows, int64_t cols, int64_t ld
                       uint8_t* codes_colT, uint8_t* scales_col,
                       int scale_layout, void* stream);
 
+/* 0, or 1 if a bounded wait inside the copy-engine-fed quantiser kernel ever gave up on the current device
+ * (its outputs are then undefined); negative on a CUDA error. Synchronises: for tests and debugging. */
+int anima_mx_quantize_status(void);
+
 /* Quantise an MLP activation without materialising it (no reference counterpart: the reference
  * runs GELU as a separate eager kernel between mlp.layer1 and mlp.layer2 and quantises its output).
  * h bf16 [rows, cols] is the pre-activation.

@@ -13,6 +13,16 @@ from oracle import mxfp8 as OQ
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=["1", "2"], ids=["plain-loads", "copy-engine-fed"])
+def quantiser_variant(request, monkeypatch):
+    """Every test of this module runs once per quantiser kernel (the library reads the variable on every call):
+    the tile kernel with plain loads, and the persistent kernel fed by bulk tensor copies."""
+    monkeypatch.setenv("ANIMA_MX_QUANTIZE_VARIANT", request.param)
+    yield request.param
+    from anima_trainer_sm120_b200 import _lib
+    assert _lib.load().anima_mx_quantize_status() == 0
+
+
 def _ops():
     from anima_trainer_sm120_b200 import ops
     return ops
