@@ -43,6 +43,16 @@ __device__ __forceinline__ uint32_t e4m3x2(float lo, float hi) {
       __nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
 }
 
+// packed bf16 pair helpers (operands and results as raw 32-bit words)
+__device__ __forceinline__ uint32_t bf16x2_max(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
 __device__ __forceinline__ int tiled_offset(int r, int j) {
   return (r & 31) * 16 + (r >> 5) * 4 + j;
 }
@@ -126,24 +136,26 @@ __global__ void __launch_bounds__(kThreads, COL ? 3 : 4) mx_quantize_kernel(cons
     const uint32_t* tile32 = reinterpret_cast<const uint32_t*>(tile);
     // one pass over the column pair: 32 packed bf16x2 words stay in registers for amax and conversion
     uint32_t cw[32];
-    float amax0 = 0.f, amax1 = 0.f;
+    // amax of both columns at once on the packed bf16 pairs (|x| by clearing the sign bits, then a packed
+    // max that ignores NaN like fmaxf); the scaling by 2^-e is a packed bf16 multiply, exact for a power of two
+    uint32_t am = 0u;
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       cw[i] = tile32[(32 * g + i) * 64 + cp];
-      amax0 = fmaxf(amax0, fabsf(__uint_as_float(cw[i] << 16)));
-      amax1 = fmaxf(amax1, fabsf(__uint_as_float(cw[i] & 0xffff0000u)));
+      am = bf16x2_max(am, cw[i] & 0x7fff7fffu);
     }
-    const int e0 = mx_exponent(fmaxf(amax0, kAmaxFloor));
-    const int e1 = mx_exponent(fmaxf(amax1, kAmaxFloor));
-    const float inv0 = mx_inv_scale(e0), inv1 = mx_inv_scale(e1);
+    const int e0 = mx_exponent(fmaxf(__uint_as_float(am << 16), kAmaxFloor));
+    const int e1 = mx_exponent(fmaxf(__uint_as_float(am & 0xffff0000u), kAmaxFloor));
+    const uint32_t inv2 = (__float_as_uint(mx_inv_scale(e0)) >> 16) | (__float_as_uint(mx_inv_scale(e1)) & 0xffff0000u);
     uint32_t w0[8], w1[8];
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
       float a[4], b[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        a[k] = __uint_as_float(cw[4 * q + k] << 16) * inv0;
-        b[k] = __uint_as_float(cw[4 * q + k] & 0xffff0000u) * inv1;
+        const uint32_t sc = bf16x2_mul(cw[4 * q + k], inv2);
+        a[k] = __uint_as_float(sc << 16);
+        b[k] = __uint_as_float(sc & 0xffff0000u);
       }
       w0[q] = e4m3x2(a[0], a[1]) | (e4m3x2(a[2], a[3]) << 16);
       w1[q] = e4m3x2(b[0], b[1]) | (e4m3x2(b[2], b[3]) << 16);

@@ -104,24 +104,26 @@ mx_quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantPar
       const int g = t >> 6;   // 32-row group within the tile
       const uint32_t* tile32 = reinterpret_cast<const uint32_t*>(tile);
       uint32_t cw[32];
-      float amax0 = 0.f, amax1 = 0.f;
+      // amax of both columns at once on the packed bf16 pairs (|x| by clearing the sign bits, then a packed
+      // max that ignores NaN like fmaxf); the scaling by 2^-e is a packed bf16 multiply, exact for a power of two
+      uint32_t am = 0u;
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         cw[i] = tile32[(32 * g + i) * 64 + cp];
-        amax0 = fmaxf(amax0, fabsf(__uint_as_float(cw[i] << 16)));
-        amax1 = fmaxf(amax1, fabsf(__uint_as_float(cw[i] & 0xffff0000u)));
+        am = bf16x2_max(am, cw[i] & 0x7fff7fffu);
       }
-      const int e0 = mx_exponent(fmaxf(amax0, kAmaxFloor));
-      const int e1 = mx_exponent(fmaxf(amax1, kAmaxFloor));
-      const float inv0 = mx_inv_scale(e0), inv1 = mx_inv_scale(e1);
+      const int e0 = mx_exponent(fmaxf(__uint_as_float(am << 16), kAmaxFloor));
+      const int e1 = mx_exponent(fmaxf(__uint_as_float(am & 0xffff0000u), kAmaxFloor));
+      const uint32_t inv2 = (__float_as_uint(mx_inv_scale(e0)) >> 16) | (__float_as_uint(mx_inv_scale(e1)) & 0xffff0000u);
       uint32_t w0[8], w1[8];
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         float a[4], b[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          a[k] = __uint_as_float(cw[4 * q + k] << 16) * inv0;
-          b[k] = __uint_as_float(cw[4 * q + k] & 0xffff0000u) * inv1;
+          const uint32_t sc = bf16x2_mul(cw[4 * q + k], inv2);
+          a[k] = __uint_as_float(sc << 16);
+          b[k] = __uint_as_float(sc & 0xffff0000u);
         }
         w0[q] = e4m3x2(a[0], a[1]) | (e4m3x2(a[2], a[3]) << 16);
         w1[q] = e4m3x2(b[0], b[1]) | (e4m3x2(b[2], b[3]) << 16);
