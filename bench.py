@@ -173,14 +173,15 @@ class Shape:
         self.w2 = (torch.randn(n // FACTOR, k // FACTOR, generator=g) * 0.02).to(dev).requires_grad_(True)
 
 
-def train_steps_per_s(dev, world: int, steps: int = 6, warmup: int = 2) -> dict:
+def train_steps_per_s(dev, world: int, steps: int = 6, warmup: int = 2, checkpointing: bool = True) -> dict:
     """Optimizer steps per second of the config-5 training step (CUDA events, max over ranks)."""
     import torch.distributed as dist
 
     from anima_trainer_sm120_b200.anima_dit import AnimaConfig
     from anima_trainer_sm120_b200.train_step import StepConfig, Trainer
 
-    tr = Trainer(AnimaConfig(), StepConfig(precision="mxfp8", variant="lokr"), dev)
+    torch.cuda.reset_peak_memory_stats(dev)
+    tr = Trainer(AnimaConfig(), StepConfig(precision="mxfp8", variant="lokr", gradient_checkpointing=checkpointing), dev)
     times = []
     for i in range(warmup + steps):
         lat, ctx, seed = tr.synthetic_batch(8, 128, 512, i)
@@ -199,7 +200,7 @@ def train_steps_per_s(dev, world: int, steps: int = 6, warmup: int = 2) -> dict:
             "samples_per_s": per_rank * 8 * world, "n_gpus": world, "steps": steps, "warmup": warmup,
             "config": {"model": "Anima-shaped stand-in DiT, 28 blocks, d=2048, 16x128 heads, MLP 8192 (random init)",
                        "batch_per_gpu": 8, "latent_tokens": 4096, "text_tokens": 512, "adapters": "LoKr factor 8 dim 128",
-                       "gradient_checkpointing": True, "optimizer": "AdamW (stand-in)", "data": "synthetic"},
+                       "gradient_checkpointing": checkpointing, "optimizer": "AdamW (stand-in)", "data": "synthetic"},
             "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 2 ** 30}
 
 
@@ -357,8 +358,14 @@ def run_gpu_arm(args) -> None:
         torch.cuda.empty_cache()
         try:
             train = train_steps_per_s(dev, world)
+            torch.cuda.empty_cache()
+            # the same step keeping all activations: 87 GB of the 180 GB, no recomputation (not the reference's
+            # configuration, which checkpoints every block; reported beside it, never instead of it)
+            train["without_checkpointing"] = {k: v for k, v in train_steps_per_s(dev, world, steps=4, checkpointing=False).items()
+                                              if k in ("value", "unit", "samples_per_s", "peak_mem_gb", "steps", "warmup")}
         except Exception as e:  # noqa: BLE001 - the extra object must never cost the contract line
-            train = {"metric": "anima_lokr_train_steps_per_s", "error": f"{type(e).__name__}: {str(e)[:300]}"}
+            train = {**(train or {}), "metric": "anima_lokr_train_steps_per_s",
+                     "error": f"{type(e).__name__}: {str(e)[:300]}"}
 
     if rank == 0:
         peaks = {}
