@@ -38,19 +38,28 @@ struct PlainLoader {
 
 // ---- GELU inside the quantiser ----------------------------------------------------------------
 // A bf16 GELU is a function of 16 input bits, and so is the factor gelu'(x) that multiplies the incoming
-// gradient. Both are tabulated for |x| in [2^-11, 8) (14 binades x 128 mantissas x 2 signs = 3584 entries):
-// the table is filled once per device by evaluating, with the CUDA math library, exactly the expressions an
-// eager bf16 GELU kernel evaluates in fp32,
+// gradient. Both are tabulated for |x| in [2^-11, 8) (14 binades x 128 mantissas per sign): the table is
+// filled once per device by evaluating, with the CUDA math library, exactly the expressions an eager bf16
+// GELU kernel evaluates in fp32,
 //     forward   x * 0.5 * (1 + erf(x / sqrt 2))                         stored rounded to bf16
 //     backward  0.5 * (1 + erf(x / sqrt 2)) + x * exp(-x^2 / 2) / sqrt(2 pi)   stored as fp32, then dy * factor
 // so the quantised codes equal those of quantising the materialised activation / gradient bit for bit,
 // while a lookup costs a fraction of the ~25 instructions of an erf evaluation (which made this loader
 // compute-bound). Inputs outside the table (|x| < 2^-11 or >= 8, NaN, inf: about 1 in 2500 for N(0,1) data)
-// take the same expressions directly. Each CTA copies the table it needs (7 or 14 KB) into shared memory.
+// take the same expressions directly. Each CTA copies the table it needs (7.5 or 15 KB) into shared memory.
+//
+// Index arithmetic runs on both bf16 values of a 32-bit word at once: clear the signs, clamp each half to the
+// table's range with packed 16-bit max / min (a half that moved is outside the table), subtract the range
+// start, and put the sign at bit 11 (negative inputs live at entries 2048..3839). One multiply-add turns the
+// pair of indices into a pair of shared-memory byte addresses (each below 64 KB, so they fit their halves).
 constexpr int kGeluLutMinExp = 127 - 11;   // biased exponent of 2^-11
 constexpr int kGeluLutMaxExp = 127 + 3;    // first binade NOT in the table: [8, 16)
-constexpr int kGeluLutHalf = (kGeluLutMaxExp - kGeluLutMinExp) * 128;
-constexpr int kGeluLutSize = 2 * kGeluLutHalf;
+constexpr int kGeluLutHalf = (kGeluLutMaxExp - kGeluLutMinExp) * 128;   // 1792 magnitudes per sign
+constexpr int kGeluLutNeg = 2048;                                       // first entry of the negative inputs
+constexpr int kGeluLutSize = kGeluLutNeg + kGeluLutHalf;                // entries 1792..2047 are unused
+constexpr uint32_t kGeluLo2 = static_cast<uint32_t>(kGeluLutMinExp << 7) * 0x10001u;
+constexpr uint32_t kGeluHi2 = static_cast<uint32_t>((kGeluLutMaxExp << 7) - 1) * 0x10001u;
+static_assert(kGeluLutHalf <= kGeluLutNeg && kGeluLutSize * 4 < 32768, "index pairs must fit 16 bits after scaling");
 __device__ __align__(16) uint16_t g_gelu_lut[kGeluLutSize];
 __device__ __align__(16) float g_gelu_grad_lut[kGeluLutSize];
 
@@ -62,20 +71,68 @@ __device__ __noinline__ float gelu_grad_factor_eager_f(float x) {
   const float pdf = expf(-0.5f * x * x) * 0.39894228040143267794f;   // M_2_SQRTPI * M_SQRT1_2 * 0.5
   return cdf + x * pdf;
 }
-// index of a bf16 bit pattern in the tables, or -1
+// index of a bf16 bit pattern in the tables, or -1 (scalar form: table fill and the rare path)
 __device__ __forceinline__ int gelu_lut_index(uint32_t bits16) {
   const int mag = static_cast<int>(bits16 & 0x7fffu) - (kGeluLutMinExp << 7);
   if (static_cast<unsigned>(mag) >= static_cast<unsigned>(kGeluLutHalf)) return -1;
-  return mag + ((bits16 & 0x8000u) ? kGeluLutHalf : 0);
+  return mag + ((bits16 & 0x8000u) ? kGeluLutNeg : 0);
+}
+__device__ __forceinline__ uint32_t u16x2_max(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t u16x2_min(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("min.u16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+// Both table indices of the bf16 pair `w`, one per 16-bit half; false when either value is outside the table.
+__device__ __forceinline__ bool gelu_lut_index2(uint32_t w, uint32_t& idx2) {
+  const uint32_t a = w & 0x7fff7fffu;
+  const uint32_t c = u16x2_min(u16x2_max(a, kGeluLo2), kGeluHi2);
+  idx2 = (c - kGeluLo2) | ((w >> 4) & 0x08000800u);   // no borrow between the halves: c >= range start in each
+  return c == a;
+}
+// The table is written once per CTA before a barrier; volatile keeps the loads behind that barrier.
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
 }
 
 __global__ void gelu_lut_init_kernel() {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= kGeluLutSize) return;
-  const uint32_t bits = static_cast<uint32_t>((i % kGeluLutHalf) + (kGeluLutMinExp << 7)) | (i >= kGeluLutHalf ? 0x8000u : 0u);
+  const int mag = i & (kGeluLutNeg - 1);
+  if (mag >= kGeluLutHalf) {   // the gap between the two signs
+    g_gelu_lut[i] = 0;
+    g_gelu_grad_lut[i] = 0.f;
+    return;
+  }
+  const uint32_t bits = static_cast<uint32_t>(mag + (kGeluLutMinExp << 7)) | (i >= kGeluLutNeg ? 0x8000u : 0u);
   const float x = __uint_as_float(bits << 16);
   g_gelu_lut[i] = __bfloat16_as_ushort(__float2bfloat16_rn(gelu_eager_f(x)));
   g_gelu_grad_lut[i] = gelu_grad_factor_eager_f(x);
+}
+
+template <class T>
+__device__ __forceinline__ uint32_t copy_lut(void* smem, const T* table) {
+  uint4* dst = static_cast<uint4*>(smem);
+  const uint4* src = reinterpret_cast<const uint4*>(table);
+  for (int i = threadIdx.x; i < kGeluLutSize * static_cast<int>(sizeof(T)) / 16; i += blockDim.x) dst[i] = src[i];
+  return smem_u32(smem) * 0x10001u;   // the table's shared-memory address in both halves
+}
+
+__device__ __noinline__ uint32_t gelu_pair_eager(uint32_t w) {   // a pair with a value outside the table
+  const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rn(gelu_eager_f(__uint_as_float(w << 16))));
+  const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rn(gelu_eager_f(__uint_as_float(w & 0xffff0000u))));
+  return lo | (hi << 16);
 }
 
 struct GeluLoader {
@@ -86,29 +143,26 @@ struct GeluLoader {
   int64_t ld;
   __nv_bfloat16* act_out;                    // optional: the bf16 activation itself, [rows, cols] contiguous
   int64_t cols;
-  const uint16_t* lut;                       // shared-memory copy, set by prepare()
-  __device__ __forceinline__ void prepare(void* smem) {
-    uint4* dst = static_cast<uint4*>(smem);
-    const uint4* src = reinterpret_cast<const uint4*>(g_gelu_lut);
-    for (int i = threadIdx.x; i < kGeluLutSize / 8; i += blockDim.x) dst[i] = src[i];
-    lut = static_cast<const uint16_t*>(smem);
-  }
+  uint32_t lut2;                             // shared-memory address of the table in both halves, set by prepare()
+  __device__ __forceinline__ void prepare(void* smem) { lut2 = copy_lut(smem, g_gelu_lut); }
   __device__ __forceinline__ Raw fetch(int64_t r, int64_t c) const { return ldg_stream16(h + r * ld + c); }
-  __device__ __forceinline__ uint32_t one(uint32_t bits16) const {
-    const int idx = gelu_lut_index(bits16);
-    if (idx >= 0) return lut[idx];
-    return __bfloat16_as_ushort(__float2bfloat16_rn(gelu_eager_f(__uint_as_float(bits16 << 16))));
+  __device__ __forceinline__ uint32_t pair(uint32_t w) const {
+    uint32_t idx2;
+    if (!gelu_lut_index2(w, idx2)) return gelu_pair_eager(w);
+    const uint32_t addr2 = idx2 * 2u + lut2;
+    return lds_u16(addr2 & 0xffffu) | (lds_u16(addr2 >> 16) << 16);
   }
   __device__ __forceinline__ uint4 finish(const Raw& raw, int64_t r, int64_t c) const {
-    uint4 out;
-    const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
-    uint32_t* o = reinterpret_cast<uint32_t*>(&out);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) o[k] = one(w[k] & 0xffffu) | (one(w[k] >> 16) << 16);
+    const uint4 out = make_uint4(pair(raw.x), pair(raw.y), pair(raw.z), pair(raw.w));
     if (act_out) stg_stream16(act_out + r * cols + c, out);
     return out;
   }
 };
+
+__device__ __noinline__ float2 gelu_grad_factor_pair_eager(uint32_t w) {
+  return make_float2(gelu_grad_factor_eager_f(__uint_as_float(w << 16)),
+                     gelu_grad_factor_eager_f(__uint_as_float(w & 0xffff0000u)));
+}
 
 // d(pre-activation) = grad_act * gelu'(h), rounded to bf16.
 struct GeluBwdLoader {
@@ -120,18 +174,14 @@ struct GeluBwdLoader {
   int64_t ld;
   __nv_bfloat16* act_out;                    // optional: the bf16 gradient itself, [rows, cols] contiguous
   int64_t cols;
-  const float* lut;
-  __device__ __forceinline__ void prepare(void* smem) {
-    uint4* dst = static_cast<uint4*>(smem);
-    const uint4* src = reinterpret_cast<const uint4*>(g_gelu_grad_lut);
-    for (int i = threadIdx.x; i < kGeluLutSize / 4; i += blockDim.x) dst[i] = src[i];
-    lut = static_cast<const float*>(smem);
-  }
+  uint32_t lut2;
+  __device__ __forceinline__ void prepare(void* smem) { lut2 = copy_lut(smem, g_gelu_grad_lut); }
   __device__ __forceinline__ Raw fetch(int64_t r, int64_t c) const { return ldg_stream16(h + r * ld + c); }
-  __device__ __forceinline__ float factor(uint32_t bits16) const {
-    const int idx = gelu_lut_index(bits16);
-    if (idx >= 0) return lut[idx];
-    return gelu_grad_factor_eager_f(__uint_as_float(bits16 << 16));
+  __device__ __forceinline__ float2 factors(uint32_t w) const {
+    uint32_t idx2;
+    if (!gelu_lut_index2(w, idx2)) return gelu_grad_factor_pair_eager(w);
+    const uint32_t addr2 = idx2 * 4u + lut2;
+    return make_float2(lds_f32(addr2 & 0xffffu), lds_f32(addr2 >> 16));
   }
   __device__ __forceinline__ uint4 finish(const Raw& raw, int64_t r, int64_t c) const {
     float g[8], o[8];
@@ -139,8 +189,9 @@ struct GeluBwdLoader {
     const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      o[2 * k] = g[2 * k] * factor(w[k] & 0xffffu);
-      o[2 * k + 1] = g[2 * k + 1] * factor(w[k] >> 16);
+      const float2 f = factors(w[k]);
+      o[2 * k] = g[2 * k] * f.x;
+      o[2 * k + 1] = g[2 * k + 1] * f.y;
     }
     const uint4 out = pack8(o);
     if (act_out) stg_stream16(act_out + r * cols + c, out);
@@ -401,11 +452,11 @@ extern "C" int anima_mx_quantize_gelu(const void* h, const void* grad_act, int64
   if (int rc = ensure_gelu_tables(static_cast<cudaStream_t>(stream))) return rc;
   if (grad_act) {
     const GeluBwdLoader load{static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(grad_act), ld,
-                             static_cast<__nv_bfloat16*>(act_bf16), cols, nullptr};
+                             static_cast<__nv_bfloat16*>(act_bf16), cols, 0u};
     return launch_quantize("mx_quantize_gelu", load, rows, cols, codes_row, scales_row, codes_colT, scales_col,
                            scale_layout, stream);
   }
-  const GeluLoader load{static_cast<const __nv_bfloat16*>(h), ld, static_cast<__nv_bfloat16*>(act_bf16), cols, nullptr};
+  const GeluLoader load{static_cast<const __nv_bfloat16*>(h), ld, static_cast<__nv_bfloat16*>(act_bf16), cols, 0u};
   return launch_quantize("mx_quantize_gelu", load, rows, cols, codes_row, scales_row, codes_colT, scales_col,
                          scale_layout, stream);
 }
