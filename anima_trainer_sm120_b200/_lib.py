@@ -56,6 +56,8 @@ PROTOTYPES: dict[str, tuple[object, list[object]]] = {
     "anima_adaln_bwd": (c_int, [P, P, P, P, P, I64, I64, I64, P, P, P, P, I64, P]),
     "anima_adaln_bwd_noalloc": (c_int, [P, P, P, P, P, I64, I64, I64, P, P, P, P]),
     "anima_gated_add_adaln_fwd": (c_int, [P, P, P, P, P, c_float, I64, I64, I64, P, P, P, P, P]),
+    "anima_adaln_fwd_quant": (c_int, [P, P, P, c_float, I64, I64, I64, P, P, P, P, P, c_int, P]),
+    "anima_gated_add_adaln_fwd_quant": (c_int, [P, P, P, P, P, c_float, I64, I64, I64, P, P, P, P, P, P, c_int, P]),
     "anima_gated_add_adaln_bwd_workspace_bytes": (I64, [I64, I64, I64]),
     "anima_gated_add_adaln_bwd": (c_int, [P, P, P, P, P, P, P, P, I64, I64, I64, P, P, P, P, P, P, I64, P]),
     "anima_gated_add_fwd": (c_int, [P, P, P, I64, I64, I64, P, P]),

@@ -16,6 +16,23 @@ from . import ops
 
 BF16 = torch.bfloat16
 
+# When set, the AdaLN forward kernels also write the row-wise MXFP8 operand of their output (same pass, one
+# more byte per element) and hand it to the quantised linears that consume the output through
+# ``fp8_quant.adopt_row_operand``; those linears then launch no quantiser for it (the column-wise operand a
+# trainable linear needs for its weight gradient is still made from y when asked for).
+_EMIT_ROW_OPERAND = False
+
+
+def emit_row_operand(enabled: bool = True) -> None:
+    """Switch the quantise-in-the-producer forward on or off (off by default: it only pays when the consumers
+    of the AdaLN output are this package's MXFP8 linears)."""
+    global _EMIT_ROW_OPERAND
+    _EMIT_ROW_OPERAND = bool(enabled)
+
+
+def _emits(x: torch.Tensor, rows: int, d: int) -> bool:
+    return _EMIT_ROW_OPERAND and x.dtype == BF16 and ops.can_emit_row_codes(rows, d)
+
 
 def _flat(t: torch.Tensor, d: int) -> torch.Tensor:
     t = t.contiguous().view(-1, d)
@@ -32,7 +49,12 @@ class FusedAdaLN(torch.autograd.Function):
         x_flat, scale_flat, shift_flat = _flat(x, D), _flat(scale, D), _flat(shift, D)
         N, M, HW = x_flat.shape[0], scale_flat.shape[0], H * W
         assert N == M * HW, f"shape mismatch: N={N}, M={M}, HW={HW}"
-        y, mean, rstd = ops.adaln_fwd(x_flat, scale_flat, shift_flat, eps, HW)
+        if _emits(x, N, D):
+            from . import fp8_quant
+            y, mean, rstd, y_row = ops.adaln_fwd(x_flat, scale_flat, shift_flat, eps, HW, quant=True)
+            fp8_quant.adopt_row_operand(y, y_row)
+        else:
+            y, mean, rstd = ops.adaln_fwd(x_flat, scale_flat, shift_flat, eps, HW)
         ctx.save_for_backward(x_flat, scale_flat, mean, rstd)
         ctx.x_shape, ctx.scale_shape, ctx.HW = (B, T, H, W, D), scale.shape, HW
         ctx.dtypes = (x.dtype, scale.dtype, shift.dtype)
@@ -99,7 +121,13 @@ class FusedGatedAddAdaLN(torch.autograd.Function):
         gate_flat, scale_flat, shift_flat = _flat(gate, D), _flat(scale, D), _flat(shift, D)
         HW = H * W
         assert x_flat.shape[0] == gate_flat.shape[0] * HW == scale_flat.shape[0] * HW, "modulation shape mismatch"
-        x_new, y, mean, rstd = ops.gated_add_adaln_fwd(x_flat, gate_flat, sub_flat, scale_flat, shift_flat, eps, HW)
+        if _emits(x, x_flat.shape[0], D):
+            from . import fp8_quant
+            x_new, y, mean, rstd, y_row = ops.gated_add_adaln_fwd(x_flat, gate_flat, sub_flat, scale_flat, shift_flat,
+                                                                  eps, HW, quant=True)
+            fp8_quant.adopt_row_operand(y, y_row)
+        else:
+            x_new, y, mean, rstd = ops.gated_add_adaln_fwd(x_flat, gate_flat, sub_flat, scale_flat, shift_flat, eps, HW)
         ctx.save_for_backward(sub_flat, gate_flat, x_new, scale_flat, mean, rstd)
         ctx.shape, ctx.mod_shape, ctx.HW = (B, T, H, W, D), gate.shape, HW
         ctx.dtypes = (x.dtype, gate.dtype, sub.dtype, scale.dtype, shift.dtype)

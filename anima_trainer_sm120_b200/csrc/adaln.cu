@@ -17,6 +17,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "mx_quantize_tile.cuh"
 
 namespace anima {
 namespace {
@@ -33,13 +34,25 @@ constexpr int kRowsPerIter = 4;
 // arithmetic as gated_add_fwd_kernel: one fp32 fma, rounded once to bf16), which is also written out; the
 // two kernels of "residual update, then modulation of the next sublayer" become one pass that reads x and sub
 // and writes x_new and y (8 B/elem instead of 6 + 4).
-template <int NCH, bool GATED>
+//
+// QUANT: the row-wise MXFP8 operand of y (e4m3 codes + one scale byte per 32 columns, the arithmetic of
+// mx_quantize on the bf16-rounded y) leaves the same pass: the four lanes that hold 32 consecutive columns
+// share their amax with two shuffles, and the scale bytes of 128 columns are gathered into one 32-bit store.
+// The linears that consume y then need no quantiser launch of their own (+1.03 B/elem written here against
+// 2 B read + 1.03 B written there); y itself may be left unwritten (y == nullptr).
+struct RowCodes {
+  uint8_t* codes;    // [rows, d]
+  uint8_t* scales;   // plain [rows, d/32] or tiled (128 x 4 chunks)
+  int tiled;
+};
+
+template <int NCH, bool GATED, bool QUANT>
 __global__ void __launch_bounds__(kThreads, NCH <= 8 ? 4 : 2)
 adaln_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate,
                  const __nv_bfloat16* __restrict__ sub, const __nv_bfloat16* __restrict__ scale,
                  const __nv_bfloat16* __restrict__ shift, float eps, int64_t rows, int64_t hw,
                  int d, __nv_bfloat16* __restrict__ x_new, __nv_bfloat16* __restrict__ y,
-                 float* __restrict__ mean_out, float* __restrict__ rstd_out) {
+                 float* __restrict__ mean_out, float* __restrict__ rstd_out, const RowCodes q) {
   const int lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -96,14 +109,43 @@ adaln_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
 #pragma unroll
   for (int i = 0; i < NCH; ++i) {
     const int col = (i * 32 + lane) * 8;
-    if (col < d) {
+    const bool ok = col < d;
+    uint4 out = make_uint4(0u, 0u, 0u, 0u);
+    if (ok) {
       float v[8], s[8], b[8], o[8];
       unpack8(raw[i], v);
       unpack8(*reinterpret_cast<const uint4*>(scale + bt * d + col), s);
       unpack8(*reinterpret_cast<const uint4*>(shift + bt * d + col), b);
 #pragma unroll
       for (int k = 0; k < 8; ++k) o[k] = (v[k] - mean) * rstd * (1.0f + s[k]) + b[k];
-      stg_stream16(y + row * d + col, pack8(o));
+      out = pack8(o);
+      if (!QUANT || y != nullptr) stg_stream16(y + row * d + col, out);
+    }
+    if (QUANT) {   // reached by all 32 lanes (d % 32 == 0: the four lanes of a block are in or out together)
+      float f[8];
+      unpack8(out, f);
+      float amax = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(f[k]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const int e = mxq::mx_exponent(fmaxf(amax, mxq::kAmaxFloor));
+      const float inv = mxq::mx_inv_scale(e);
+      uint2 codes;
+      codes.x = mxq::e4m3x2(f[0] * inv, f[1] * inv) | (mxq::e4m3x2(f[2] * inv, f[3] * inv) << 16);
+      codes.y = mxq::e4m3x2(f[4] * inv, f[5] * inv) | (mxq::e4m3x2(f[6] * inv, f[7] * inv) << 16);
+      if (ok) *reinterpret_cast<uint2*>(q.codes + row * d + col) = codes;
+      // scale bytes of blocks 8i + lane/4; lanes 0 and 16 collect the four bytes of their 128 columns
+      uint32_t sb = ok ? static_cast<uint32_t>(e + 127) : 0u;
+      sb |= __shfl_down_sync(0xffffffffu, sb, 4) << 8;
+      sb |= __shfl_down_sync(0xffffffffu, sb, 8) << 16;
+      if ((lane & 15) == 0 && ok) {
+        const int64_t kb4 = d / 128;   // d % 128 == 0 (checked by the host)
+        const int64_t c4 = i * 2 + (lane >> 4);
+        uint8_t* dst = q.tiled ? q.scales + ((row >> 7) * kb4 + c4) * 512 + mxq::tiled_offset(static_cast<int>(row & 127), 0)
+                               : q.scales + (row * kb4 + c4) * 4;
+        *reinterpret_cast<uint32_t*>(dst) = sb;
+      }
     }
   }
   if (lane == 0) {
@@ -434,6 +476,48 @@ int check_rows(const char* who, int64_t rows, int64_t hw, int64_t d, int64_t max
 
 using namespace anima;
 
+namespace {
+
+// One launcher for the four forward forms; the kernel is picked by the row length (256 columns per chunk).
+template <bool GATED, bool QUANT>
+void launch_adaln_fwd(const void* x, const void* gate, const void* sub, const void* scale, const void* shift, float eps,
+                      int64_t rows, int64_t hw, int64_t d, void* x_new, void* y, float* mean, float* rstd,
+                      const RowCodes& q, void* stream) {
+  const auto* xp = static_cast<const __nv_bfloat16*>(x);
+  const auto* gp = static_cast<const __nv_bfloat16*>(gate);
+  const auto* up = static_cast<const __nv_bfloat16*>(sub);
+  const auto* sp = static_cast<const __nv_bfloat16*>(scale);
+  const auto* bp = static_cast<const __nv_bfloat16*>(shift);
+  auto* xn = static_cast<__nv_bfloat16*>(x_new);
+  auto* yp = static_cast<__nv_bfloat16*>(y);
+  const unsigned grid = static_cast<unsigned>(ceil_div(rows, kThreads / 32));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int di = static_cast<int>(d);
+#define ANIMA_LAUNCH_FWD(N) \
+  adaln_fwd_kernel<N, GATED, QUANT><<<grid, kThreads, 0, s>>>(xp, gp, up, sp, bp, eps, rows, hw, di, xn, yp, mean, rstd, q)
+  if (d <= 256) ANIMA_LAUNCH_FWD(1);
+  else if (d <= 512) ANIMA_LAUNCH_FWD(2);
+  else if (d <= 1024) ANIMA_LAUNCH_FWD(4);
+  else if (d <= 2048) ANIMA_LAUNCH_FWD(8);
+  else ANIMA_LAUNCH_FWD(16);
+#undef ANIMA_LAUNCH_FWD
+}
+
+int check_row_codes(const char* who, int64_t rows, int64_t d, const uint8_t* codes_row, const uint8_t* scales_row,
+                    int scale_layout) {
+  ANIMA_REQUIRE(codes_row && scales_row, ANIMA_E_ARG, "%s: null code or scale buffer", who);
+  ANIMA_REQUIRE(scale_layout == ANIMA_SCALES_PLAIN || scale_layout == ANIMA_SCALES_TILED, ANIMA_E_ARG,
+                "%s: bad scale_layout %d", who, scale_layout);
+  ANIMA_REQUIRE(d % 128 == 0, ANIMA_E_SHAPE, "%s: d=%lld must be a multiple of 128", who, (long long)d);
+  ANIMA_REQUIRE(scale_layout == ANIMA_SCALES_PLAIN || rows % 128 == 0, ANIMA_E_SHAPE,
+                "%s: tiled scales need rows %% 128 == 0 (rows=%lld)", who, (long long)rows);
+  ANIMA_REQUIRE((reinterpret_cast<uintptr_t>(codes_row) & 7) == 0 && (reinterpret_cast<uintptr_t>(scales_row) & 3) == 0,
+                ANIMA_E_ALIGN, "%s: codes must be 8-byte and scales 4-byte aligned", who);
+  return ANIMA_OK;
+}
+
+}  // namespace
+
 extern "C" int anima_adaln_fwd(const void* x, const void* scale, const void* shift, float eps,
                                int64_t rows, int64_t hw, int64_t d, void* y, float* mean, float* rstd,
                                void* stream) {
@@ -442,22 +526,24 @@ extern "C" int anima_adaln_fwd(const void* x, const void* scale, const void* shi
   ANIMA_REQUIRE(aligned16(x) && aligned16(scale) && aligned16(shift) && aligned16(y), ANIMA_E_ALIGN,
                 "adaln_fwd: tensors must be 16-byte aligned");
   if (rows == 0) return ANIMA_OK;
-  const auto* xp = static_cast<const __nv_bfloat16*>(x);
-  const auto* sp = static_cast<const __nv_bfloat16*>(scale);
-  const auto* bp = static_cast<const __nv_bfloat16*>(shift);
-  auto* yp = static_cast<__nv_bfloat16*>(y);
-  const unsigned grid = static_cast<unsigned>(ceil_div(rows, kThreads / 32));
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int di = static_cast<int>(d);
-#define ANIMA_LAUNCH_FWD(N) \
-  adaln_fwd_kernel<N, false><<<grid, kThreads, 0, s>>>(xp, nullptr, nullptr, sp, bp, eps, rows, hw, di, nullptr, yp, mean, rstd)
-  if (d <= 256) ANIMA_LAUNCH_FWD(1);
-  else if (d <= 512) ANIMA_LAUNCH_FWD(2);
-  else if (d <= 1024) ANIMA_LAUNCH_FWD(4);
-  else if (d <= 2048) ANIMA_LAUNCH_FWD(8);
-  else ANIMA_LAUNCH_FWD(16);
-#undef ANIMA_LAUNCH_FWD
+  launch_adaln_fwd<false, false>(x, nullptr, nullptr, scale, shift, eps, rows, hw, d, nullptr, y, mean, rstd,
+                                 RowCodes{}, stream);
   ANIMA_CHECK_LAUNCH("adaln_fwd");
+  return ANIMA_OK;
+}
+
+extern "C" int anima_adaln_fwd_quant(const void* x, const void* scale, const void* shift, float eps, int64_t rows,
+                                     int64_t hw, int64_t d, void* y, float* mean, float* rstd, uint8_t* codes_row,
+                                     uint8_t* scales_row, int scale_layout, void* stream) {
+  ANIMA_REQUIRE(x && scale && shift && mean && rstd, ANIMA_E_ARG, "adaln_fwd_quant: null pointer");
+  if (int rc = check_rows("adaln_fwd_quant", rows, hw, d, 4096)) return rc;
+  if (int rc = check_row_codes("adaln_fwd_quant", rows, d, codes_row, scales_row, scale_layout)) return rc;
+  ANIMA_REQUIRE(aligned16(x) && aligned16(scale) && aligned16(shift) && aligned16(y), ANIMA_E_ALIGN,
+                "adaln_fwd_quant: tensors must be 16-byte aligned");
+  if (rows == 0) return ANIMA_OK;
+  launch_adaln_fwd<false, true>(x, nullptr, nullptr, scale, shift, eps, rows, hw, d, nullptr, y, mean, rstd,
+                                RowCodes{codes_row, scales_row, scale_layout == ANIMA_SCALES_TILED}, stream);
+  ANIMA_CHECK_LAUNCH("adaln_fwd_quant");
   return ANIMA_OK;
 }
 
@@ -471,25 +557,26 @@ extern "C" int anima_gated_add_adaln_fwd(const void* x, const void* gate, const 
                     aligned16(x_new) && aligned16(y),
                 ANIMA_E_ALIGN, "gated_add_adaln_fwd: tensors must be 16-byte aligned");
   if (rows == 0) return ANIMA_OK;
-  const auto* xp = static_cast<const __nv_bfloat16*>(x);
-  const auto* gp = static_cast<const __nv_bfloat16*>(gate);
-  const auto* up = static_cast<const __nv_bfloat16*>(sub);
-  const auto* sp = static_cast<const __nv_bfloat16*>(scale);
-  const auto* bp = static_cast<const __nv_bfloat16*>(shift);
-  auto* xn = static_cast<__nv_bfloat16*>(x_new);
-  auto* yp = static_cast<__nv_bfloat16*>(y);
-  const unsigned grid = static_cast<unsigned>(ceil_div(rows, kThreads / 32));
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int di = static_cast<int>(d);
-#define ANIMA_LAUNCH_GFWD(N) \
-  adaln_fwd_kernel<N, true><<<grid, kThreads, 0, s>>>(xp, gp, up, sp, bp, eps, rows, hw, di, xn, yp, mean, rstd)
-  if (d <= 256) ANIMA_LAUNCH_GFWD(1);
-  else if (d <= 512) ANIMA_LAUNCH_GFWD(2);
-  else if (d <= 1024) ANIMA_LAUNCH_GFWD(4);
-  else if (d <= 2048) ANIMA_LAUNCH_GFWD(8);
-  else ANIMA_LAUNCH_GFWD(16);
-#undef ANIMA_LAUNCH_GFWD
+  launch_adaln_fwd<true, false>(x, gate, sub, scale, shift, eps, rows, hw, d, x_new, y, mean, rstd, RowCodes{}, stream);
   ANIMA_CHECK_LAUNCH("gated_add_adaln_fwd");
+  return ANIMA_OK;
+}
+
+extern "C" int anima_gated_add_adaln_fwd_quant(const void* x, const void* gate, const void* sub, const void* scale,
+                                               const void* shift, float eps, int64_t rows, int64_t hw, int64_t d,
+                                               void* x_new, void* y, float* mean, float* rstd, uint8_t* codes_row,
+                                               uint8_t* scales_row, int scale_layout, void* stream) {
+  ANIMA_REQUIRE(x && gate && sub && scale && shift && x_new && mean && rstd, ANIMA_E_ARG,
+                "gated_add_adaln_fwd_quant: null pointer");
+  if (int rc = check_rows("gated_add_adaln_fwd_quant", rows, hw, d, 4096)) return rc;
+  if (int rc = check_row_codes("gated_add_adaln_fwd_quant", rows, d, codes_row, scales_row, scale_layout)) return rc;
+  ANIMA_REQUIRE(aligned16(x) && aligned16(gate) && aligned16(sub) && aligned16(scale) && aligned16(shift) &&
+                    aligned16(x_new) && aligned16(y),
+                ANIMA_E_ALIGN, "gated_add_adaln_fwd_quant: tensors must be 16-byte aligned");
+  if (rows == 0) return ANIMA_OK;
+  launch_adaln_fwd<true, true>(x, gate, sub, scale, shift, eps, rows, hw, d, x_new, y, mean, rstd,
+                               RowCodes{codes_row, scales_row, scale_layout == ANIMA_SCALES_TILED}, stream);
+  ANIMA_CHECK_LAUNCH("gated_add_adaln_fwd_quant");
   return ANIMA_OK;
 }
 

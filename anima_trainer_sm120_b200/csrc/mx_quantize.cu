@@ -29,7 +29,11 @@ struct PlainLoader {
   using Raw = uint4;
   static constexpr bool kZeroSafe = true;
   static constexpr int kSmemBytes = 0;
+  static constexpr bool kIdentity = true, kSecond = false;
+  static constexpr int kTmaCtasPerSm = 3;
   __device__ __forceinline__ void prepare(void*) {}
+  __device__ __forceinline__ uint4 second(int64_t, int64_t) const { return make_uint4(0u, 0u, 0u, 0u); }
+  __device__ __forceinline__ uint4 transform(const uint4& raw, const uint4&, int64_t, int64_t) const { return raw; }
   const __nv_bfloat16* x;
   int64_t ld;
   __device__ __forceinline__ Raw fetch(int64_t r, int64_t c) const { return ldg_stream16(x + r * ld + c); }
@@ -139,6 +143,12 @@ struct GeluLoader {
   using Raw = uint4;
   static constexpr bool kZeroSafe = false;  // finish may store the activation at (row, col)
   static constexpr int kSmemBytes = kGeluLutSize * 2;
+  static constexpr bool kIdentity = false, kSecond = false;
+  static constexpr int kTmaCtasPerSm = 3;     // 3 x (64 KB of stages + 7.5 KB table)
+  __device__ __forceinline__ uint4 second(int64_t, int64_t) const { return make_uint4(0u, 0u, 0u, 0u); }
+  __device__ __forceinline__ uint4 transform(const uint4& raw, const uint4&, int64_t r, int64_t c) const {
+    return finish(raw, r, c);
+  }
   const __nv_bfloat16* h;
   int64_t ld;
   __nv_bfloat16* act_out;                    // optional: the bf16 activation itself, [rows, cols] contiguous
@@ -169,6 +179,9 @@ struct GeluBwdLoader {
   using Raw = uint4;                           // the pre-activation; the incoming gradient is read in finish
   static constexpr bool kZeroSafe = false;     // (keeping both tiles in registers up front spills)
   static constexpr int kSmemBytes = kGeluLutSize * 4;
+  static constexpr bool kIdentity = false, kSecond = true;
+  static constexpr int kTmaCtasPerSm = 2;     // 2 x (64 KB of stages + 15 KB table)
+  __device__ __forceinline__ uint4 second(int64_t r, int64_t c) const { return ldg_stream16(grad_act + r * ld + c); }
   const __nv_bfloat16* h;
   const __nv_bfloat16* grad_act;
   int64_t ld;
@@ -184,8 +197,11 @@ struct GeluBwdLoader {
     return make_float2(lds_f32(addr2 & 0xffffu), lds_f32(addr2 >> 16));
   }
   __device__ __forceinline__ uint4 finish(const Raw& raw, int64_t r, int64_t c) const {
+    return transform(raw, ldg_stream16(grad_act + r * ld + c), r, c);
+  }
+  __device__ __forceinline__ uint4 transform(const uint4& raw, const uint4& grad, int64_t r, int64_t c) const {
     float g[8], o[8];
-    unpack8(ldg_stream16(grad_act + r * ld + c), g);
+    unpack8(grad, g);
     const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -350,35 +366,54 @@ bool make_x_map(CUtensorMap* map, const void* x, int64_t rows, int64_t cols, int
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <bool ROW, bool COL>
-int launch_tma(const CUtensorMap& map, const QuantParams& p, unsigned grid, cudaStream_t s) {
+template <bool ROW, bool COL, class Loader>
+int launch_tma(const CUtensorMap& map, const QuantParams& p, const Loader& load, unsigned grid, cudaStream_t s) {
+  constexpr int kBytes = kTmaSmemBytes + ((Loader::kSmemBytes + 127) & ~127);
   static std::once_flag once;
   static cudaError_t attr_rc = cudaSuccess;
   std::call_once(once, [] {
-    attr_rc = cudaFuncSetAttribute(mx_quantize_tma_kernel<ROW, COL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   kTmaSmemBytes);
+    attr_rc = cudaFuncSetAttribute(mx_quantize_tma_kernel<ROW, COL, Loader>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   kBytes);
   });
   ANIMA_REQUIRE(attr_rc == cudaSuccess, ANIMA_E_CUDA, "mx_quantize: cannot reserve %d bytes of shared memory: %s",
-                kTmaSmemBytes, cudaGetErrorString(attr_rc));
-  mx_quantize_tma_kernel<ROW, COL><<<grid, kThreads, kTmaSmemBytes, s>>>(map, p);
+                kBytes, cudaGetErrorString(attr_rc));
+  mx_quantize_tma_kernel<ROW, COL, Loader><<<grid, kThreads, kBytes, s>>>(map, p, load);
   ANIMA_CHECK_LAUNCH("mx_quantize (TMA)");
   return ANIMA_OK;
 }
 
 // Returns ANIMA_OK when launched, 1 when this path does not apply (the caller then takes the tile kernel).
-int try_quantize_tma(const void* x, int64_t rows, int64_t cols, int64_t ld, uint8_t* codes_row, uint8_t* scales_row,
-                     uint8_t* codes_colT, uint8_t* scales_col, int scale_layout, void* stream) {
+// x is the tensor the copy engine reads (the loader's first input).
+template <class Loader>
+int try_quantize_tma(const Loader& load, const void* x, int64_t rows, int64_t cols, int64_t ld, uint8_t* codes_row,
+                     uint8_t* scales_row, uint8_t* codes_colT, uint8_t* scales_col, int scale_layout, void* stream) {
   if (rows >= (1ll << 31) || cols >= (1ll << 31)) return 1;
   CUtensorMap map;
   if (!make_x_map(&map, x, rows, cols, ld)) return 1;
   const bool row = codes_row != nullptr, col = codes_colT != nullptr;
   QuantParams p{rows, cols, codes_row, scales_row, codes_colT, scales_col, scale_layout == ANIMA_SCALES_TILED};
   const int64_t tiles = ceil_div(rows, static_cast<int64_t>(kTile)) * ceil_div(cols, static_cast<int64_t>(kTile));
-  const unsigned grid = static_cast<unsigned>(std::min<int64_t>(tiles, 3LL * sm_count()));
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>(tiles, static_cast<int64_t>(Loader::kTmaCtasPerSm) * sm_count()));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (row && col) return launch_tma<true, true>(map, p, grid, s);
-  if (row) return launch_tma<true, false>(map, p, grid, s);
-  return launch_tma<false, true>(map, p, grid, s);
+  if (row && col) return launch_tma<true, true>(map, p, load, grid, s);
+  if (row) return launch_tma<true, false>(map, p, load, grid, s);
+  return launch_tma<false, true>(map, p, load, grid, s);
+}
+
+// The kernel choice shared by the quantising entry points: `tma_by_default` says whether the copy-engine-fed
+// kernel is the one to take when the variable does not force either.
+template <class Loader>
+int quantize_dispatch(const char* who, const Loader& load, bool tma_by_default, const void* x, int64_t rows, int64_t cols,
+                      int64_t ld, uint8_t* codes_row, uint8_t* scales_row, uint8_t* codes_colT, uint8_t* scales_col,
+                      int scale_layout, void* stream) {
+  const int variant = forced_quantize_variant();
+  if (variant == 2 || (variant == 0 && tma_by_default)) {
+    const int rc = try_quantize_tma(load, x, rows, cols, ld, codes_row, scales_row, codes_colT, scales_col,
+                                    scale_layout, stream);
+    if (rc <= 0) return rc;
+    ANIMA_REQUIRE(variant != 2, ANIMA_E_UNSUPPORTED, "%s: the TMA path is not available for this call", who);
+  }
+  return launch_quantize(who, load, rows, cols, codes_row, scales_row, codes_colT, scales_col, scale_layout, stream);
 }
 
 }  // namespace
@@ -399,16 +434,9 @@ extern "C" int anima_mx_quantize(const void* x, int64_t rows, int64_t cols, int6
   if (rows == 0 || cols == 0) return ANIMA_OK;
   // The copy-engine-fed kernel wins whenever the column form is made (row+column 4401 -> 4930 GB/s, column only
   // 4966 -> 5517); the row-only form has no shared-memory tile and runs as well or better on plain loads (5758 vs 5675).
-  const int variant = forced_quantize_variant();
-  if (variant == 2 || (variant == 0 && codes_colT != nullptr)) {
-    const int rc = try_quantize_tma(x, rows, cols, ld, codes_row, scales_row, codes_colT, scales_col, scale_layout,
-                                    stream);
-    if (rc <= 0) return rc;
-    ANIMA_REQUIRE(variant != 2, ANIMA_E_UNSUPPORTED, "mx_quantize: the TMA path is not available for this call");
-  }
   const PlainLoader load{static_cast<const __nv_bfloat16*>(x), ld};
-  return launch_quantize("mx_quantize", load, rows, cols, codes_row, scales_row, codes_colT, scales_col,
-                         scale_layout, stream);
+  return quantize_dispatch("mx_quantize", load, codes_colT != nullptr, x, rows, cols, ld, codes_row, scales_row,
+                           codes_colT, scales_col, scale_layout, stream);
 }
 
 namespace {
@@ -453,12 +481,12 @@ extern "C" int anima_mx_quantize_gelu(const void* h, const void* grad_act, int64
   if (grad_act) {
     const GeluBwdLoader load{static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(grad_act), ld,
                              static_cast<__nv_bfloat16*>(act_bf16), cols, 0u};
-    return launch_quantize("mx_quantize_gelu", load, rows, cols, codes_row, scales_row, codes_colT, scales_col,
-                           scale_layout, stream);
+    return quantize_dispatch("mx_quantize_gelu", load, true, h, rows, cols, ld, codes_row, scales_row, codes_colT,
+                             scales_col, scale_layout, stream);
   }
   const GeluLoader load{static_cast<const __nv_bfloat16*>(h), ld, static_cast<__nv_bfloat16*>(act_bf16), cols, 0u};
-  return launch_quantize("mx_quantize_gelu", load, rows, cols, codes_row, scales_row, codes_colT, scales_col,
-                         scale_layout, stream);
+  return quantize_dispatch("mx_quantize_gelu", load, true, h, rows, cols, ld, codes_row, scales_row, codes_colT,
+                           scales_col, scale_layout, stream);
 }
 
 extern "C" int anima_mx_dequantize(const uint8_t* codes, const uint8_t* scales, int64_t rows,

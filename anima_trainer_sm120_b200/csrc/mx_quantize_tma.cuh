@@ -1,5 +1,5 @@
-// TMA-fed, persistent form of the plain MXFP8 quantiser (same arithmetic and outputs as
-// mx_quantize_kernel<ROW, COL, PlainLoader>; see mx_quantize_tile.cuh for the tile algorithm).
+// TMA-fed, persistent form of the MXFP8 quantiser (same arithmetic and outputs as
+// mx_quantize_kernel<ROW, COL, Loader>; see mx_quantize_tile.cuh for the tile algorithm).
 //
 // A CTA walks tiles b, b + gridDim.x, ... of 128 x 128 bf16 values. Two shared-memory stages hold input
 // tiles; one elected thread keeps a `cp.async.bulk.tensor.2d` load of the NEXT tile in flight while the CTA
@@ -9,6 +9,18 @@
 // are zero-filled by the copy engine; stores are predicated as in the tile kernel.
 // Stage s, once its tile is in registers, doubles as the staging buffer for the transposed codes.
 // Every mbarrier wait is bounded; a CTA that gives up raises g_quantize_timeout and leaves the loop.
+//
+// A loader that computes (GELU, GELU gradient) transforms the raw tile in place during the row pass: each
+// thread rewrites the chunks it reads, a barrier follows, and the column pass sees the transformed tile. Its
+// lookup table is copied to shared memory once per CTA instead of once per tile, and a second input (the
+// incoming gradient) is fetched into registers one tile ahead, right after the row pass has consumed the
+// current one. What the loader adds to the interface of mx_quantize_tile.cuh:
+//   static constexpr bool kIdentity;        finish() returns the raw chunk (no rewrite, no extra barrier)
+//   static constexpr bool kSecond;          there is a second input
+//   static constexpr int kTmaCtasPerSm;     resident CTAs the kernel is compiled for (shared memory: two 32 KB
+//                                           stages plus the table)
+//   uint4 second(int64_t row, int64_t col) const;                         the second input's chunk (a load)
+//   uint4 transform(const uint4& raw, const uint4& second, int64_t row, int64_t col) const;
 #pragma once
 
 #include "mx_quantize_tile.cuh"
@@ -18,14 +30,15 @@ namespace anima {
 namespace mxq {
 
 constexpr int kTmaStageBytes = kTile * kTile * 2;                      // 32 KB
-constexpr int kTmaSmemBytes = 2 * kTmaStageBytes + 128 /*alignment*/;  // + static barriers and scale staging
+constexpr int kTmaSmemBytes = 2 * kTmaStageBytes + 128 /*alignment*/;  // + the loader's table; barriers and scale staging are static
 
 __device__ int g_quantize_timeout;  // sticky; read by anima_mx_quantize_status()
 
-template <bool ROW, bool COL>
-__global__ void __launch_bounds__(kThreads, 3)
-mx_quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantParams p) {
+template <bool ROW, bool COL, class Loader>
+__global__ void __launch_bounds__(kThreads, Loader::kTmaCtasPerSm)
+mx_quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantParams p, const Loader load_arg) {
   extern __shared__ uint8_t smem_raw[];
+  Loader load = load_arg;
   __shared__ __align__(8) uint64_t full_bar[2];
   __shared__ volatile int abort_flag;
   __shared__ __align__(16) uint8_t sc_row[ROW ? 512 : 16];
@@ -34,8 +47,13 @@ mx_quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantPar
   const int t = threadIdx.x;
   const int c16 = t & 15;  // 16-byte chunk (8 elements) within the tile row
   const int r0 = t >> 4;   // 0..15
-  const uint32_t stage0 = (smem_u32(smem_raw) + 127u) & ~127u;
-  uint8_t* const stage_ptr0 = smem_raw + (stage0 - smem_u32(smem_raw));
+  // dynamic shared memory: the loader's table first (its lookups pack two addresses into 16-bit halves, so it
+  // must sit low), then the two stages
+  constexpr uint32_t kTableBytes = (Loader::kSmemBytes + 127u) & ~127u;
+  const uint32_t table0 = (smem_u32(smem_raw) + 127u) & ~127u;
+  uint8_t* const table_ptr = smem_raw + (table0 - smem_u32(smem_raw));
+  const uint32_t stage0 = table0 + kTableBytes;
+  uint8_t* const stage_ptr0 = table_ptr + kTableBytes;
   const int64_t tiles_x = ceil_div(p.cols, static_cast<int64_t>(kTile));
   const int64_t n_tiles = tiles_x * ceil_div(p.rows, static_cast<int64_t>(kTile));
   const int64_t first = blockIdx.x, step = gridDim.x;
@@ -57,6 +75,22 @@ mx_quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantPar
     if (first < n_tiles) issue(first, 0);
     if (first + step < n_tiles) issue(first + step, 1);
   }
+  load.prepare(table_ptr);  // the table, once per CTA, behind the first copies
+  // chunk i of this thread: tile row r0 + 16 i, columns 8 c16 .. + 7
+  auto chunk_in_range = [&](int64_t tile_id, int i) {
+    const int64_t ty = tile_id / tiles_x, tx = tile_id - ty * tiles_x;
+    return tx * kTile + c16 * 8 < p.cols && ty * kTile + r0 + 16 * i < p.rows;
+  };
+  uint4 second[Loader::kSecond ? 8 : 1];
+  auto fetch_second = [&](int64_t tile_id) {
+    const int64_t ty = tile_id / tiles_x, tx = tile_id - ty * tiles_x;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      second[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (chunk_in_range(tile_id, i)) second[i] = load.second(ty * kTile + r0 + 16 * i, tx * kTile + c16 * 8);
+    }
+  };
+  if (Loader::kSecond && first < n_tiles) fetch_second(first);
   __syncthreads();
 
   int it = 0;
@@ -71,13 +105,20 @@ mx_quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantPar
 
     if (!mbar_wait(smem_u32(&full_bar[s]), (it >> 1) & 1u, &abort_flag)) break;
 
-    if (ROW) {
+    if (ROW || !Loader::kIdentity) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int r_in = r0 + 16 * i;
         const int64_t r = tile_r + r_in;
+        uint4 v = tile[r_in * 16 + c16];
+        if (!Loader::kIdentity) {
+          v = (col_ok && r < p.rows) ? load.transform(v, second[Loader::kSecond ? i : 0], r, col)
+                                     : make_uint4(0u, 0u, 0u, 0u);
+          if (COL) tile_w[r_in * 16 + c16] = v;
+        }
+        if (!ROW) continue;
         float f[8];
-        unpack8(tile[r_in * 16 + c16], f);
+        unpack8(v, f);
         float amax = 0.f;
 #pragma unroll
         for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(f[k]));
@@ -99,7 +140,10 @@ mx_quantize_tma_kernel(const __grid_constant__ CUtensorMap map_x, const QuantPar
       }
     }
 
+    if (Loader::kSecond && tile_id + step < n_tiles) fetch_second(tile_id + step);  // lands under the column pass
+
     if (COL) {
+      if (!Loader::kIdentity) __syncthreads();  // the transformed tile is complete
       const int cp = t & 63;  // column pair
       const int g = t >> 6;   // 32-row group within the tile
       const uint32_t* tile32 = reinterpret_cast<const uint32_t*>(tile);

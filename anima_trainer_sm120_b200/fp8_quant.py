@@ -60,30 +60,68 @@ def _flat2d(x: torch.Tensor) -> torch.Tensor:
 
 # Activation quantisation shared between consumers of one tensor (q / k / v projections read the same
 # AdaLN output; the reference measured this sharing at 5.339 -> 5.085 ms per block,
-# docs/claude/sm120-optimization-audit-2026-08.md:116-119). Keyed on the identity of the tensor object
-# handed to the linear (weak reference, so a freed tensor can never alias a new one at the same
-# address) and on its in-place version counter; two most recent tensors are kept.
-_ACT_MEMO: list[tuple[weakref.ref, int, ops.MXOperand, ops.MXOperand | None]] = []
+# docs/claude/sm120-optimization-audit-2026-08.md:116-119), and between a producer that already made the
+# operand (the AdaLN forward kernels can emit the row-wise codes of their output) and its consumers.
+# An entry is keyed on the tensor whose storage holds the values (the base of a view; weak reference, so a
+# freed tensor can never alias a new one at the same address), the extent viewed (address, element count,
+# row length) and the in-place version counter: a contiguous reshape of the producer's output still hits.
+# The two most recent tensors are kept.
+class _MemoEntry:
+    __slots__ = ("base", "addr", "numel", "k", "version", "row", "col")
+
+    def __init__(self, x: torch.Tensor, row: ops.MXOperand, col: ops.MXOperand | None):
+        self.base = weakref.ref(_storage_owner(x))
+        self.addr, self.numel, self.k, self.version = x.data_ptr(), x.numel(), x.shape[-1], x._version
+        self.row, self.col = row, col
+
+    def holds(self, x: torch.Tensor) -> bool:
+        return (self.base() is _storage_owner(x) and self.addr == x.data_ptr() and self.numel == x.numel()
+                and self.k == x.shape[-1] and self.version == x._version)
+
+
+def _storage_owner(x: torch.Tensor) -> torch.Tensor:
+    # only a contiguous bf16 view reads its base's bytes in the order the operand was made from
+    if x._base is not None and x.is_contiguous() and x.dtype == BF16:
+        return x._base
+    return x
+
+
+_ACT_MEMO: list[_MemoEntry] = []
 _ACT_MEMO_SLOTS = 2
-act_memo_stats = {"hits": 0, "misses": 0}
+act_memo_stats = {"hits": 0, "misses": 0, "adopted": 0}
 
 
 def clear_activation_memo() -> None:
     _ACT_MEMO.clear()
 
 
+def _memo_insert(entry: _MemoEntry) -> None:
+    _ACT_MEMO[:] = [e for e in _ACT_MEMO if e.base() is not None and e.base() is not entry.base()][:_ACT_MEMO_SLOTS - 1]
+    _ACT_MEMO.insert(0, entry)
+
+
+def adopt_row_operand(x: torch.Tensor, row: ops.MXOperand) -> None:
+    """Register ``row`` as the row-wise MXFP8 operand of the contiguous bf16 tensor ``x`` (made by x's producer),
+    so the linears that consume x, or a contiguous reshape of it, skip their own quantiser launch."""
+    if x.dtype != BF16 or not x.is_contiguous() or row.codes.shape[1] != x.shape[-1]:
+        raise ValueError("adopt_row_operand: x must be contiguous bfloat16 with the operand's row length")
+    act_memo_stats["adopted"] += 1
+    _memo_insert(_MemoEntry(x, row, None))
+
+
 def quantize_activation(x: torch.Tensor, *, colwise: bool) -> tuple[ops.MXOperand, ops.MXOperand | None]:
-    """Row-wise (and, if asked, column-wise) MXFP8 operands of ``x`` flattened to 2-D, memoised per tensor object."""
-    for i, (ref, ver, row, col) in enumerate(_ACT_MEMO):
-        if ref() is x and ver == x._version and (col is not None or not colwise):
+    """Row-wise (and, if asked, column-wise) MXFP8 operands of ``x`` flattened to 2-D, memoised per tensor."""
+    for i, e in enumerate(_ACT_MEMO):
+        if e.holds(x):
             if i:
                 _ACT_MEMO.insert(0, _ACT_MEMO.pop(i))
             act_memo_stats["hits"] += 1
-            return row, (col if colwise else None)
+            if colwise and e.col is None:     # the row-wise form is there already: add the other one
+                e.col = ops.mx_quantize(_flat2d(x), rowwise=False, colwise=True)[1]
+            return e.row, (e.col if colwise else None)
     act_memo_stats["misses"] += 1
     row, col = ops.mx_quantize(_flat2d(x), rowwise=True, colwise=colwise)
-    _ACT_MEMO[:] = [e for e in _ACT_MEMO if e[0]() is not None and e[0]() is not x][:_ACT_MEMO_SLOTS - 1]
-    _ACT_MEMO.insert(0, (weakref.ref(x), x._version, row, col))
+    _memo_insert(_MemoEntry(x, row, col))
     return row, col
 
 

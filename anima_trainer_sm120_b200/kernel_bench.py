@@ -146,11 +146,15 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
         sc, sh, ga = _acts(BT, D, 0.1), _acts(BT, D, 0.1), _acts(BT, D, 0.1)
         _, mean, rstd = ops.adaln_fwd(xa, sc, sh, 1e-6, HW)
         hbm("adaln_fwd", [BT, HW, D], M * D * 4 + M * 8, lambda: ops.adaln_fwd(xa, sc, sh, 1e-6, HW))
+        hbm("adaln_fwd + row-wise MXFP8 operand of y", [BT, HW, D], int(M * D * 5.03125) + M * 8,
+            lambda: ops.adaln_fwd(xa, sc, sh, 1e-6, HW, quant=True))
         hbm("adaln_bwd (dx+dscale+dshift)", [BT, HW, D], M * D * 6 + M * 8, lambda: ops.adaln_bwd(dy, xa, sc, mean, rstd, HW))
         hbm("gated_add_fwd", [BT, HW, D], M * D * 6, lambda: ops.gated_add_fwd(xa, ga, y2, HW))
         hbm("gated_add_bwd (dy+dgate)", [BT, HW, D], M * D * 6, lambda: ops.gated_add_bwd(dy, y2, ga, HW))
         hbm("gated_add + adaln fwd (one pass)", [BT, HW, D], M * D * 8 + M * 8,
             lambda: ops.gated_add_adaln_fwd(xa, ga, y2, sc, sh, 1e-6, HW))
+        hbm("gated_add + adaln fwd + row-wise MXFP8 operand of y", [BT, HW, D], int(M * D * 9.03125) + M * 8,
+            lambda: ops.gated_add_adaln_fwd(xa, ga, y2, sc, sh, 1e-6, HW, quant=True))
         hid = (torch.randn(8, M // 8, 8, 128, device="cuda")).to(BF16)
         gm = torch.randn_like(hid)
         c = _acts(8, 8)

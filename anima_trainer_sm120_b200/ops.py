@@ -245,30 +245,52 @@ def lokr_kron_backward(dw: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, alp
     return dw1, dw2
 
 
-def adaln_fwd(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, eps: float, hw: int
-              ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """x ``[rows, d]``, scale/shift ``[rows/hw, d]`` (bf16, contiguous) -> (y, mean, rstd)."""
+def can_emit_row_codes(rows: int, d: int) -> bool:
+    """Shapes for which the AdaLN forward kernels can also write the row-wise MXFP8 operand of their output."""
+    return rows > 0 and rows % 128 == 0 and d % 128 == 0 and d <= 4096
+
+
+def _row_operand(rows: int, d: int, dev) -> MXOperand:
+    return MXOperand(torch.empty((rows, d), dtype=torch.uint8, device=dev),
+                     torch.empty(scales_bytes(rows, d, SCALES_TILED), dtype=torch.uint8, device=dev), SCALES_TILED)
+
+
+def adaln_fwd(x: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor, eps: float, hw: int, *, quant: bool = False):
+    """x ``[rows, d]``, scale/shift ``[rows/hw, d]`` (bf16, contiguous) -> (y, mean, rstd); with ``quant`` also
+    the row-wise MXFP8 operand of y (tiled scales), bit-identical to ``mx_quantize(y)``, from the same pass."""
     dev = _lib.require_cuda(x, scale, shift)
     rows, d = x.shape
     y = torch.empty_like(x)
     mean = torch.empty(rows, dtype=torch.float32, device=dev)
     rstd = torch.empty(rows, dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
+        if quant:
+            op = _row_operand(rows, d, dev)
+            check(_lib.load().anima_adaln_fwd_quant(ptr(x), ptr(scale), ptr(shift), float(eps), rows, hw, d, ptr(y),
+                                                    ptr(mean), ptr(rstd), ptr(op.codes), ptr(op.scales), op.layout,
+                                                    _lib.stream_ptr(dev)))
+            return y, mean, rstd, op
         check(_lib.load().anima_adaln_fwd(ptr(x), ptr(scale), ptr(shift), float(eps), rows, hw, d, ptr(y),
                                           ptr(mean), ptr(rstd), _lib.stream_ptr(dev)))
     return y, mean, rstd
 
 
 def gated_add_adaln_fwd(x: torch.Tensor, gate: torch.Tensor, sub: torch.Tensor, scale: torch.Tensor,
-                        shift: torch.Tensor, eps: float, hw: int
-                        ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
-    """``x_new = x + gate * sub`` and ``y = AdaLN(x_new)`` in one pass -> (x_new, y, mean, rstd)."""
+                        shift: torch.Tensor, eps: float, hw: int, *, quant: bool = False):
+    """``x_new = x + gate * sub`` and ``y = AdaLN(x_new)`` in one pass -> (x_new, y, mean, rstd); with ``quant``
+    also the row-wise MXFP8 operand of y."""
     dev = _lib.require_cuda(x, gate, sub, scale, shift)
     rows, d = x.shape
     x_new, y = torch.empty_like(x), torch.empty_like(x)
     mean = torch.empty(rows, dtype=torch.float32, device=dev)
     rstd = torch.empty(rows, dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
+        if quant:
+            op = _row_operand(rows, d, dev)
+            check(_lib.load().anima_gated_add_adaln_fwd_quant(
+                ptr(x), ptr(gate), ptr(sub), ptr(scale), ptr(shift), float(eps), rows, hw, d, ptr(x_new), ptr(y),
+                ptr(mean), ptr(rstd), ptr(op.codes), ptr(op.scales), op.layout, _lib.stream_ptr(dev)))
+            return x_new, y, mean, rstd, op
         check(_lib.load().anima_gated_add_adaln_fwd(ptr(x), ptr(gate), ptr(sub), ptr(scale), ptr(shift), float(eps),
                                                     rows, hw, d, ptr(x_new), ptr(y), ptr(mean), ptr(rstd),
                                                     _lib.stream_ptr(dev)))

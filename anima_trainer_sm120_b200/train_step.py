@@ -26,7 +26,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from . import adaln_merge, adaln_patch, lokr_patch, mlp_patch, qk_norm_rope
+from . import adaln_kernel, adaln_merge, adaln_patch, lokr_patch, mlp_patch, qk_norm_rope
 from .anima_dit import AnimaConfig, AnimaDiT, Attention, Block, GPT2FeedForward
 from .lokr import attach_lokr
 
@@ -84,6 +84,7 @@ class Trainer:
             adaln_patch.install(Block)
             qk_norm_rope.install(Attention)
             mlp_patch.install(GPT2FeedForward)       # takes effect for plain LoKr adapters on the quantised path
+            adaln_kernel.emit_row_operand(True)      # every consumer of an AdaLN output is a quantised linear here
             wrapped = fp8_quant.collect_lokr_wrapped_linears(self.network)
             self.n_frozen_quantised = fp8_quant.quantize_frozen_linears(self.dit, skip=wrapped)
             if self.tlokr:
@@ -101,11 +102,13 @@ class Trainer:
             qk_norm_rope.install(Attention)
             mlp_patch.uninstall(GPT2FeedForward)
             lokr_patch.disable_fp8()
+            adaln_kernel.emit_row_operand(False)
         else:
             adaln_patch.uninstall(Block)
             qk_norm_rope.uninstall(Attention)
             mlp_patch.uninstall(GPT2FeedForward)
             lokr_patch.disable_fp8()
+            adaln_kernel.emit_row_operand(False)
         self.dit.train()
         self.params = [p for p in self.network.parameters() if p.requires_grad]
         # flat fp32 gradient buffer; every .grad is a view into it, so the DP exchange is one call

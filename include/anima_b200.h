@@ -239,6 +239,20 @@ int anima_gated_add_adaln_fwd(const void* x, const void* gate, const void* sub, 
                               const void* shift, float eps, int64_t rows, int64_t hw, int64_t d,
                               void* x_new, void* y, float* mean, float* rstd, void* stream);
 
+/* AdaLN forward that also emits the row-wise MXFP8 operand of y (no reference counterpart: the reference
+ * writes y in adaln_kernel.py:34-68 and quantises it again inside each consuming linear, fp8_quant.py:149-150,
+ * 483-485; its audit lists "quantise in the producer" as the open item). codes_row u8 [rows, d] and scales_row
+ * (PLAIN [rows, d/32] or TILED) are bit-identical to anima_mx_quantize of the bf16 y. y may be NULL (then only
+ * the operand and the statistics are written). d % 128 == 0; TILED needs rows % 128 == 0. The _gated_add_ form
+ * is anima_gated_add_adaln_fwd with the same extra outputs. */
+int anima_adaln_fwd_quant(const void* x, const void* scale, const void* shift, float eps, int64_t rows,
+                          int64_t hw, int64_t d, void* y, float* mean, float* rstd, uint8_t* codes_row,
+                          uint8_t* scales_row, int scale_layout, void* stream);
+int anima_gated_add_adaln_fwd_quant(const void* x, const void* gate, const void* sub, const void* scale,
+                                    const void* shift, float eps, int64_t rows, int64_t hw, int64_t d,
+                                    void* x_new, void* y, float* mean, float* rstd, uint8_t* codes_row,
+                                    uint8_t* scales_row, int scale_layout, void* stream);
+
 /* Backward of the pair in one pass. d_y is the gradient of y, d_xnew the gradient reaching x_new through
  * the residual stream. With dx_ln the AdaLN input gradient (as anima_adaln_bwd):
  *   dx   = d_xnew + dx_ln        (gradient of x, bf16)        dsub  = gate * dx

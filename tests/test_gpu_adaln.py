@@ -194,3 +194,75 @@ def test_gated_add_adaln_one_pass_equals_the_two_ops(B, H, W, D):
         results.append([x_new.detach(), y.detach()] + [t.grad for t in leaves])
     for ref, got in zip(*results):
         assert torch.equal(ref, got)
+
+
+@pytest.mark.parametrize("BT,HW,D", [(2, 64, 128), (1, 128, 384), (3, 128, 1024), (8, 512, 2048), (2, 192, 4096)])
+def test_adaln_forward_emits_the_row_operand_of_its_output(BT, HW, D):
+    """The quantising forward writes the same y / mean / rstd as the plain one, and codes and scales equal to
+    quantising that y afterwards (tiled scales), bit for bit; the same holds for the one-pass residual form and
+    when y itself is not written."""
+    from anima_trainer_sm120_b200 import _lib
+    ops = _ops()
+    x, s, b, gate, sub, _ = (t.cuda() for t in _case(BT, HW, D, seed=5))
+    y, mean, rstd = ops.adaln_fwd(x, s, b, 1e-6, HW)
+    y_q, mean_q, rstd_q, op = ops.adaln_fwd(x, s, b, 1e-6, HW, quant=True)
+    want, _ = ops.mx_quantize(y, rowwise=True)
+    assert torch.equal(y_q, y) and torch.equal(mean_q, mean) and torch.equal(rstd_q, rstd)
+    assert torch.equal(op.codes, want.codes) and torch.equal(op.scales, want.scales)
+
+    x_new, y2, mean2, rstd2 = ops.gated_add_adaln_fwd(x, gate, sub, s, b, 1e-6, HW)
+    x_new_q, y2_q, mean2_q, rstd2_q, op2 = ops.gated_add_adaln_fwd(x, gate, sub, s, b, 1e-6, HW, quant=True)
+    want2, _ = ops.mx_quantize(y2, rowwise=True)
+    assert torch.equal(x_new_q, x_new) and torch.equal(y2_q, y2) and torch.equal(mean2_q, mean2)
+    assert torch.equal(op2.codes, want2.codes) and torch.equal(op2.scales, want2.scales)
+
+    # plain scale layout and no bf16 output, through the C ABI directly
+    rows = BT * HW
+    codes = torch.zeros(rows, D, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(rows, D // 32, dtype=torch.uint8, device="cuda")
+    mean3, rstd3 = torch.empty_like(mean), torch.empty_like(rstd)
+    rc = _lib.load().anima_adaln_fwd_quant(ops.ptr(x), ops.ptr(s), ops.ptr(b), 1e-6, rows, HW, D, None, ops.ptr(mean3),
+                                           ops.ptr(rstd3), ops.ptr(codes), ops.ptr(scales), ops.SCALES_PLAIN,
+                                           _lib.stream_ptr(x.device))
+    assert rc == 0
+    plain, _ = ops.mx_quantize(y, rowwise=True, layout=ops.SCALES_PLAIN)
+    assert torch.equal(codes, plain.codes) and torch.equal(scales, plain.scales.view(rows, D // 32))
+    assert torch.equal(mean3, mean) and torch.equal(rstd3, rstd)
+
+
+def test_adaln_quantising_forward_refuses_shapes_it_cannot_tile():
+    ops = _ops()
+    x, s, b, _, _, _ = (t.cuda() for t in _case(2, 24, 256))
+    with pytest.raises(ValueError):
+        ops.adaln_fwd(x, s, b, 1e-6, 24, quant=True)          # 48 rows: tiled scales need whole 128-row chunks
+    assert not ops.can_emit_row_codes(48, 256) and not ops.can_emit_row_codes(128, 96)
+
+
+def test_autograd_adaln_hands_its_operand_to_the_quantised_linears():
+    """With emission on, a quantised linear fed a reshape of the AdaLN output launches no quantiser and returns
+    exactly what it returns with emission off."""
+    from anima_trainer_sm120_b200 import adaln_kernel, fp8_quant
+    torch.manual_seed(3)
+    B, H, W, D = 2, 8, 16, 256
+    x = torch.randn(B, 1, H, W, D, device="cuda", dtype=BF16)
+    sc = (torch.randn(B, 1, 1, 1, D, device="cuda") * 0.1).to(BF16)
+    sh = (torch.randn(B, 1, 1, 1, D, device="cuda") * 0.1).to(BF16)
+    Wq = fp8_quant.quantize_weight((torch.randn(384, D, device="cuda") * 0.05).to(BF16))
+    W_bf16 = torch.zeros(384, D, device="cuda", dtype=BF16)
+
+    def run():
+        fp8_quant.clear_activation_memo()
+        fp8_quant.act_memo_stats.update(hits=0, misses=0, adopted=0)
+        n = adaln_kernel.fused_adaln(x, sc, sh, 1e-6)
+        out = fp8_quant.mxfp8_frozen_linear(n.reshape(B, H * W, D), Wq, W_bf16)
+        return n, out, dict(fp8_quant.act_memo_stats)
+
+    try:
+        adaln_kernel.emit_row_operand(True)
+        n1, out1, stats1 = run()
+    finally:
+        adaln_kernel.emit_row_operand(False)
+    n0, out0, stats0 = run()
+    assert stats1 == {"hits": 1, "misses": 0, "adopted": 1} and stats0 == {"hits": 0, "misses": 1, "adopted": 0}
+    assert torch.equal(n1, n0) and torch.equal(out1, out0)
+    fp8_quant.clear_activation_memo()

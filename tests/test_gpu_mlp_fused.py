@@ -18,7 +18,18 @@ def _same(a, b):
     assert torch.equal(a.codes, b.codes)
 
 
-def test_quantize_gelu_is_bit_exact_for_every_finite_bf16_input():
+@pytest.fixture(params=["1", "2"], ids=["plain-loads", "copy-engine-fed"])
+def quantiser_variant(request, monkeypatch):
+    """The kernel tests run once per quantiser kernel (the library reads the variable on every call): the tile
+    kernel with plain loads, and the persistent kernel fed by bulk tensor copies (whose bounded waits must not
+    have given up)."""
+    monkeypatch.setenv("ANIMA_MX_QUANTIZE_VARIANT", request.param)
+    yield request.param
+    from anima_trainer_sm120_b200 import _lib
+    assert _lib.load().anima_mx_quantize_status() == 0
+
+
+def test_quantize_gelu_is_bit_exact_for_every_finite_bf16_input(quantiser_variant):
     from anima_trainer_sm120_b200 import ops
     bits = torch.arange(65536, dtype=torch.int32)
     finite = bits[(bits & 0x7F80) != 0x7F80]                                  # 65280 patterns
@@ -41,8 +52,8 @@ def test_quantize_gelu_is_bit_exact_for_every_finite_bf16_input():
         _same(row, want)
 
 
-@pytest.mark.parametrize("rows,cols", [(256, 512), (96, 160), (1024, 8192)])
-def test_quantize_gelu_forward_and_gradient_match_eager_then_quantise(rows, cols):
+@pytest.mark.parametrize("rows,cols", [(256, 512), (96, 160), (1024, 8192), (8192 + 32, 2048 + 32)])
+def test_quantize_gelu_forward_and_gradient_match_eager_then_quantise(rows, cols, quantiser_variant):
     from anima_trainer_sm120_b200 import ops
     torch.manual_seed(rows + cols)
     h = (torch.randn(rows, cols, device=DEV) * 2.0).to(BF16)
@@ -58,6 +69,9 @@ def test_quantize_gelu_forward_and_gradient_match_eager_then_quantise(rows, cols
     want_row, want_col = ops.mx_quantize(hr.grad, rowwise=True, colwise=True)
     _same(row, want_row)
     _same(col, want_col)
+    _same(ops.mx_quantize_gelu(h, g, rowwise=False, colwise=True)[1], want_col)      # one form at a time
+    _same(ops.mx_quantize_gelu(h, g, rowwise=True, colwise=False)[0], want_row)
+    _same(ops.mx_quantize_gelu(h, rowwise=False, colwise=True)[1], ops.mx_quantize(F.gelu(h), rowwise=False, colwise=True)[1])
 
 
 def test_quantize_gelu_rejects_mismatched_gradient():
@@ -128,9 +142,9 @@ def test_activation_memo_shares_one_quantisation_between_consumers():
     Ws = [fp8_quant.quantize_weight((torch.randn(256, 256, device=DEV) * 0.05).to(BF16)) for _ in range(3)]
     W_bf16 = torch.zeros(256, 256, device=DEV, dtype=BF16)
     fp8_quant.clear_activation_memo()
-    fp8_quant.act_memo_stats.update(hits=0, misses=0)
+    fp8_quant.act_memo_stats.update(hits=0, misses=0, adopted=0)
     ys = [fp8_quant.mxfp8_frozen_linear(x, W, W_bf16) for W in Ws]          # q / k / v pattern: same tensor object
-    assert fp8_quant.act_memo_stats == {"hits": 2, "misses": 1}
+    assert fp8_quant.act_memo_stats == {"hits": 2, "misses": 1, "adopted": 0}
     x_row, _ = ops.mx_quantize(x, rowwise=True)
     for y, W in zip(ys, Ws):
         assert torch.equal(y, ops.mx_gemm(x_row, W.row))
@@ -138,6 +152,7 @@ def test_activation_memo_shares_one_quantisation_between_consumers():
     y = fp8_quant.mxfp8_frozen_linear(x, Ws[0], W_bf16)
     assert fp8_quant.act_memo_stats["misses"] == 2
     assert torch.equal(y, ops.mx_gemm(ops.mx_quantize(x, rowwise=True)[0], Ws[0].row))
-    row, col = fp8_quant.quantize_activation(x, colwise=True)               # asking for a form the entry lacks
-    assert col is not None and fp8_quant.act_memo_stats["misses"] == 3
+    row, col = fp8_quant.quantize_activation(x, colwise=True)               # the entry lacks this form: only it is made
+    assert fp8_quant.act_memo_stats["misses"] == 2
+    assert torch.equal(col.codes, ops.mx_quantize(x, rowwise=False, colwise=True)[1].codes)
     fp8_quant.clear_activation_memo()

@@ -24,27 +24,47 @@ def fake_quantiser(monkeypatch):
 
     monkeypatch.setattr(ops, "mx_quantize", fake)
     fp8_quant.clear_activation_memo()
-    fp8_quant.act_memo_stats.update(hits=0, misses=0)
+    fp8_quant.act_memo_stats.update(hits=0, misses=0, adopted=0)
     yield calls
     fp8_quant.clear_activation_memo()
 
 
-def test_memo_hits_on_the_same_tensor_object_only(fake_quantiser):
+def test_memo_hits_on_the_tensor_and_on_contiguous_views_of_all_of_it(fake_quantiser):
     x = torch.zeros(64, 32, dtype=torch.bfloat16)
     r1, c1 = fp8_quant.quantize_activation(x, colwise=False)
     r2, _ = fp8_quant.quantize_activation(x, colwise=False)
     assert r2 is r1 and c1 is None and len(fake_quantiser) == 1
-    same_storage_other_object = x.view(64, 32)
-    fp8_quant.quantize_activation(same_storage_other_object, colwise=False)
-    assert len(fake_quantiser) == 2                                   # identity, not storage, is the key
-    assert fp8_quant.act_memo_stats == {"hits": 1, "misses": 2}
+    r3, _ = fp8_quant.quantize_activation(x.view(2, 32, 32), colwise=False)   # same bytes, same row length
+    assert r3 is r1 and len(fake_quantiser) == 1
+    fp8_quant.quantize_activation(x.view(32, 64), colwise=False)              # other row length: other operand
+    assert len(fake_quantiser) == 2
+    fp8_quant.quantize_activation(x[:32], colwise=False)                      # part of the tensor
+    assert len(fake_quantiser) == 3
+    fp8_quant.quantize_activation(torch.zeros(64, 32, dtype=torch.bfloat16), colwise=False)   # equal values, other tensor
+    assert len(fake_quantiser) == 4
+    assert fp8_quant.act_memo_stats == {"hits": 2, "misses": 4, "adopted": 0}
+
+
+def test_memo_adopts_an_operand_made_by_the_producer(fake_quantiser):
+    y = torch.zeros(2, 64, 32, dtype=torch.bfloat16)
+    made = ops.MXOperand(torch.zeros(128, 32, dtype=torch.uint8), torch.zeros(512, dtype=torch.uint8), 1)
+    fp8_quant.adopt_row_operand(y, made)
+    row, col = fp8_quant.quantize_activation(y.reshape(2, 64, 32).view(128, 32), colwise=False)
+    assert row is made and col is None and len(fake_quantiser) == 0
+    row, col = fp8_quant.quantize_activation(y, colwise=True)                 # only the missing form is made
+    assert row is made and col is not None and fake_quantiser == [((128, 32), False, True)]
+    y.mul_(2)
+    fp8_quant.quantize_activation(y, colwise=False)                           # stale after an in-place change
+    assert len(fake_quantiser) == 2
+    with pytest.raises(ValueError):
+        fp8_quant.adopt_row_operand(y.transpose(0, 1), made)
 
 
 def test_memo_misses_after_in_place_change_and_when_a_form_is_missing(fake_quantiser):
     x = torch.zeros(64, 32, dtype=torch.bfloat16)
     fp8_quant.quantize_activation(x, colwise=False)
-    _, col = fp8_quant.quantize_activation(x, colwise=True)             # entry has no column form: quantise again
-    assert col is not None and len(fake_quantiser) == 2
+    _, col = fp8_quant.quantize_activation(x, colwise=True)             # entry has no column form: make that one
+    assert col is not None and fake_quantiser[1] == ((64, 32), False, True)
     row, col2 = fp8_quant.quantize_activation(x, colwise=True)          # now both forms are there
     assert col2 is col and len(fake_quantiser) == 2
     row_only, none = fp8_quant.quantize_activation(x, colwise=False)    # a richer entry serves a poorer request
