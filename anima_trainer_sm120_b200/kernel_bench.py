@@ -163,6 +163,7 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
         hbm("tlokr_rank_mix_wgrad", list(hid.shape), hid.numel() * 4, lambda: ops.tlokr_rank_mix_wgrad(gm, hid, mask))
         hh, gg = _acts(M, 8192), _acts(M, 8192)
         nh = M * 8192
+        hbm("mx_quantize_gelu rowwise", [M, 8192], int(nh * 3.03125), lambda: ops.mx_quantize_gelu(hh, rowwise=True))
         hbm("mx_quantize_gelu row+col", [M, 8192], int(nh * 4.0625),
             lambda: ops.mx_quantize_gelu(hh, rowwise=True, colwise=True))
         hbm("mx_quantize_gelu backward row+col", [M, 8192], int(nh * 6.0625),
