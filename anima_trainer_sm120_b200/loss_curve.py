@@ -15,6 +15,7 @@ AdamW for its Prodigy + ScheduleFree optimizer, neither of which is available.
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 
@@ -53,6 +54,9 @@ def main() -> None:
                       "variant": a.variant, "n_gpus": world, "steps": a.steps, "optimizer": "AdamW (stand-in)",
                       "gradient_checkpointing": not a.no_checkpoint, "data": "synthetic"}, "losses": {}, "steps_per_s": {}}
     for arm in a.arms.split(","):
+        gc.collect()                              # the previous arm's model sits in reference cycles (hooks)
+        torch.cuda.empty_cache()
+        torch.cuda.reset_peak_memory_stats(dev)   # peak memory is reported per arm
         tr = Trainer(mcfg, StepConfig(precision=arm, variant=a.variant, lr=a.lr,
                                        gradient_checkpointing=not a.no_checkpoint), dev)
         losses, times = [], []
