@@ -50,7 +50,8 @@ struct PlainLoader {
 // so the quantised codes equal those of quantising the materialised activation / gradient bit for bit,
 // while a lookup costs a fraction of the ~25 instructions of an erf evaluation (which made this loader
 // compute-bound). Inputs outside the table (|x| < 2^-11 or >= 8, NaN, inf: about 1 in 2500 for N(0,1) data)
-// take the same expressions directly. Each CTA copies the table it needs (7.5 or 15 KB) into shared memory.
+// take the same expressions directly. A CTA copies the table it needs (7.5 or 15 KB) into shared memory: once per
+// tile in the tile kernel, once for all its tiles in the persistent copy-engine-fed kernel (the default here).
 //
 // Index arithmetic runs on both bf16 values of a 32-bit word at once: clear the signs, clamp each half to the
 // table's range with packed 16-bit max / min (a half that moved is outside the table), subtract the range
@@ -74,12 +75,6 @@ __device__ __noinline__ float gelu_grad_factor_eager_f(float x) {
   const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752440f));
   const float pdf = expf(-0.5f * x * x) * 0.39894228040143267794f;   // M_2_SQRTPI * M_SQRT1_2 * 0.5
   return cdf + x * pdf;
-}
-// index of a bf16 bit pattern in the tables, or -1 (scalar form: table fill and the rare path)
-__device__ __forceinline__ int gelu_lut_index(uint32_t bits16) {
-  const int mag = static_cast<int>(bits16 & 0x7fffu) - (kGeluLutMinExp << 7);
-  if (static_cast<unsigned>(mag) >= static_cast<unsigned>(kGeluLutHalf)) return -1;
-  return mag + ((bits16 & 0x8000u) ? kGeluLutNeg : 0);
 }
 __device__ __forceinline__ uint32_t u16x2_max(uint32_t a, uint32_t b) {
   uint32_t r;

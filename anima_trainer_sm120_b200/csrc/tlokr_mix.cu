@@ -12,6 +12,7 @@
 // The wgrad reduction is two-stage (per-CTA partial 8x8 blocks in caller scratch,
 // then a fixed-order sum) and therefore bit-reproducible.
 #include "common.cuh"
+#include "mx_quantize_tile.cuh"
 
 namespace anima {
 namespace {
@@ -65,6 +66,140 @@ rank_mix_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16* _
       for (int e = 0; e < 8; ++e) acc[i][e] *= m[e];
     }
     stg_stream16(dst + i * rank, pack8(acc[i]));
+  }
+}
+
+// rank_mix whose output leaves as MXFP8 operands (the factor GEMM that consumes the mixed tensor wants e4m3
+// codes, and writing it in bf16 only to read it back in a quantiser launch costs 4 B/elem of the 4 + 3..4 the
+// pair moves). The mix is computed and rounded to bf16 exactly as in rank_mix_kernel, then quantised with the
+// arithmetic of the tile quantiser, so codes and scales equal those of quantising the bf16 tensor.
+//   row form   [R, rank], R = items * 8: a block is 32 consecutive ranks of one row = the 8-rank chunks of four
+//              adjacent lanes (two shuffles);
+//   column form, stored transposed [rank, R]: a block is 32 consecutive rows of one rank = rows i = 0..7 of four
+//              consecutive items, i.e. four threads r8 apart, which exchange their 8-row amax through shared
+//              memory; a thread then writes 8 code bytes (its item's rows) per rank.
+// The host guarantees rank in {128, 256, 512} (whole 128-column scale chunks, whole item groups per CTA) and
+// items % 16 == 0 (every CTA full, R % 128 == 0: no padding entries in the tiled scale buffers).
+struct MixCodes {
+  uint8_t* codes_row;    // [R, rank] or null
+  uint8_t* scales_row;   // tiled
+  uint8_t* codes_colT;   // [rank, R] or null
+  uint8_t* scales_col;   // tiled
+};
+
+template <bool TRANSPOSE, bool HAS_MASK, bool ROW, bool COL>
+__global__ void __launch_bounds__(256, 2)
+rank_mix_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16* __restrict__ c,
+                      const __nv_bfloat16* __restrict__ mask, int64_t items, int64_t n_per_batch, int r8,
+                      __nv_bfloat16* __restrict__ out, const MixCodes q) {
+  __shared__ float cw[64];
+  __shared__ __align__(16) float col_amax[COL ? 2048 : 4];   // [thread][8 ranks]
+  if (threadIdx.x < 64) {
+    const int i = threadIdx.x >> 3, j = threadIdx.x & 7;
+    cw[threadIdx.x] = __bfloat162float(TRANSPOSE ? c[j * 8 + i] : c[i * 8 + j]);
+  }
+  __syncthreads();
+  const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;   // < items * r8: every CTA is full
+  const int64_t item = idx / r8;  // (b, n) flattened
+  const int rc = static_cast<int>(idx - item * r8);
+  const int rank = r8 * 8;
+  const int64_t R = items * 8;
+  const __nv_bfloat16* src = hidden + item * 8 * rank + rc * 8;
+
+  uint4 h[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) h[j] = ldg_stream16(src + j * rank);
+  float m[8];
+  if (HAS_MASK) unpack8(*reinterpret_cast<const uint4*>(mask + (item / n_per_batch) * rank + rc * 8), m);
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float hf[8];
+    unpack8(h[j], hf);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float w = cw[i * 8 + j];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[i][e] = fmaf(hf[e], w, acc[i][e]);
+    }
+  }
+  float cmax[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) cmax[e] = 0.f;
+  uint4 packed[8];   // the rows as rank_mix would have written them (bf16); the column pass re-reads them from here
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if (HAS_MASK) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[i][e] *= m[e];
+    }
+    packed[i] = pack8(acc[i]);
+    if (out != nullptr) stg_stream16(out + (item * 8 + i) * rank + rc * 8, packed[i]);
+    float f[8];
+    unpack8(packed[i], f);                         // quantise the rounded values
+    float amax = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float a = fabsf(f[e]);
+      amax = fmaxf(amax, a);
+      if (COL) cmax[e] = fmaxf(cmax[e], a);
+    }
+    if (ROW) {
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const int ex = mxq::mx_exponent(fmaxf(amax, mxq::kAmaxFloor));
+      const float inv = mxq::mx_inv_scale(ex);
+      uint2 codes;
+      codes.x = mxq::e4m3x2(f[0] * inv, f[1] * inv) | (mxq::e4m3x2(f[2] * inv, f[3] * inv) << 16);
+      codes.y = mxq::e4m3x2(f[4] * inv, f[5] * inv) | (mxq::e4m3x2(f[6] * inv, f[7] * inv) << 16);
+      const int64_t row = item * 8 + i;
+      *reinterpret_cast<uint2*>(q.codes_row + row * rank + rc * 8) = codes;
+      if ((rc & 3) == 0) {
+        const int kb = rc >> 2;
+        q.scales_row[((row >> 7) * (rank >> 7) + (kb >> 2)) * 512 + mxq::tiled_offset(static_cast<int>(row & 127), kb & 3)] =
+            static_cast<uint8_t>(ex + 127);
+      }
+    }
+  }
+  if (COL) {
+    float4* mine = reinterpret_cast<float4*>(col_amax + threadIdx.x * 8);
+    mine[0] = make_float4(cmax[0], cmax[1], cmax[2], cmax[3]);
+    mine[1] = make_float4(cmax[4], cmax[5], cmax[6], cmax[7]);
+    __syncthreads();
+    const int item_local = threadIdx.x / r8;
+    const int group0 = (item_local & ~3) * r8 + rc;   // the thread of the group's first item with this rank chunk
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float4* other = reinterpret_cast<const float4*>(col_amax + (group0 + k * r8) * 8);
+      const float4 lo = other[0], hi = other[1];
+      cmax[0] = fmaxf(cmax[0], lo.x); cmax[1] = fmaxf(cmax[1], lo.y); cmax[2] = fmaxf(cmax[2], lo.z); cmax[3] = fmaxf(cmax[3], lo.w);
+      cmax[4] = fmaxf(cmax[4], hi.x); cmax[5] = fmaxf(cmax[5], hi.y); cmax[6] = fmaxf(cmax[6], hi.z); cmax[7] = fmaxf(cmax[7], hi.w);
+    }
+    const int64_t blk = item >> 2;                    // 32-row block of R
+    const int64_t kb4 = R >> 7;                       // scale chunks per 128 ranks
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int ex = mxq::mx_exponent(fmaxf(cmax[e], mxq::kAmaxFloor));
+      const float inv = mxq::mx_inv_scale(ex);
+      float v[8];   // rank e of rows 0..7: half e % 2 of word e / 2 of each packed row
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t w = reinterpret_cast<const uint32_t*>(&packed[i])[e >> 1];
+        v[i] = __uint_as_float((e & 1) ? (w & 0xffff0000u) : (w << 16));
+      }
+      uint2 codes;
+      codes.x = mxq::e4m3x2(v[0] * inv, v[1] * inv) | (mxq::e4m3x2(v[2] * inv, v[3] * inv) << 16);
+      codes.y = mxq::e4m3x2(v[4] * inv, v[5] * inv) | (mxq::e4m3x2(v[6] * inv, v[7] * inv) << 16);
+      const int col = rc * 8 + e;
+      *reinterpret_cast<uint2*>(q.codes_colT + static_cast<int64_t>(col) * R + item * 8) = codes;
+      if ((item_local & 3) == 0)
+        q.scales_col[((col >> 7) * kb4 + (blk >> 2)) * 512 + mxq::tiled_offset(col & 127, static_cast<int>(blk & 3))] =
+            static_cast<uint8_t>(ex + 127);
+    }
   }
 }
 
@@ -180,6 +315,50 @@ extern "C" int anima_tlokr_rank_mix(const void* hidden, const void* c, const voi
   }
 #undef ANIMA_MIX
   ANIMA_CHECK_LAUNCH("tlokr_rank_mix");
+  return ANIMA_OK;
+}
+
+extern "C" int anima_tlokr_rank_mix_quant(const void* hidden, const void* c, const void* mask, int64_t batch,
+                                          int64_t n_per_batch, int64_t rank, int transpose, void* out,
+                                          uint8_t* codes_row, uint8_t* scales_row, uint8_t* codes_colT,
+                                          uint8_t* scales_col, void* stream) {
+  ANIMA_REQUIRE(hidden && c, ANIMA_E_ARG, "tlokr_rank_mix_quant: null pointer");
+  ANIMA_REQUIRE(codes_row || codes_colT, ANIMA_E_ARG, "tlokr_rank_mix_quant: no operand requested");
+  ANIMA_REQUIRE((codes_row == nullptr) == (scales_row == nullptr) && (codes_colT == nullptr) == (scales_col == nullptr),
+                ANIMA_E_ARG, "tlokr_rank_mix_quant: codes and scales must be given in pairs");
+  ANIMA_REQUIRE(batch >= 0 && n_per_batch >= 0, ANIMA_E_ARG, "tlokr_rank_mix_quant: bad sizes");
+  ANIMA_REQUIRE(rank == 128 || rank == 256 || rank == 512, ANIMA_E_SHAPE,
+                "tlokr_rank_mix_quant: rank=%lld must be 128, 256 or 512", (long long)rank);
+  const int64_t items = batch * n_per_batch;
+  ANIMA_REQUIRE(items % 16 == 0, ANIMA_E_SHAPE, "tlokr_rank_mix_quant: batch * n = %lld must be a multiple of 16",
+                (long long)items);
+  ANIMA_REQUIRE(aligned16(hidden) && aligned16(out) && (!mask || aligned16(mask)) &&
+                    (reinterpret_cast<uintptr_t>(codes_row) & 7) == 0 && (reinterpret_cast<uintptr_t>(codes_colT) & 7) == 0,
+                ANIMA_E_ALIGN, "tlokr_rank_mix_quant: misaligned tensor");
+  if (items == 0) return ANIMA_OK;
+  const int r8 = static_cast<int>(rank / 8);
+  const unsigned grid = static_cast<unsigned>(items * r8 / 256);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const auto* hp = static_cast<const __nv_bfloat16*>(hidden);
+  const auto* cp = static_cast<const __nv_bfloat16*>(c);
+  const auto* mp = static_cast<const __nv_bfloat16*>(mask);
+  auto* op = static_cast<__nv_bfloat16*>(out);
+  const MixCodes q{codes_row, scales_row, codes_colT, scales_col};
+#define ANIMA_MIXQ(T, M, R, C) rank_mix_quant_kernel<T, M, R, C><<<grid, 256, 0, s>>>(hp, cp, mp, items, n_per_batch, r8, op, q)
+#define ANIMA_MIXQ_FORMS(T, M)                                     \
+  do {                                                             \
+    if (codes_row && codes_colT) ANIMA_MIXQ(T, M, true, true);     \
+    else if (codes_row) ANIMA_MIXQ(T, M, true, false);             \
+    else ANIMA_MIXQ(T, M, false, true);                            \
+  } while (0)
+  if (transpose) {
+    if (mask) ANIMA_MIXQ_FORMS(true, true); else ANIMA_MIXQ_FORMS(true, false);
+  } else {
+    if (mask) ANIMA_MIXQ_FORMS(false, true); else ANIMA_MIXQ_FORMS(false, false);
+  }
+#undef ANIMA_MIXQ_FORMS
+#undef ANIMA_MIXQ
+  ANIMA_CHECK_LAUNCH("tlokr_rank_mix_quant");
   return ANIMA_OK;
 }
 

@@ -369,6 +369,37 @@ def tlokr_rank_mix(hidden: torch.Tensor, c: torch.Tensor, mask: torch.Tensor | N
     return out
 
 
+def can_quantise_rank_mix(batch: int, n: int, rank: int) -> bool:
+    """Shapes for which the mix kernel can write the MXFP8 operands of its output itself."""
+    return rank in (128, 256, 512) and batch * n > 0 and (batch * n) % 16 == 0
+
+
+def tlokr_rank_mix_quant(hidden: torch.Tensor, c: torch.Tensor, mask: torch.Tensor | None, transpose: bool, *,
+                         rowwise: bool = True, colwise: bool = False, want_bf16: bool = False
+                         ) -> tuple[MXOperand | None, MXOperand | None, torch.Tensor | None]:
+    """The 8x8 mix of ``hidden [batch, n, 8, rank]`` leaving as the MXFP8 operands of the mixed tensor viewed as
+    ``[batch * n * 8, rank]`` (row form, and / or column form stored ``[rank, batch * n * 8]``), bit-identical to
+    ``mx_quantize(tlokr_rank_mix(...))``; the bf16 tensor is written only with ``want_bf16``."""
+    dev = _lib.require_cuda(hidden, c, mask)
+    batch, n, _, rank = hidden.shape
+    R = batch * n * 8
+    row = col = out = None
+    if rowwise:
+        row = MXOperand(torch.empty((R, rank), dtype=torch.uint8, device=dev),
+                        torch.empty(scales_bytes(R, rank, SCALES_TILED), dtype=torch.uint8, device=dev), SCALES_TILED)
+    if colwise:
+        col = MXOperand(torch.empty((rank, R), dtype=torch.uint8, device=dev),
+                        torch.empty(scales_bytes(rank, R, SCALES_TILED), dtype=torch.uint8, device=dev), SCALES_TILED)
+    if want_bf16:
+        out = torch.empty_like(hidden)
+    with torch.cuda.device(dev):
+        check(_lib.load().anima_tlokr_rank_mix_quant(
+            ptr(hidden), ptr(c), ptr(mask), batch, n, rank, 1 if transpose else 0, ptr(out),
+            ptr(row.codes) if row else None, ptr(row.scales) if row else None,
+            ptr(col.codes) if col else None, ptr(col.scales) if col else None, _lib.stream_ptr(dev)))
+    return row, col, out
+
+
 def tlokr_rank_mix_wgrad(grad_mixed: torch.Tensor, hidden: torch.Tensor, mask: torch.Tensor | None
                          ) -> torch.Tensor:
     dev = _lib.require_cuda(grad_mixed, hidden, mask)

@@ -274,6 +274,17 @@ int anima_tlokr_rank_mix(const void* hidden, const void* c, const void* mask, in
                          int64_t n_per_batch, int64_t rank, int transpose, void* out,
                          void* stream);
 
+/* The same mix with its output leaving as MXFP8 operands for the factor GEMMs (no reference counterpart:
+ * _FP8StructuredLoKr, tlokr.py:589-667, writes the mixed tensor in bf16 and quantises it in a second pass).
+ * Row form: codes_row u8 [R, rank] + TILED scales, R = batch * n_per_batch * 8; column form, transposed:
+ * codes_colT u8 [rank, R] + TILED scales. Either pair may be NULL; out (bf16, as anima_tlokr_rank_mix) may be
+ * NULL too. Codes and scales are bit-identical to anima_mx_quantize of the bf16 output.
+ * rank in {128, 256, 512}; batch * n_per_batch % 16 == 0. */
+int anima_tlokr_rank_mix_quant(const void* hidden, const void* c, const void* mask, int64_t batch,
+                               int64_t n_per_batch, int64_t rank, int transpose, void* out,
+                               uint8_t* codes_row, uint8_t* scales_row, uint8_t* codes_colT,
+                               uint8_t* scales_col, void* stream);
+
 /* ref: tlokr_kernels.py:85-122, :168-204 (rank_mix_wgrad).
  *   dc[i,j] = sum_{b,n,r} grad_mixed[b,n,i,r] * hidden[b,n,j,r] * mask[b,r]   (fp32 [8,8])
  * Reads both tensors once (the reference reads them once per (i,j) pair). */

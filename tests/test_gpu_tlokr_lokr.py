@@ -67,6 +67,43 @@ def test_rank_mix_shapes_vs_oracle(B, n, r):
         assert torch.equal(dc, again)  # deterministic reduction
 
 
+@pytest.mark.parametrize("B,n,r", [(2, 64, 128), (1, 16, 256), (3, 16, 512), (8, 512, 128)])
+def test_rank_mix_emits_the_operands_of_its_output(B, n, r):
+    """The quantising mix writes codes and tiled scales equal to quantising the bf16 mix afterwards, in the row
+    form, the transposed column form, or both, with and without mask and transpose; the optional bf16 output is
+    the plain kernel's."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(B + n + r)
+    hidden = (torch.randn(B, n, 8, r, generator=g) * 3.0).to(BF16).cuda()
+    hidden[0, 0, :, :32] = 0                                  # an all-zero block takes the amax floor
+    weight = torch.randn(8, 8, generator=g).to(BF16).cuda()
+    mask = OT.rank_mask(torch.rand(B, generator=g), max_rank=r, min_rank=max(1, r // 2), dtype=BF16).cuda()
+    for m in (mask, None):
+        for tr in (False, True):
+            mixed = ops.tlokr_rank_mix(hidden, weight, m, tr)
+            want_row, want_col = ops.mx_quantize(mixed.view(-1, r), rowwise=True, colwise=True)
+            for row, col in ((True, True), (True, False), (False, True)):
+                got_row, got_col, out = ops.tlokr_rank_mix_quant(hidden, weight, m, tr, rowwise=row, colwise=col,
+                                                                 want_bf16=row and col)
+                if row:
+                    assert torch.equal(got_row.codes, want_row.codes) and torch.equal(got_row.scales, want_row.scales)
+                if col:
+                    assert torch.equal(got_col.codes, want_col.codes) and torch.equal(got_col.scales, want_col.scales)
+                assert (out is None) != (row and col)
+                if out is not None:
+                    assert torch.equal(out, mixed)
+
+
+def test_rank_mix_quant_refuses_shapes_it_cannot_tile():
+    ops = _ops()
+    w = torch.eye(8, dtype=BF16, device="cuda")
+    assert not ops.can_quantise_rank_mix(1, 16, 64) and not ops.can_quantise_rank_mix(1, 8, 128)
+    with pytest.raises(ValueError):
+        ops.tlokr_rank_mix_quant(torch.zeros(1, 16, 8, 64, dtype=BF16, device="cuda"), w, None, False)
+    with pytest.raises(ValueError):
+        ops.tlokr_rank_mix_quant(torch.zeros(1, 8, 8, 128, dtype=BF16, device="cuda"), w, None, False)
+
+
 def test_rank_mix_rejects_unsupported_shapes():
     from anima_trainer_sm120_b200.tlokr_kernels import rank_mix
     h = torch.zeros(1, 2, 4, 16, dtype=BF16, device="cuda")
