@@ -94,6 +94,7 @@ rank_mix_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloa
                       __nv_bfloat16* __restrict__ out, const MixCodes q) {
   __shared__ float cw[64];
   __shared__ __align__(16) float col_amax[COL ? 2048 : 4];   // [thread][8 ranks]
+  __shared__ __align__(16) uint2 stage[COL ? 2048 : 2];      // transposed codes of the CTA: [rank][item] x 8 bytes
   if (threadIdx.x < 64) {
     const int i = threadIdx.x >> 3, j = threadIdx.x & 7;
     cw[threadIdx.x] = __bfloat162float(TRANSPOSE ? c[j * 8 + i] : c[i * 8 + j]);
@@ -181,6 +182,11 @@ rank_mix_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloa
     }
     const int64_t blk = item >> 2;                    // 32-row block of R
     const int64_t kb4 = R >> 7;                       // scale chunks per 128 ranks
+    // A rank owns P = 256 / r8 pieces of 8 bytes (one per item of the CTA), contiguous in the output. They are
+    // staged in shared memory, piece p of rank chunk rc at p ^ (2 * (rc % (P/2))) (pairs stay together and the
+    // stores of a half-warp spread over the banks), and leave as 16-byte stores in runs of 8 P bytes.
+    const int P = 256 / r8;
+    const int swz = (rc & (P / 2 - 1)) << 1;
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       const int ex = mxq::mx_exponent(fmaxf(cmax[e], mxq::kAmaxFloor));
@@ -195,10 +201,21 @@ rank_mix_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloa
       codes.x = mxq::e4m3x2(v[0] * inv, v[1] * inv) | (mxq::e4m3x2(v[2] * inv, v[3] * inv) << 16);
       codes.y = mxq::e4m3x2(v[4] * inv, v[5] * inv) | (mxq::e4m3x2(v[6] * inv, v[7] * inv) << 16);
       const int col = rc * 8 + e;
-      *reinterpret_cast<uint2*>(q.codes_colT + static_cast<int64_t>(col) * R + item * 8) = codes;
+      stage[col * P + (item_local ^ swz)] = codes;
       if ((item_local & 3) == 0)
         q.scales_col[((col >> 7) * kb4 + (blk >> 2)) * 512 + mxq::tiled_offset(col & 127, static_cast<int>(blk & 3))] =
             static_cast<uint8_t>(ex + 127);
+    }
+    __syncthreads();
+    const int64_t row0 = static_cast<int64_t>(blockIdx.x) * P * 8;   // first row of R this CTA covers
+    const int half = P / 2;                                           // 16-byte units per rank
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      const int u = threadIdx.x + h * 256;          // 1024 units: rank u / half, unit u % half
+      const int col = u / half, unit = u - col * half;
+      const int s2 = ((col >> 3) & (half - 1)) << 1;
+      const uint4 v = *reinterpret_cast<const uint4*>(&stage[col * P + ((2 * unit) ^ s2)]);
+      stg_stream16(q.codes_colT + static_cast<int64_t>(col) * R + row0 + unit * 16, v);
     }
   }
 }

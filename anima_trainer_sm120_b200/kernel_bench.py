@@ -162,6 +162,8 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
         hbm("tlokr_rank_mix", list(hid.shape), hid.numel() * 4, lambda: ops.tlokr_rank_mix(hid, c, mask, False))
         hbm("tlokr_rank_mix + row-wise operand (no bf16 output)", list(hid.shape), int(hid.numel() * 3.03125),
             lambda: ops.tlokr_rank_mix_quant(hid, c, mask, False, rowwise=True))
+        hbm("tlokr_rank_mix + column operand (no bf16 output)", list(hid.shape), int(hid.numel() * 3.03125),
+            lambda: ops.tlokr_rank_mix_quant(hid, c, mask, False, rowwise=False, colwise=True))
         hbm("tlokr_rank_mix + row and column operands (no bf16 output)", list(hid.shape), int(hid.numel() * 4.0625),
             lambda: ops.tlokr_rank_mix_quant(hid, c, mask, True, rowwise=True, colwise=True))
         hbm("tlokr_rank_mix_wgrad", list(hid.shape), hid.numel() * 4, lambda: ops.tlokr_rank_mix_wgrad(gm, hid, mask))

@@ -337,8 +337,8 @@ def _mix_operands(hidden, c, mask, transpose: bool, *, row: bool, col: bool):
     ``[-1, rank]``. The mix kernel writes them itself where the shape allows, so the mixed tensor never exists in
     bf16; otherwise the mix is followed by a quantiser launch. Same bits either way."""
     batch, n, _, rank = hidden.shape
-    # the kernel's column form writes 8-byte pieces and measured slower than mix + quantiser (60.9 against
-    # 28.7 + 26 us at [8, 4096, 8, 128]); its row form wins (38.4 against 28.7 + 18)
+    # at [8, 4096, 8, 128] the kernel's row form beats mix + quantiser (38.4 against 28.7 + 18.9 us); its column
+    # forms do not (46.6 against 28.7 + 16.9, 62.0 against 28.7 + 30.7), so those keep the two kernels
     if not col and ops.can_quantise_rank_mix(batch, n, rank):
         m = None if mask is None else mask.contiguous().to(BF16)
         r, cl, _ = ops.tlokr_rank_mix_quant(hidden.contiguous(), c.contiguous(), m, transpose, rowwise=row, colwise=col)
