@@ -48,12 +48,13 @@ struct RowCodes {
 };
 
 //
-// STAGED (residual form only; hw % 8 == 0: the 8 rows of a CTA belong to one sample): the CTA converts the sample's modulation row
+// STAGED (hw % 8 == 0: the 8 rows of a CTA belong to one sample; which forms use it is decided where the
+// kernel is launched): the CTA converts the sample's modulation row
 // once, (1 + scale) and shift as fp32 in shared memory, instead of every warp unpacking and adding them for
 // its own row; the output pass then reads two 16-byte pieces per operand (split so that consecutive lanes read
 // consecutive 16 bytes) and saves 3 of its ~7.5 instructions per element. Same arithmetic, same bits.
 template <int NCH, bool GATED, bool QUANT, bool STAGED>
-__global__ void __launch_bounds__(kThreads, NCH <= 8 ? 4 : 2)
+__global__ void __launch_bounds__(kThreads, NCH > 8 ? 2 : (NCH == 8 && STAGED && !GATED && !QUANT) ? 3 : 4)
 adaln_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gate,
                  const __nv_bfloat16* __restrict__ sub, const __nv_bfloat16* __restrict__ scale,
                  const __nv_bfloat16* __restrict__ shift, float eps, int64_t rows, int64_t hw,
@@ -531,17 +532,20 @@ void launch_adaln_fwd(const void* x, const void* gate, const void* sub, const vo
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int di = static_cast<int>(d);
   // one sample per CTA (8 rows) lets the CTA convert the modulation row once; 8 * d bytes of shared memory
-  // Measured at [8, 4096, 2048]: the residual form gains (119.8 -> 107.5 us, with the operand 137.7 -> 129.5); the
-  // plain form, already at its 64-register cap, spills more and loses (65.0 -> 85.5 us), so it is never staged.
-  const bool staged = GATED && hw % (kThreads / 32) == 0 && adaln_fwd_staging_enabled();
+  // Measured at [8, 4096, 2048], 4 CTAs/SM (64 registers): the residual form gains from the staging (119.8 ->
+  // 107.5 us, with the operand 137.7 -> 129.5); the plain form spills 168 bytes with it and loses (65.0 -> 85.5).
+  // At 3 CTAs/SM (80 registers, no spills) the staged plain form is the fastest of all (58.9 us) while every
+  // other form is slower than at 4 (plain + operand 90.1 against 86.5 unstaged, residual 116.7, residual +
+  // operand 141.8). Hence: residual forms staged at 4 CTAs/SM, plain form staged at 3, plain + operand unstaged.
+  const bool staged = (GATED || !QUANT) && hw % (kThreads / 32) == 0 && adaln_fwd_staging_enabled();
   const size_t smem = staged ? static_cast<size_t>(d) * 8 : 0;
 #define ANIMA_LAUNCH_FWD(N)                                                                                      \
   do {                                                                                                           \
     bool launched = false;                                                                                       \
-    if constexpr (GATED) {                                                                                       \
+    if constexpr (GATED || (!QUANT && N <= 8)) { /* the plain form of a row longer than 2048 spills when staged */ \
       if (staged) {                                                                                              \
-        adaln_fwd_kernel<N, true, QUANT, true><<<grid, kThreads, smem, s>>>(xp, gp, up, sp, bp, eps, rows, hw,   \
-                                                                            di, xn, yp, mean, rstd, q);          \
+        adaln_fwd_kernel<N, GATED, QUANT, true><<<grid, kThreads, smem, s>>>(xp, gp, up, sp, bp, eps, rows, hw,  \
+                                                                             di, xn, yp, mean, rstd, q);         \
         launched = true;                                                                                         \
       }                                                                                                          \
     }                                                                                                            \

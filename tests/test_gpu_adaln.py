@@ -270,14 +270,14 @@ def test_autograd_adaln_hands_its_operand_to_the_quantised_linears():
 
 @pytest.mark.parametrize("BT,HW,D", [(2, 64, 256), (3, 128, 1024), (4, 1024, 2048), (2, 24, 4096)])
 def test_staged_modulation_gives_the_same_bits(BT, HW, D, monkeypatch):
-    """The residual forward converts the sample's modulation row once per CTA (hw % 8 == 0); every output equals
+    """The forward kernels convert the sample's modulation row once per CTA (hw % 8 == 0); every output equals
     the kernel that reads it from global memory per row (the library reads the variable on every call)."""
     ops = _ops()
     x, s, b, gate, sub, _ = (t.cuda() for t in _case(BT, HW, D, seed=9))
     outs = {}
     for flag in ("0", "1"):
         monkeypatch.setenv("ANIMA_ADALN_FWD_STAGING", flag)
-        outs[flag] = ops.gated_add_adaln_fwd(x, gate, sub, s, b, 1e-6, HW)
+        outs[flag] = (*ops.gated_add_adaln_fwd(x, gate, sub, s, b, 1e-6, HW), *ops.adaln_fwd(x, s, b, 1e-6, HW))
         if ops.can_emit_row_codes(BT * HW, D):
             *plain, op = ops.gated_add_adaln_fwd(x, gate, sub, s, b, 1e-6, HW, quant=True)
             outs[flag] = (*outs[flag], *plain, op.codes, op.scales)
