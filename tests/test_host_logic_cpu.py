@@ -155,3 +155,23 @@ def test_patches_fall_through_on_cpu():
         assert torch.equal(attn(x, None, None, rope_emb=rope), ref)
     finally:
         qk_norm_rope.uninstall(Attention)
+
+
+def test_producer_side_quantisation_is_offered_only_for_shapes_the_kernels_tile():
+    from anima_trainer_sm120_b200 import adaln_kernel
+    assert ops.can_emit_row_codes(32768, 2048) and ops.can_emit_row_codes(128, 128)
+    assert not ops.can_emit_row_codes(0, 2048)            # nothing to do
+    assert not ops.can_emit_row_codes(96, 2048)           # tiled scales need whole 128-row chunks
+    assert not ops.can_emit_row_codes(128, 2080)          # and whole 128-column chunks
+    assert not ops.can_emit_row_codes(128, 8192)          # longer than the AdaLN kernels' longest row
+    assert ops.can_quantise_rank_mix(8, 4096, 128) and ops.can_quantise_rank_mix(1, 16, 512)
+    assert not ops.can_quantise_rank_mix(8, 4096, 64) and not ops.can_quantise_rank_mix(1, 24, 128)
+    x = torch.zeros(1, 1, 8, 16, 256, dtype=torch.bfloat16)
+    assert not adaln_kernel._emits(x, 128, 256)           # off unless switched on
+    adaln_kernel.emit_row_operand(True)
+    try:
+        assert adaln_kernel._emits(x, 128, 256)
+        assert not adaln_kernel._emits(x.float(), 128, 256)   # the fp32 path returns a cast copy: nothing to adopt
+        assert not adaln_kernel._emits(x, 120, 256)
+    finally:
+        adaln_kernel.emit_row_operand(False)
