@@ -258,20 +258,24 @@ __global__ void mx_scales_retile_kernel(const uint8_t* __restrict__ plain, int64
 // TILED scales of a code matrix [rows_in, k_in] -> TILED scales of the SAME codes viewed as
 // [rows_out, k_out] (rows_in * k_in == rows_out * k_out): the 32-element blocks keep their row-major
 // order, only their (row, block) coordinates and therefore their place in the 128 x 4 tiling change.
-__global__ void mx_scales_regroup_kernel(const uint8_t* __restrict__ in, int64_t kb_in, int64_t rows_out,
-                                         int64_t kb_out, uint8_t* __restrict__ out) {
-  const int64_t kb4_out = ceil_div(kb_out, 4), kb4_in = ceil_div(kb_in, 4);
-  const int64_t total = ceil_div(rows_out, 128) * kb4_out * 512;
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t chunk = i / 512;
+// Index arithmetic in Idx: 32-bit when every extent fits (64-bit divisions cost ~10x here and the kernel moves
+// one byte per thread-iteration: 16 us for the 2 MB of scales of a [32768, 2048] operand before, 504 launches
+// per T-LoKr step).
+template <class Idx>
+__global__ void mx_scales_regroup_kernel(const uint8_t* __restrict__ in, Idx kb_in, Idx rows_out, Idx kb_out, Idx total,
+                                         uint8_t* __restrict__ out) {
+  const Idx kb4_out = (kb_out + 3) / 4, kb4_in = (kb_in + 3) / 4;
+  for (Idx i = blockIdx.x * static_cast<Idx>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<Idx>(gridDim.x) * blockDim.x) {
+    const Idx chunk = i / 512;
     const int off = static_cast<int>(i % 512);
     const int j = off & 3, r_in = ((off >> 2) & 3) * 32 + (off >> 4);
-    const int64_t r = (chunk / kb4_out) * 128 + r_in, b = (chunk % kb4_out) * 4 + j;
+    const Idx cr = chunk / kb4_out;
+    const Idx r = cr * 128 + r_in, b = (chunk - cr * kb4_out) * 4 + j;
     uint8_t v = 0;
     if (r < rows_out && b < kb_out) {
-      const int64_t flat = r * kb_out + b;
-      const int64_t ri = flat / kb_in, bi = flat - ri * kb_in;
+      const Idx flat = r * kb_out + b;
+      const Idx ri = flat / kb_in, bi = flat - ri * kb_in;
       v = in[((ri / 128) * kb4_in + bi / 4) * 512 + tiled_offset(static_cast<int>(ri % 128), static_cast<int>(bi % 4))];
     }
     out[i] = v;
@@ -523,8 +527,15 @@ extern "C" int anima_mx_scales_regroup(const uint8_t* tiled_in, int64_t rows_in,
   if (rows_out == 0) return ANIMA_OK;
   const int64_t total = anima_mx_scales_bytes(rows_out, k_out, ANIMA_SCALES_TILED);
   const int blocks = static_cast<int>(std::min<int64_t>(ceil_div(total, 256), sm_count() * 16));
-  mx_scales_regroup_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(tiled_in, k_in / 32, rows_out,
-                                                                                  k_out / 32, tiled_out);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // 32-bit indices when the padded extents of both tilings (and r * kb_out + b for padded r) stay below 2^31
+  if ((rows_out + 128) * (k_out / 32 + 4) < (1ll << 31) && (rows_in + 128) * (k_in / 32 + 4) < (1ll << 31))
+    mx_scales_regroup_kernel<uint32_t><<<blocks, 256, 0, s>>>(tiled_in, static_cast<uint32_t>(k_in / 32),
+                                                               static_cast<uint32_t>(rows_out),
+                                                               static_cast<uint32_t>(k_out / 32),
+                                                               static_cast<uint32_t>(total), tiled_out);
+  else
+    mx_scales_regroup_kernel<int64_t><<<blocks, 256, 0, s>>>(tiled_in, k_in / 32, rows_out, k_out / 32, total, tiled_out);
   ANIMA_CHECK_LAUNCH("mx_scales_regroup");
   return ANIMA_OK;
 }

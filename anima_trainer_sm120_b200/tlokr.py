@@ -224,6 +224,27 @@ class _StructuredLoKr(torch.autograd.Function):
         return g_x.to(x.dtype), g_c.to(w1.dtype), g_a.to(w2_a.dtype), g_b.to(w2_b.dtype), None
 
 
+def _factor_forms(p: torch.Tensor, *, quantise: bool):
+    """bf16 copy (``quantise=False``) or both MXFP8 operands (``quantise=True``) of a small adapter factor.
+
+    A checkpointed step reads every factor three times with the same values (first pass, recomputation,
+    backward); for a leaf parameter the result is kept on the parameter object, keyed on its in-place version
+    counter and storage address (an optimizer step or a reassigned ``.data`` invalidates it), which removes two
+    thirds of these tiny launches. Sliced or computed factors are converted on every call."""
+    cacheable = p.is_leaf and isinstance(p, nn.Parameter)
+    slot = "_anima_mx_forms" if quantise else "_anima_bf16_form"
+    key = (p._version, p.data_ptr())
+    if cacheable:
+        hit = getattr(p, slot, None)
+        if hit is not None and hit[0] == key:
+            return hit[1]
+    with torch.no_grad():
+        val = _q(p.detach(), col=True) if quantise else p.detach().to(BF16).contiguous()
+    if cacheable:
+        setattr(p, slot, (key, val))
+    return val
+
+
 def _q(t2d: torch.Tensor, *, col: bool = False):
     return ops.mx_quantize(t2d.contiguous() if t2d.dtype == BF16 else t2d.to(BF16).contiguous(),
                            rowwise=True, colwise=col)
@@ -352,12 +373,12 @@ def _mx_linear_fwd(x_row, gq, lead_shape, W_mx, bias, w1, w2_a, w2_b, mask, alph
     (``x_row``) and as the grouped ``[rows * uq, K / uq]`` (``gq``): the same code bytes under two scale tilings.
     Returns (y, small factor operands kept for backward)."""
     from .fp8_quant import _bias_bf16
-    c = w1.to(BF16)
+    c = _factor_forms(w1, quantise=False)
     uq = c.shape[1]
     vp, rank = w2_a.shape
     n_out = W_mx.row.rows
-    aq, aq_col = _q(w2_a.detach(), col=True)      # A [vp, r]: row form for out, column form for dgrad
-    bq, bq_col = _q(w2_b.detach(), col=True)      # B [r, vq]
+    aq, aq_col = _factor_forms(w2_a, quantise=True)      # A [vp, r]: row form for out, column form for dgrad
+    bq, bq_col = _factor_forms(w2_b, quantise=True)      # B [r, vq]
     y = torch.empty(*lead_shape, n_out, dtype=BF16, device=x_row.codes.device)
     ops.mx_gemm(x_row, W_mx.row, bias=_bias_bf16(bias), out=y.view(-1, n_out))
     hidden = ops.mx_gemm(gq, bq).view(lead_shape[0], -1, uq, rank)
@@ -387,7 +408,7 @@ def _mx_linear_bwd(quant_grad, quant_grouped, lead_shape, K, W_mx, w1, w2_a, w2_
     activation) into that quantisation; ``quant_grouped(rows, k)`` returns the operands of the layer input in its
     grouped view (saved by the forward pass). Returns (grad_x bf16 [*lead, K], grad_w1, grad_A, grad_B)."""
     aq_col, bq, bq_col = factor_ops
-    c = w1.to(BF16)
+    c = _factor_forms(w1, quantise=False)
     up, uq = c.shape
     vp, rank = w2_a.shape
     vq = K // uq

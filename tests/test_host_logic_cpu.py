@@ -175,3 +175,27 @@ def test_producer_side_quantisation_is_offered_only_for_shapes_the_kernels_tile(
         assert not adaln_kernel._emits(x, 120, 256)
     finally:
         adaln_kernel.emit_row_operand(False)
+
+
+def test_factor_forms_are_kept_per_parameter_version(monkeypatch):
+    calls = []
+
+    def fake_q(t, *, col=False):
+        calls.append(tuple(t.shape))
+        return ("row", len(calls)), ("col", len(calls))
+
+    monkeypatch.setattr(tlokr, "_q", fake_q)
+    p = torch.nn.Parameter(torch.randn(16, 8))
+    first = tlokr._factor_forms(p, quantise=True)
+    assert tlokr._factor_forms(p, quantise=True) is first and len(calls) == 1      # same values: no new launch
+    c = tlokr._factor_forms(p, quantise=False)
+    assert c.dtype == torch.bfloat16 and tlokr._factor_forms(p, quantise=False) is c
+    with torch.no_grad():
+        p.add_(1.0)                                                               # what an optimizer step does
+    assert tlokr._factor_forms(p, quantise=True) is not first and len(calls) == 2
+    assert tlokr._factor_forms(p, quantise=False) is not c
+    assert torch.equal(tlokr._factor_forms(p, quantise=False), p.detach().to(torch.bfloat16))
+    sliced = p[:, :4]                                                            # computed factors are never kept
+    tlokr._factor_forms(sliced, quantise=True)
+    tlokr._factor_forms(sliced, quantise=True)
+    assert len(calls) == 4
