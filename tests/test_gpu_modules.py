@@ -203,7 +203,7 @@ def test_training_arms_track_each_other(variant):
 def test_scale_regroup_equals_quantising_the_reshaped_tensor():
     from anima_trainer_sm120_b200 import ops
     torch.manual_seed(4)
-    for rows, K, u in ((96, 512, 8), (1024, 2048, 8), (33, 256, 4)):
+    for rows, K, u in ((96, 512, 8), (1024, 2048, 8), (33, 256, 4), (160, 1024, 8), (256, 8192, 8), (72, 1024, 4)):
         x = (torch.randn(rows, K, device=DEV) * 3).to(BF16)
         row, _ = ops.mx_quantize(x, rowwise=True)
         want, _ = ops.mx_quantize(x.view(rows * u, K // u), rowwise=True)
