@@ -88,13 +88,18 @@ adaln_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __res
     __syncthreads();   // far ahead of the first read: two reductions over the row come first
   }
   if (GATED) {
+    // the sublayer output is fetched one chunk ahead of its use (the row of x already fills half the registers)
+    uint4 sub_next = make_uint4(0u, 0u, 0u, 0u);
+    if (lane * 8 < d) sub_next = ldg_stream16(sub + row * d + lane * 8);
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
       const int col = (i * 32 + lane) * 8;
+      const uint4 sub_cur = sub_next;
+      if (i + 1 < NCH && col + 256 < d) sub_next = ldg_stream16(sub + row * d + col + 256);
       if (col < d) {
         float xf[8], yf[8], gf[8], o[8];
         unpack8(raw[i], xf);
-        unpack8(ldg_stream16(sub + row * d + col), yf);
+        unpack8(sub_cur, yf);
         unpack8(*reinterpret_cast<const uint4*>(gate + bt * d + col), gf);
 #pragma unroll
         for (int e = 0; e < 8; ++e) o[e] = xf[e] + gf[e] * yf[e];
