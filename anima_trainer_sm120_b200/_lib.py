@@ -166,3 +166,10 @@ def check_status_word(device: torch.device) -> None:
     if int(w.item()) != 0:
         w.zero_()
         raise RuntimeError("anima_mx_gemm: a bounded wait inside the kernel timed out")
+
+
+def check_quantize_status() -> None:
+    """Synchronising check of the quantiser's bounded-wait flag on the current device."""
+    rc = check(load().anima_mx_quantize_status())
+    if rc != 0:
+        raise RuntimeError("anima_mx_quantize: a bounded wait inside the copy-engine-fed kernel timed out")

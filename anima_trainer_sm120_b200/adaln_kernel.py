@@ -39,12 +39,23 @@ def _flat(t: torch.Tensor, d: int) -> torch.Tensor:
     return t if t.dtype == BF16 else t.to(BF16)
 
 
+def _need_bf16_stream(name: str, *tensors: torch.Tensor) -> None:
+    """The kernels store bf16. The reference's ops keep the input dtype (``torch.empty_like(x_flat)``,
+    adaln_kernel.py:185-187), so an fp32 residual stream would be rounded to bf16 at every sublayer here without
+    notice; it is refused instead (modulation tensors of another dtype are cast, their gradients cast back)."""
+    for t in tensors:
+        if t.dtype != BF16:
+            raise TypeError(f"{name}: activations must be bfloat16, got {t.dtype} (the fused kernels have no "
+                            "fp32-stream form; use the block's unpatched forward for use_fp32)")
+
+
 class FusedAdaLN(torch.autograd.Function):
     """``LayerNorm(x, no affine, eps) * (1 + scale) + shift``."""
 
     @staticmethod
     def forward(ctx, x, scale, shift, eps):
         assert x.is_cuda, "FusedAdaLN requires CUDA tensors"
+        _need_bf16_stream("FusedAdaLN", x)
         B, T, H, W, D = x.shape
         x_flat, scale_flat, shift_flat = _flat(x, D), _flat(scale, D), _flat(shift, D)
         N, M, HW = x_flat.shape[0], scale_flat.shape[0], H * W
@@ -82,6 +93,7 @@ class FusedGatedAdd(torch.autograd.Function):
     def forward(ctx, x, gate, y):
         assert x.is_cuda, "FusedGatedAdd requires CUDA tensors"
         assert x.shape == y.shape, f"x {x.shape} != y {y.shape}"
+        _need_bf16_stream("FusedGatedAdd", x, y)
         B, T, H, W, D = x.shape
         x_flat, y_flat, gate_flat = _flat(x, D), _flat(y, D), _flat(gate, D)
         N, M, HW = x_flat.shape[0], gate_flat.shape[0], H * W
@@ -116,6 +128,7 @@ class FusedGatedAddAdaLN(torch.autograd.Function):
     def forward(ctx, x, gate, sub, scale, shift, eps):
         assert x.is_cuda, "FusedGatedAddAdaLN requires CUDA tensors"
         assert x.shape == sub.shape, f"x {x.shape} != sub {sub.shape}"
+        _need_bf16_stream("FusedGatedAddAdaLN", x, sub)
         B, T, H, W, D = x.shape
         x_flat, sub_flat = _flat(x, D), _flat(sub, D)
         gate_flat, scale_flat, shift_flat = _flat(gate, D), _flat(scale, D), _flat(shift, D)

@@ -25,10 +25,19 @@ def _patched_forward(self, x_B_T_H_W_D: torch.Tensor, emb_B_T_D: torch.Tensor, c
                      attn_params=None, use_fp32: bool = False, rope_emb_L_1_1_D: Optional[torch.Tensor] = None,
                      adaln_lora_B_T_3D: Optional[torch.Tensor] = None,
                      extra_per_block_pos_emb: Optional[torch.Tensor] = None) -> torch.Tensor:
-    x = x_B_T_H_W_D.float() if use_fp32 else x_B_T_H_W_D
+    if use_fp32 or x_B_T_H_W_D.dtype != torch.bfloat16:
+        # The fused kernels read and write bf16. A caller that wants the residual stream carried in fp32
+        # (``use_fp32``; the reference's kernels keep x.dtype, adaln_kernel.py:185-187) gets the block's own
+        # unpatched forward instead of a silently bf16-rounded stream.
+        orig = next((f for cls, f in _PATCHED.items() if isinstance(self, cls)), None)
+        if orig is None:
+            raise TypeError("adaln_patch: the fused Block forward needs a bfloat16 residual stream")
+        return orig(self, x_B_T_H_W_D, emb_B_T_D, crossattn_emb, attn_params, use_fp32, rope_emb_L_1_1_D,
+                    adaln_lora_B_T_3D, extra_per_block_pos_emb)
+    x = x_B_T_H_W_D
     if extra_per_block_pos_emb is not None:
         x = x + extra_per_block_pos_emb
-    ctx = torch.autocast(device_type=x.device.type, dtype=torch.float32) if use_fp32 else contextlib.nullcontext()
+    ctx = contextlib.nullcontext()
     lora = adaln_lora_B_T_3D if self.use_adaln_lora else None
     with ctx:
         if getattr(self, "_adaln_modulation_merged", False):

@@ -157,7 +157,7 @@ class Block(nn.Module):
 
     def _forward(self, x_B_T_H_W_D, emb_B_T_D, crossattn_emb, attn_params=None, use_fp32=False,
                  rope_emb_L_1_1_D=None, adaln_lora_B_T_3D=None, extra_per_block_pos_emb=None):
-        x = x_B_T_H_W_D
+        x = x_B_T_H_W_D.float() if use_fp32 else x_B_T_H_W_D     # fp32 residual stream on request
         if extra_per_block_pos_emb is not None:
             x = x + extra_per_block_pos_emb
         B, T, H, W, D = x.shape

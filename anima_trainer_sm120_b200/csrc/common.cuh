@@ -14,6 +14,7 @@
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
+#include <mutex>
 
 #include "../../include/anima_b200.h"
 
@@ -44,6 +45,26 @@ __host__ __device__ static inline int64_t ceil_div(int64_t a, int64_t b) { retur
 
 // Number of SMs of the current device (cached per device).
 int sm_count();
+
+// Runs `f` (which returns a cudaError_t) once per CUDA device, with that device current, and remembers a
+// success. cudaFuncAttributeMaxDynamicSharedMemorySize belongs to a kernel's image in ONE device's context, so
+// a process that uses several GPUs has to opt every kernel in on each of them.
+struct PerDeviceOnce {
+  std::mutex mu;
+  bool done[64] = {};
+};
+template <class F>
+cudaError_t per_device_once(PerDeviceOnce& st, F&& f) {
+  int dev = 0;
+  cudaError_t rc = cudaGetDevice(&dev);
+  if (rc != cudaSuccess) return rc;
+  if (dev < 0 || dev >= 64) return f();
+  std::lock_guard<std::mutex> lock(st.mu);
+  if (st.done[dev]) return cudaSuccess;
+  rc = f();
+  if (rc == cudaSuccess) st.done[dev] = true;
+  return rc;
+}
 
 // ---- device helpers ------------------------------------------------------------
 #if defined(__CUDACC__)

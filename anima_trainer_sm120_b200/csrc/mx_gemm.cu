@@ -821,10 +821,9 @@ bool make_c_map(CUtensorMap* map, const GemmParams& p) {
 }
 
 int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmParams p, cudaStream_t s) {
-  static std::once_flag once;
-  static cudaError_t attr_rc = cudaSuccess;
-  std::call_once(once, [] {
-    attr_rc = cudaFuncSetAttribute(mx_gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg2::kSmemBytes);
+  static PerDeviceOnce once;
+  const cudaError_t attr_rc = per_device_once(once, [] {
+    return cudaFuncSetAttribute(mx_gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg2::kSmemBytes);
   });
   ANIMA_REQUIRE(attr_rc == cudaSuccess, ANIMA_E_CUDA, "mx_gemm: cannot reserve %d bytes of shared memory: %s",
                 Cfg2::kSmemBytes, cudaGetErrorString(attr_rc));
@@ -862,11 +861,10 @@ int forced_variant() {
 
 template <int BN>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, cudaStream_t s) {
-  static std::once_flag once;
-  static cudaError_t attr_rc = cudaSuccess;
-  std::call_once(once, [] {
-    attr_rc = cudaFuncSetAttribute(mx_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   Cfg<BN>::kSmemBytes);
+  static PerDeviceOnce once;
+  const cudaError_t attr_rc = per_device_once(once, [] {
+    return cudaFuncSetAttribute(mx_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                Cfg<BN>::kSmemBytes);
   });
   ANIMA_REQUIRE(attr_rc == cudaSuccess, ANIMA_E_CUDA, "mx_gemm: cannot reserve %d bytes of shared memory: %s",
                 Cfg<BN>::kSmemBytes, cudaGetErrorString(attr_rc));

@@ -388,11 +388,10 @@ bool make_x_map(CUtensorMap* map, const void* x, int64_t rows, int64_t cols, int
 template <bool ROW, bool COL, class Loader>
 int launch_tma(const CUtensorMap& map, const QuantParams& p, const Loader& load, unsigned grid, cudaStream_t s) {
   constexpr int kBytes = kTmaSmemBytes + ((Loader::kSmemBytes + 127) & ~127);
-  static std::once_flag once;
-  static cudaError_t attr_rc = cudaSuccess;
-  std::call_once(once, [] {
-    attr_rc = cudaFuncSetAttribute(mx_quantize_tma_kernel<ROW, COL, Loader>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   kBytes);
+  static PerDeviceOnce once;
+  const cudaError_t attr_rc = per_device_once(once, [] {
+    return cudaFuncSetAttribute(mx_quantize_tma_kernel<ROW, COL, Loader>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                kBytes);
   });
   ANIMA_REQUIRE(attr_rc == cudaSuccess, ANIMA_E_CUDA, "mx_quantize: cannot reserve %d bytes of shared memory: %s",
                 kBytes, cudaGetErrorString(attr_rc));
@@ -441,7 +440,12 @@ extern "C" int anima_mx_quantize_status(void) {
   int flag = 0;
   const cudaError_t rc = cudaMemcpyFromSymbol(&flag, g_quantize_timeout, sizeof(int));   // synchronises
   ANIMA_REQUIRE(rc == cudaSuccess, ANIMA_E_CUDA, "mx_quantize_status: %s", cudaGetErrorString(rc));
-  return flag;
+  if (flag) {  // reported once: clear it so that a later check speaks about later launches
+    const int zero = 0;
+    const cudaError_t rc2 = cudaMemcpyToSymbol(g_quantize_timeout, &zero, sizeof(int));
+    ANIMA_REQUIRE(rc2 == cudaSuccess, ANIMA_E_CUDA, "mx_quantize_status: %s", cudaGetErrorString(rc2));
+  }
+  return flag ? 1 : 0;
 }
 
 extern "C" int anima_mx_quantize(const void* x, int64_t rows, int64_t cols, int64_t ld,

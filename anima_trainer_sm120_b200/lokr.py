@@ -112,6 +112,62 @@ class LokrNetwork(nn.Module):
         for m in self.unet_loras:
             m.apply_to()
 
+    # A LyCORIS network serialises ``{lora_name}.{key}`` from every module's ``custom_state_dict()`` (which the
+    # forward patch extends with the T-LoKr marker); this is the key set the adapter file carries.
+    def state_dict(self, *args, destination=None, prefix: str = "", keep_vars: bool = False):
+        sd = {} if destination is None else destination
+        for m in self.unet_loras:
+            for k, v in m.custom_state_dict().items():
+                sd[f"{prefix}{m.lora_name}.{k}"] = v if keep_vars else v.detach()
+        return sd
+
+    def load_state_dict(self, state_dict, strict: bool = True, assign: bool = False):
+        """Copy an adapter state into the modules. ``alpha`` updates the module's scale; a ``tlokr_schedule``
+        that differs from the module's is an error (anima-trainer ``tlokr.py:305-327``), as are shape
+        mismatches and, with ``strict``, missing or unexpected keys."""
+        from torch.nn.modules.module import _IncompatibleKeys
+
+        expected = self.state_dict(keep_vars=True)
+        missing = [k for k in expected if k not in state_dict]
+        unexpected = [k for k in state_dict if k not in expected]
+        errors: list[str] = []
+        by_name = {m.lora_name: m for m in self.unet_loras}
+        with torch.no_grad():
+            for key, dst in expected.items():
+                src = state_dict.get(key)
+                if src is None:
+                    continue
+                name, leaf = key.rsplit(".", 1)
+                mod = by_name[name]
+                if leaf == "tlokr_schedule":
+                    want = dst.detach().to("cpu", torch.int64)
+                    got = src.detach().to("cpu", torch.int64)
+                    if got.shape != want.shape or not torch.equal(got, want):
+                        errors.append(f"{key} is incompatible: checkpoint has {got.tolist()}, "
+                                      f"model expects {want.tolist()}")
+                    continue
+                if leaf == "alpha":
+                    if src.numel() != 1:
+                        errors.append(f"{key}: alpha must be a scalar, got shape {tuple(src.shape)}")
+                        continue
+                    mod.scale = float(src) / float(mod.lora_dim)
+                    if getattr(mod, "_tlokr_enabled", False):
+                        scalar = mod.scalar.item() if torch.is_tensor(mod.scalar) else mod.scalar
+                        mod._tlokr_alpha = float(mod.scale) * float(scalar) * float(mod.multiplier)
+                    continue
+                if tuple(src.shape) != tuple(dst.shape):
+                    errors.append(f"size mismatch for {key}: checkpoint {tuple(src.shape)}, model {tuple(dst.shape)}")
+                    continue
+                dst.copy_(src.to(device=dst.device, dtype=dst.dtype))
+        if strict:
+            if unexpected:
+                errors.insert(0, "Unexpected key(s) in state_dict: " + ", ".join(map(repr, unexpected)))
+            if missing:
+                errors.insert(0, "Missing key(s) in state_dict: " + ", ".join(map(repr, missing)))
+        if errors:
+            raise RuntimeError("Error(s) in loading state_dict for LokrNetwork:\n\t" + "\n\t".join(errors))
+        return _IncompatibleKeys(missing, unexpected)
+
 
 def attach_lokr(dit: nn.Module, *, preset: str = "anima-cross-mlp", factor: int = 8, dim: int = 128,
                 alpha: float = 128.0, full_matrix: bool = True, variant: str = "lokr",

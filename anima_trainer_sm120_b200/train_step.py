@@ -26,7 +26,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
-from . import adaln_kernel, adaln_merge, adaln_patch, lokr_patch, mlp_patch, qk_norm_rope
+from . import adaln_kernel, adaln_merge, adaln_patch, lokr_patch, mlp_patch, precision, qk_norm_rope
 from .anima_dit import AnimaConfig, AnimaDiT, Attention, Block, GPT2FeedForward
 from .lokr import attach_lokr
 
@@ -52,6 +52,8 @@ class StepConfig:
     gradient_checkpointing: bool = True
     max_grad_norm: float = 1.0
     seed: int = 42
+    grad_bucket_blocks: int = 4       # DP: adapter gradients of this many DiT blocks travel in one all-reduce
+    status_check_every: int = 1       # steps between reads of the kernels' bounded-wait status words (0 = never)
 
 
 class Trainer:
@@ -120,6 +122,68 @@ class Trainer:
             off += p.numel()
         self.opt = torch.optim.AdamW(self.params, lr=cfg.lr, betas=(0.9, 0.99), weight_decay=0.0)
         self.step_idx = 0
+        self.autocast_mode = "bf16" if cfg.precision.startswith("bf16") else "mxfp8"
+        self.last_allreduce_exposed_ms: float | None = None
+        self._build_buckets()
+
+    # ---------------------------------------------------------------- data-parallel exchange
+    def _build_buckets(self) -> None:
+        """Split the flat gradient into contiguous buckets of ``grad_bucket_blocks`` DiT blocks each. Backward
+        retires the blocks last to first; a hook on every parameter counts its bucket down and the bucket's
+        all-reduce is launched (asynchronously: the communication library runs it on its own stream, ordered
+        after the kernels that produced the bucket) the moment its last gradient has been accumulated, so the
+        exchange of all but the first blocks' gradients hides under the rest of backward."""
+        self._buckets: list[tuple[int, int]] = []          # (start, end) offsets into flat_grad
+        self._bucket_of: dict[int, int] = {}               # id(param) -> bucket index
+        self._bucket_size: list[int] = []
+        self._pending: list[int] = []
+        self._works: list = []
+        if self.world == 1:
+            return
+        per_bucket = max(1, int(self.cfg.grad_bucket_blocks))
+        n_mod_per_block = max(1, len(self.network.unet_loras) // max(1, self.model_cfg.depth))
+        params_per_module = len(self.params) // max(1, len(self.network.unet_loras))
+        group = max(1, n_mod_per_block * params_per_module * per_bucket)
+        off = 0
+        for i in range(0, len(self.params), group):
+            chunk = self.params[i:i + group]
+            n = sum(p.numel() for p in chunk)
+            for p in chunk:
+                self._bucket_of[id(p)] = len(self._buckets)
+            self._buckets.append((off, off + n))
+            self._bucket_size.append(len(chunk))
+            off += n
+        for p in self.params:
+            p.register_post_accumulate_grad_hook(self._on_grad_ready)
+
+    def _on_grad_ready(self, p: torch.Tensor) -> None:
+        if not self._pending:
+            return                                         # a backward outside step(): nothing to exchange
+        b = self._bucket_of[id(p)]
+        self._pending[b] -= 1
+        if self._pending[b] == 0:
+            lo, hi = self._buckets[b]
+            self._works.append(dist.all_reduce(self.flat_grad[lo:hi], async_op=True))
+
+    def _finish_exchange(self) -> None:
+        """Launch what the hooks did not (a parameter that received no gradient keeps its bucket open), wait for
+        every bucket and average."""
+        for b, left in enumerate(self._pending):
+            if left > 0:
+                lo, hi = self._buckets[b]
+                self._works.append(dist.all_reduce(self.flat_grad[lo:hi], async_op=True))
+        self._pending = []
+        timed = self.device.type == "cuda"
+        if timed:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        for w in self._works:
+            w.wait()
+        self._works = []
+        if timed:
+            e1.record()
+            self._exchange_events = (e0, e1)
+        self.flat_grad.mul_(1.0 / self.world)
 
     # ---------------------------------------------------------------- data
     def synthetic_batch(self, batch: int, latent_hw: int, text_tokens: int, step: int):
@@ -137,25 +201,54 @@ class Trainer:
         noisy, target, t = noisy_input_and_target(latents, g)
         if self.tlokr:
             self._tlokr.set_timestep(t)
-        with torch.autocast(device_type=self.device.type, dtype=torch.bfloat16):
+        with precision.autocast_for(self.autocast_mode, self.device.type), precision.fp8_autocast_for(self.autocast_mode):
             pred = self.dit(noisy, t, ctx)
         return F.mse_loss(pred.float(), target.float())
 
     def step(self, latents, ctx, noise_seed: int) -> float:
         self.flat_grad.zero_()
+        if self.world > 1:
+            self._pending = list(self._bucket_size)
         try:
             loss = self.forward_and_loss(latents, ctx, noise_seed)
             loss.backward()
         finally:
             if self.tlokr:
                 self._tlokr.clear_timestep()
+            if self.world > 1 and not self._works and self._pending == self._bucket_size:
+                self._pending = []              # forward or backward raised before any bucket left
         if self.world > 1:                      # the only exchange of the data-parallel step
-            dist.all_reduce(self.flat_grad)
-            self.flat_grad.mul_(1.0 / self.world)
+            self._finish_exchange()
         torch.nn.utils.clip_grad_norm_(self.params, self.cfg.max_grad_norm)
         self.opt.step()
         self.step_idx += 1
-        return float(loss.detach())
+        value = float(loss.detach())            # synchronises: everything the step launched has run
+        ev = getattr(self, "_exchange_events", None)
+        if ev is not None:
+            self.last_allreduce_exposed_ms = ev[0].elapsed_time(ev[1])
+            self._exchange_events = None
+        every = self.cfg.status_check_every
+        if self.cfg.precision == "mxfp8" and every and self.step_idx % every == 0:
+            self.check_kernel_status()
+        return value
+
+    def check_kernel_status(self) -> None:
+        """Raise if a bounded wait inside one of the library's kernels gave up since the last check (its outputs
+        are then undefined, and so are this step's loss and update). Call after a synchronisation."""
+        from . import _lib
+        _lib.check_status_word(self.device)
+        _lib.check_quantize_status()
+
+    # ---------------------------------------------------------------- adapter file
+    def save(self, path) -> int:
+        """Publish the adapter file (rank 0 writes, every rank waits; ``adapter_io.save_adapter``)."""
+        from .adapter_io import save_adapter
+        return save_adapter(self.network, path)
+
+    def load(self, path) -> dict:
+        """Load an adapter file on every rank (``adapter_io.load_adapter``)."""
+        from .adapter_io import load_adapter
+        return load_adapter(self.network, path)
 
     def run(self, steps: int, batch: int, latent_hw: int, text_tokens: int) -> list[float]:
         losses = []

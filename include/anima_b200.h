@@ -71,8 +71,9 @@ int anima_mx_quantize(const void* x_bf16, int64_t rows, int64_t cols, int64_t ld
                       uint8_t* codes_colT, uint8_t* scales_col,
                       int scale_layout, void* stream);
 
-/* 0, or 1 if a bounded wait inside the copy-engine-fed quantiser kernel ever gave up on the current device
- * (its outputs are then undefined); negative on a CUDA error. Synchronises: for tests and debugging. */
+/* 0, or 1 if a bounded wait inside the copy-engine-fed quantiser kernel gave up on the current device since the
+ * last call that returned 1 (the outputs of that launch are undefined; the flag is cleared when it is reported);
+ * negative on a CUDA error. Synchronises: call it where the host waits anyway (after a step's loss is read). */
 int anima_mx_quantize_status(void);
 
 /* Quantise an MLP activation without materialising it (no reference counterpart: the reference
