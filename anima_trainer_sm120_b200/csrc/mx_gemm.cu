@@ -31,7 +31,10 @@
 #include <cuda.h>
 
 #include <cstdlib>
+#include <map>
 #include <mutex>
+#include <tuple>
+#include <vector>
 
 #include "common.cuh"
 #include "tma_util.cuh"
@@ -130,21 +133,72 @@ struct GemmParams {
   const __nv_bfloat16* residual;
   int64_t ldr;
   float alpha;
+  // Work list of the CTA-pair kernel (see PairPlan below): tile columns 0 .. n_wide-1 are 192 wide; if
+  // `narrow`, one more column of at most 128 valid outputs follows and is computed with N = 128 instructions.
+  // Items 0 .. full_items-1 are whole tiles (wide ones first, narrow ones after them), dealt round-robin to the
+  // pairs (full_items is a multiple of the pair count). The tail_tiles tiles after them are each split along K
+  // into tail_splits ranges of tail_kbs K-blocks; those items are dealt round-robin starting at pair tail_shift
+  // and leave as fp32 partial tiles in pair_partial [item][256][192], summed by pair_tail_finalize_kernel.
+  int n_wide, narrow;
+  int full_items, tail_tiles, tail_splits, tail_kbs, tail_shift;
+  float* pair_partial;
+  int sf_bufs;  // tensor-memory scale buffers the K-blocks rotate through (1, 2 or 4)
 };
 
 
-// Tile order of the CTA-pair kernel. The tiles that run at the same time should cover the SHORTER side of
-// the tile grid completely, so that the operand of the longer side is streamed once instead of once per
-// tile row: with n fastest, the wgrad dW[2048, 8192] (8 x 43 tiles) re-read its 268 MB B operand 8 times and
-// ran HBM-bound. The index along the shorter side varies fastest.
+// Tile order of the CTA-pair kernel. Wide tiles come first, the narrow last column after them (cheaper items at
+// the end balance the round robin). Inside the wide region the tiles that run at the same time should cover the
+// SHORTER side of the tile grid completely, so that the operand of the longer side is streamed once instead of
+// once per tile row: with n fastest, the wgrad dW[2048, 8192] (8 x 43 tiles) re-read its 268 MB B operand 8
+// times and ran HBM-bound. The index along the shorter side varies fastest.
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& mt, int& nt) {
-  if (p.m_tiles < p.n_tiles) {
+  const int wide = p.m_tiles * p.n_wide;
+  if (tile >= wide) {
+    mt = tile - wide;
+    nt = p.n_wide;
+  } else if (p.m_tiles < p.n_wide) {
     nt = tile / p.m_tiles;
     mt = tile - nt * p.m_tiles;
   } else {
-    mt = tile / p.n_tiles;
-    nt = tile - mt * p.n_tiles;
+    mt = tile / p.n_wide;
+    nt = tile - mt * p.n_wide;
   }
+}
+
+// One unit of work of a CTA pair: a whole tile (part < 0) or the K-range [kb0, kb1) of a tail tile, whose fp32
+// partial goes to slot `part`. valid == false marks a padding slot of the round robin (nothing to do).
+struct PairItem {
+  int mt, nt, kb0, kb1, part;
+  bool valid;
+};
+__device__ __forceinline__ int pair_total_slots(const GemmParams& p) {
+  const int split_items = p.tail_tiles * p.tail_splits;
+  return p.full_items + (split_items ? p.tail_shift + split_items : 0);
+}
+__device__ __forceinline__ PairItem pair_item(const GemmParams& p, int slot) {
+  PairItem it;
+  it.kb0 = 0;
+  it.kb1 = p.k_blocks;
+  it.part = -1;
+  it.valid = true;
+  int tile = slot;
+  if (slot >= p.full_items) {
+    const int r = slot - p.full_items - p.tail_shift;
+    if (r < 0) {
+      it.valid = false;
+      it.mt = it.nt = 0;
+      return it;
+    }
+    const int t = r / p.tail_splits, sp = r - t * p.tail_splits;
+    tile = p.full_items + t;
+    if (p.tail_splits > 1) {
+      it.kb0 = sp * p.tail_kbs;
+      it.kb1 = min(p.k_blocks, it.kb0 + p.tail_kbs);
+      it.part = r;
+    }
+  }
+  tile_coords(p, tile, it.mt, it.nt);
+  return it;
 }
 
 // Epilogue store of one 32-column accumulator chunk of one row: bias, rounding, predicated 16-byte stores.
@@ -423,8 +477,7 @@ struct Cfg2 {
   static constexpr int kABytes = 128 * BK;
   static constexpr int kBBytes = (kBN2 / 2) * BK;  // this CTA's half of the B rows
   static constexpr int kAcc1Col = kBN2;            // second accumulator buffer
-  static constexpr int kSfaCol = 2 * kBN2;         // 4 columns
-  static constexpr int kSfbCol = kSfaCol + 4;      // 8 columns: two 128-column chunks
+  static constexpr int kSfaCol = 2 * kBN2;         // scale buffers: 16 columns each (SFA 4, SFB 2 x 4), up to 4 of them
   static constexpr int kTmemCols = 512;
   static constexpr int kSfBytes = kSfChunk * 3;  // SFA chunk + both SFB chunks
   static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
@@ -477,11 +530,16 @@ __device__ __forceinline__ void tc2_commit_both(uint32_t bar) {
 // M256 x N192 x K32 block-scaled MMAs (scale-factor id k selects the k-th byte of each scale word;
 // +32 bytes along K = +2 in the descriptor's 16-byte address field), then the commit that frees the
 // stage in both CTAs. Descriptor high words: stride 1024 B (operands, 128-byte swizzle) / 128 B (scales).
+// Instruction descriptor of the pair kernel without the scale-factor ids: e4m3 x e4m3, K-major, ue8m0 scales,
+// M = 256, N = n (192, or 128 for the narrow last tile column).
+__device__ __forceinline__ uint32_t pair_idesc(int n) {
+  return (static_cast<uint32_t>(n >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>(256 >> 4) << 24);
+}
 __device__ __forceinline__ void tc2_kblock(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t sf_lo, uint32_t sfa_t,
-                                           uint32_t sfb_t, uint32_t sfb_use, uint32_t accumulate, uint32_t empty_bar) {
+                                           uint32_t sfb_t, uint32_t sfb_use, uint32_t accumulate, uint32_t empty_bar,
+                                           uint32_t kI) {
   constexpr uint32_t kOpHi = (1024u >> 4) | (1u << 14) | (2u << 29);
   constexpr uint32_t kSfHi = (128u >> 4) | (1u << 14);
-  constexpr uint32_t kI = (static_cast<uint32_t>(kBN2 >> 3) << 17) | (1u << 23) | (static_cast<uint32_t>(256 >> 4) << 24);
   asm volatile(
       "{\n\t"
       ".reg .pred p, pt;\n\t"
@@ -529,7 +587,8 @@ __device__ __forceinline__ void tc2_kblock(uint32_t d_tmem, uint32_t a_lo, uint3
 __global__ void __launch_bounds__(kThreads, 1)
 mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
-                const __grid_constant__ CUtensorMap map_c, const GemmParams p) {
+                const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_part,
+                const GemmParams p) {
   using C = Cfg2;
   extern __shared__ uint8_t smem_raw[];
   __shared__ volatile int abort_flag;
@@ -568,6 +627,7 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfa) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_sfb) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
+    if (p.tail_splits > 1) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_part) : "memory");
   }
   if (warp == 1) {  // the same warp of both CTAs performs the pair allocation
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
@@ -583,7 +643,7 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   // every tensor-memory address warp-uniform. Anything else is reported through *status and nothing runs.
   const uint32_t tmem_alloc = tmem_base_slot;
   constexpr uint32_t tmem_base = 0;
-  const int total_tiles = (tmem_alloc == 0) ? p.m_tiles * p.n_tiles : 0;  // 256 x 192 tiles
+  const int total_slots = (tmem_alloc == 0) ? pair_total_slots(p) : 0;
   if (tmem_alloc != 0 && threadIdx.x == 0 && p.status) atomicExch(p.status, 2);
 
   // Warps 0 and 1 run their loops with all 32 lanes so that every loop variable is warp-uniform (the
@@ -596,13 +656,14 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       uint32_t ph = 0;
       bool ok = true;
       const uint32_t leader_full0 = map_to_cta(full_bar(0), 0);
-      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
-        int mt, nt;
-        tile_coords(p, tile, mt, nt);
-        const int row_a = mt * 256 + static_cast<int>(rank) * 128;
-        const int row_b = nt * kBN2 + static_cast<int>(rank) * (kBN2 / 2);
-        const int sfa_rt = mt * 2 + static_cast<int>(rank), sfb_rt = (nt * kBN2) >> 7;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+      for (int slot = pair; slot < total_slots && ok; slot += num_pairs) {
+        const PairItem it = pair_item(p, slot);
+        if (!it.valid) continue;
+        const bool narrow = it.nt >= p.n_wide;  // N = 128 instruction: each CTA supplies 64 rows of B
+        const int row_a = it.mt * 256 + static_cast<int>(rank) * 128;
+        const int row_b = it.nt * kBN2 + static_cast<int>(rank) * (narrow ? 64 : kBN2 / 2);
+        const int sfa_rt = it.mt * 2 + static_cast<int>(rank), sfb_rt = (it.nt * kBN2) >> 7;
+        for (int kb = it.kb0; kb < it.kb1; ++kb) {
           if (!mbar_try_wait(empty_bar(s), ph ^ 1u)) ok = mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
@@ -610,7 +671,7 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             if (rank == 0) mbar_expect_tx(full_bar(s), Cfg2::kTxBytes);
             const uint32_t leader_full = leader_full0 + 8 * s;
             tma2_load_2d(a_smem(s), &map_a, leader_full, kb * BK, row_a);
-            tma2_load_2d(b_smem(s), &map_b, leader_full, kb * BK, row_b);
+            tma2_load_2d(b_smem(s), &map_b, leader_full, kb * BK, row_b);  // 96-row box; rows past N read as 0
             tma2_load_3d(sfa_smem(s), &map_sfa, leader_full, 0, kb, sfa_rt);
             tma2_load_3d(sfb_smem(s), &map_sfb, leader_full, 0, kb, sfb_rt);  // the two 128-column chunks it spans
           }
@@ -624,38 +685,46 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (rank == 0) {
       const uint32_t a_lo0 = (a_smem(0) >> 4) & 0x3fffu;
       const uint32_t sf_lo0 = (sfa_smem(0) >> 4) & 0x3fffu;
-      const uint32_t sfa_t = tmem_base + C::kSfaCol, sfb_t = tmem_base + C::kSfbCol;
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      int it = 0;
-      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++it) {
-        const int as = it & 1;
-        // the epilogues of both CTAs must have drained this buffer (used by tile it - 2)
-        ok = __all_sync(0xffffffffu, mbar_wait(acc_empty_bar(as), ((it >> 1) & 1u) ^ 1u, &abort_flag));
+      int it_n = 0;
+      uint32_t sf_rot = 0;  // scale buffer of the next K-block
+      const uint32_t sf_mask = static_cast<uint32_t>(p.sf_bufs - 1);
+      for (int slot = pair; slot < total_slots && ok; slot += num_pairs) {
+        const PairItem it = pair_item(p, slot);
+        if (!it.valid) continue;
+        const int as = it_n & 1;
+        // the epilogues of both CTAs must have drained this buffer (used by item it_n - 2)
+        ok = __all_sync(0xffffffffu, mbar_wait(acc_empty_bar(as), ((it_n >> 1) & 1u) ^ 1u, &abort_flag));
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (as ? C::kAcc1Col : 0);
-        int mt_unused, nt;
-        tile_coords(p, tile, mt_unused, nt);
-        // a 192-column tile starts 0 or 64 columns into its first 128-column scale chunk: 32 columns per TMEM column
-        const uint32_t sfb_use = sfb_t + (((nt * kBN2) & 127) >> 5);
+        const uint32_t idesc = pair_idesc(it.nt >= p.n_wide ? 128 : kBN2);
+        // a tile starts 0 or 64 columns into its first 128-column scale chunk: 32 columns per TMEM column
+        const uint32_t sfb_off = ((it.nt * kBN2) & 127) >> 5;
         uint32_t acc = 0;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = it.kb0; kb < it.kb1; ++kb) {
           if (!mbar_try_wait(full_bar(s), ph)) ok = mbar_wait(full_bar(s), ph, &abort_flag);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_lo = a_lo0 + s * ((Cfg2::kABytes + Cfg2::kBBytes) >> 4);
           const uint32_t sf_lo = sf_lo0 + s * (Cfg2::kSfBytes >> 4);
+          // The scale columns rotate so that the copy for this K-block need not wait for the MMAs of the
+          // previous one to have read theirs.
+          const uint32_t sfa_t = tmem_base + C::kSfaCol + 16u * sf_rot, sfb_t = sfa_t + 4;
           if (elect_one())
-            tc2_kblock(d_tmem, a_lo, a_lo + (Cfg2::kABytes >> 4), sf_lo, sfa_t, sfb_t, sfb_use, acc, empty_bar(s));
+            tc2_kblock(d_tmem, a_lo, a_lo + (Cfg2::kABytes >> 4), sf_lo, sfa_t, sfb_t, sfb_t + sfb_off, acc, empty_bar(s),
+                       idesc);
           __syncwarp();
           acc = 1;
+          sf_rot = (sf_rot + 1) & sf_mask;
           if (++s == kStages2) { s = 0; ph ^= 1u; }
         }
         if (ok && elect_one()) tc2_commit_both(acc_full_bar(as));
         __syncwarp();
+        ++it_n;
       }
     }
   } else {
@@ -671,57 +740,67 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const bool issuer = threadIdx.x == 64;
     const uint32_t leader_empty[2] = {map_to_cta(acc_empty_bar(0), 0), map_to_cta(acc_empty_bar(1), 0)};
     bool ok = true;
-    int it = 0;
+    int it_n = 0;
     uint32_t buf = 0;
-    for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++it) {
-      int mt, nt;
-      tile_coords(p, tile, mt, nt);
-      const int as = it & 1;
-      if (!mbar_wait(acc_full_bar(as), (it >> 1) & 1u, &abort_flag, 200)) { ok = false; break; }
+    for (int slot = pair; slot < total_slots && ok; slot += num_pairs) {
+      const PairItem it = pair_item(p, slot);
+      if (!it.valid) continue;
+      const int as = it_n & 1;
+      if (!mbar_wait(acc_full_bar(as), (it_n >> 1) & 1u, &abort_flag, 200)) { ok = false; break; }
+      ++it_n;
       tc_fence_after();
-      const int row0 = mt * 256 + static_cast<int>(rank) * 128;
+      const bool partial = it.part >= 0;  // a K-range of a tail tile: raw fp32 accumulators to the scratch tile
+      const int row0 = partial ? it.part * 256 + static_cast<int>(rank) * 128 : it.mt * 256 + static_cast<int>(rank) * 128;
+      const int col_base = partial ? 0 : it.nt * kBN2;
+      const int chunks = it.nt >= p.n_wide ? 4 : kBN2 / 32;  // the narrow column accumulates 128 columns only
+      const bool fp32_stage = partial || p.out_fp32;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + (as ? C::kAcc1Col : 0);
 #pragma unroll 1
-      for (int chunk = 0; chunk < kBN2 / 32; ++chunk, buf ^= 1u) {
+      for (int chunk = 0; chunk < chunks; ++chunk, buf ^= 1u) {
         uint32_t v[32];
         tc_ld32(t_row + chunk * 32, v);
         tc_wait_ld();
-        if (chunk == kBN2 / 32 - 1) {  // buffer fully read: hand it back to the MMA warp
+        if (chunk == chunks - 1) {  // buffer fully read: hand it back to the MMA warp
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(leader_empty[as]);
         }
-        const int col0 = nt * kBN2 + chunk * 32;
+        const int col0 = col_base + chunk * 32;
         float f[32];
+        if (partial) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
-        if (p.bias) {
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+        } else {
 #pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            if (col0 + j < p.N) {
-              float bv[8];
-              unpack8(*reinterpret_cast<const uint4*>(p.bias + col0 + j), bv);
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * p.alpha;
+          if (p.bias) {
 #pragma unroll
-              for (int e = 0; e < 8; ++e) f[j + e] += bv[e];
+            for (int j = 0; j < 32; j += 8) {
+              if (col0 + j < p.N) {
+                float bv[8];
+                unpack8(*reinterpret_cast<const uint4*>(p.bias + col0 + j), bv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[j + e] += bv[e];
+              }
             }
           }
-        }
-        if (p.residual && !reduce_add && row0 + r_in < p.M) {
-          const __nv_bfloat16* res = p.residual + static_cast<int64_t>(row0 + r_in) * p.ldr + col0;
+          if (p.residual && !reduce_add && row0 + r_in < p.M) {
+            const __nv_bfloat16* res = p.residual + static_cast<int64_t>(row0 + r_in) * p.ldr + col0;
 #pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            if (col0 + j < p.N) {
-              float bv[8];
-              unpack8(*reinterpret_cast<const uint4*>(res + j), bv);
+            for (int j = 0; j < 32; j += 8) {
+              if (col0 + j < p.N) {
+                float bv[8];
+                unpack8(*reinterpret_cast<const uint4*>(res + j), bv);
 #pragma unroll
-              for (int e = 0; e < 8; ++e) f[j + e] += bv[e];
+                for (int e = 0; e < 8; ++e) f[j + e] += bv[e];
+              }
             }
           }
         }
         const uint32_t stage = store_base + buf * Cfg2::kStoreBytes;
         // the store that last read this staging buffer (two chunks ago) was waited for by the issuer
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (p.out_fp32) {  // 128-byte rows, 128-byte swizzle: 16-byte piece j of row r sits at piece j ^ (r & 7)
+        if (fp32_stage) {  // 128-byte rows, 128-byte swizzle: 16-byte piece j of row r sits at piece j ^ (r & 7)
           const uint32_t rb = stage + r_in * 128;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
@@ -745,7 +824,11 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the TMA engine
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (issuer) {
-          if (reduce_add)
+          if (partial)
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&map_part),
+                         "r"(stage), "r"(col0), "r"(row0)
+                         : "memory");
+          else if (reduce_add)
             asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
                              &map_c),
                          "r"(stage), "r"(col0), "r"(row0)
@@ -774,6 +857,50 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_alloc), "r"(C::kTmemCols) : "memory");
+  }
+}
+
+// C tile = sum over the K-range partials of a tail tile, in index order (reproducible), then the epilogue
+// (alpha, bias, residual, rounding). One thread per 4 columns of a 256 x 192 tile.
+__global__ void __launch_bounds__(256) pair_tail_finalize_kernel(const GemmParams p) {
+  constexpr int kPerRow = kBN2 / 4, kPerTile = 256 * kPerRow, kTileElems = 256 * kBN2;
+  const int64_t total = static_cast<int64_t>(p.tail_tiles) * kPerTile;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i / kPerTile), r = static_cast<int>(i - static_cast<int64_t>(t) * kPerTile);
+    const int row_in = r / kPerRow, c4 = (r - row_in * kPerRow) * 4;
+    int mt, nt;
+    tile_coords(p, p.full_items + t, mt, nt);
+    const int row = mt * 256 + row_in, col = nt * kBN2 + c4;
+    if (row >= p.M || col >= p.N) continue;
+    const float* src = p.pair_partial + static_cast<int64_t>(t) * p.tail_splits * kTileElems + row_in * kBN2 + c4;
+    float4 acc = *reinterpret_cast<const float4*>(src);
+    for (int sp = 1; sp < p.tail_splits; ++sp) {
+      const float4 v = *reinterpret_cast<const float4*>(src + static_cast<int64_t>(sp) * kTileElems);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    acc.x *= p.alpha; acc.y *= p.alpha; acc.z *= p.alpha; acc.w *= p.alpha;
+    if (p.bias) {
+      acc.x += __bfloat162float(p.bias[col]);
+      acc.y += __bfloat162float(p.bias[col + 1]);
+      acc.z += __bfloat162float(p.bias[col + 2]);
+      acc.w += __bfloat162float(p.bias[col + 3]);
+    }
+    if (p.residual) {
+      const __nv_bfloat16* res = p.residual + static_cast<int64_t>(row) * p.ldr + col;
+      acc.x += __bfloat162float(res[0]);
+      acc.y += __bfloat162float(res[1]);
+      acc.z += __bfloat162float(res[2]);
+      acc.w += __bfloat162float(res[3]);
+    }
+    if (p.out_fp32) {
+      *reinterpret_cast<float4*>(static_cast<float*>(p.c) + static_cast<int64_t>(row) * p.ldc + col) = acc;
+    } else {
+      uint2 o;
+      *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(acc.x, acc.y);
+      *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(acc.z, acc.w);
+      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.c) + static_cast<int64_t>(row) * p.ldc + col) = o;
+    }
   }
 }
 
@@ -820,24 +947,143 @@ bool make_c_map(CUtensorMap* map, const GemmParams& p) {
             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmParams p, cudaStream_t s) {
+// The scratch of the K-split tail tiles viewed as fp32 [items * 256, 192] for the epilogue's TMA stores.
+bool make_part_map(CUtensorMap* map, float* ptr, int64_t items) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(kBN2), static_cast<cuuint64_t>(std::max<int64_t>(items, 1) * 256)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(kBN2) * 4};
+  const cuuint32_t box[2] = {32, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int env_int(const char* name, int fallback) {
+  const char* v = getenv(name);
+  return v ? atoi(v) : fallback;
+}
+
+// Work list of the CTA-pair kernel for one problem. A launch holds `pairs` CTA pairs; whole tiles are dealt
+// round-robin (wide ones first, the narrow last column after them), and what does not fill a last round, or
+// the whole problem when it has fewer tiles than pairs, may be split along K so that every pair ends at about
+// the same time instead of a few pairs running one more tile while the rest idle: the weight gradient
+// dW[2048, 2048] over K = 32768 is 88 tiles on 74 pairs, i.e. two rounds for 1.19 rounds of work.
+// The choice minimises the modelled finish time (unit: one K-block of a wide tile; a narrow tile costs 2/3,
+// every item a constant, a split item a larger constant for its fp32 partial store, the finalize pass a
+// constant) over the number of splits; it depends on the shape and the SM count only, so results are
+// reproducible from call to call.
+struct PairPlan {
+  int pairs, n_wide, narrow, full_items, tail_tiles, tail_splits, tail_kbs, tail_shift;
+  int64_t ws_bytes;
+};
+
+PairPlan plan_pair_uncached(int64_t M, int64_t N, int64_t K, bool allow_split, int sms) {
+  PairPlan pl{};
+  const int m_tiles = static_cast<int>(ceil_div(M, 256));
+  pl.n_wide = static_cast<int>(N / kBN2);
+  const int rem_cols = static_cast<int>(N - static_cast<int64_t>(pl.n_wide) * kBN2);
+  pl.narrow = (rem_cols > 0 && rem_cols <= 128 && env_int("ANIMA_MX_GEMM_NARROW", 1)) ? 1 : 0;
+  if (rem_cols > 0 && !pl.narrow) pl.n_wide += 1;
+  const int wide_tiles = m_tiles * pl.n_wide, tiles = m_tiles * (pl.n_wide + pl.narrow);
+  const int kb = static_cast<int>(ceil_div(K, BK));
+  const int max_pairs = std::max(1, sms / 2);
+  const double kItem = 1.0, kSplitItem = 6.0, kFinalize = 16.0;
+  auto tile_cost = [&](int tile, double frac) { return (tile < wide_tiles ? 1.0 : 2.0 / 3.0) * kb * frac; };
+
+  double best = 1e300;
+  std::vector<double> load;
+  auto consider = [&](int pairs, int full_items, int splits) {
+    const int tail = tiles - full_items;
+    const int kbs = static_cast<int>(ceil_div(kb, splits));
+    if (static_cast<int>(ceil_div(kb, kbs)) != splits) return;   // would leave an empty K-range
+    load.assign(pairs, 0.0);
+    for (int i = 0; i < full_items; ++i) load[i % pairs] += tile_cost(i, 1.0) + kItem;
+    int shift = 0;
+    for (int q = 1; q < pairs; ++q)
+      if (load[q] < load[shift]) shift = q;                       // the round robin resumes at the least loaded pair
+    for (int t = 0; t < tail; ++t)
+      for (int sp = 0; sp < splits; ++sp) {
+        const int kbn = std::min(kb, (sp + 1) * kbs) - sp * kbs;
+        load[(shift + t * splits + sp) % pairs] +=
+            tile_cost(full_items + t, static_cast<double>(kbn) / kb) + (splits > 1 ? kSplitItem : kItem);
+      }
+    double finish = 0.0;
+    for (double l : load) finish = std::max(finish, l);
+    if (splits > 1) finish += kFinalize;
+    if (finish < best - 1e-9) {
+      best = finish;
+      pl.pairs = pairs;
+      pl.full_items = full_items;
+      pl.tail_tiles = tail;
+      pl.tail_splits = splits;
+      pl.tail_kbs = kbs;
+      pl.tail_shift = tail ? shift : 0;
+    }
+  };
+  const int base_pairs = std::min(tiles, max_pairs);
+  const int base_full = tiles / base_pairs * base_pairs;
+  consider(base_pairs, base_full, 1);
+  if (allow_split && kb >= 2 && env_int("ANIMA_MX_GEMM_TAIL", 1)) {
+    const int max_splits = std::min(kb, 32);
+    if (base_full < tiles)
+      for (int sp = 2; sp <= max_splits; ++sp) consider(base_pairs, base_full, sp);
+    if (tiles < max_pairs)                                          // fewer tiles than pairs: split all of them
+      for (int sp = 2; sp <= max_splits; ++sp) consider(max_pairs, 0, sp);
+  }
+  pl.ws_bytes = pl.tail_splits > 1 ? static_cast<int64_t>(pl.tail_tiles) * pl.tail_splits * 256 * kBN2 * 4 : 0;
+  return pl;
+}
+
+PairPlan plan_pair(int64_t M, int64_t N, int64_t K, bool allow_split) {
+  const int sms = sm_count();
+  const int narrow = env_int("ANIMA_MX_GEMM_NARROW", 1), tail = env_int("ANIMA_MX_GEMM_TAIL", 1);
+  using Key = std::tuple<int64_t, int64_t, int64_t, int, int>;
+  static std::mutex mu;
+  static std::map<Key, PairPlan> cache;
+  const Key key{M, N, K, sms, (allow_split ? 1 : 0) | (narrow ? 2 : 0) | (tail ? 4 : 0)};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  if (cache.size() > 4096) cache.clear();
+  const PairPlan pl = plan_pair_uncached(M, N, K, allow_split, sms);
+  cache.emplace(key, pl);
+  return pl;
+}
+
+int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmParams p, void* workspace, int64_t workspace_bytes,
+                cudaStream_t s) {
   static PerDeviceOnce once;
   const cudaError_t attr_rc = per_device_once(once, [] {
     return cudaFuncSetAttribute(mx_gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg2::kSmemBytes);
   });
   ANIMA_REQUIRE(attr_rc == cudaSuccess, ANIMA_E_CUDA, "mx_gemm: cannot reserve %d bytes of shared memory: %s",
                 Cfg2::kSmemBytes, cudaGetErrorString(attr_rc));
-  CUtensorMap ma, mb, msa, msb, mc;
+  const PairPlan pl = plan_pair(p.M, p.N, p.K, workspace != nullptr);
+  ANIMA_REQUIRE(workspace_bytes >= pl.ws_bytes, ANIMA_E_WORKSPACE,
+                "mx_gemm: workspace of %lld bytes is too small (need %lld)", (long long)workspace_bytes,
+                (long long)pl.ws_bytes);
+  p.m_tiles = static_cast<int>(ceil_div(p.M, 256));
+  p.n_wide = pl.n_wide;
+  p.narrow = pl.narrow;
+  p.n_tiles = pl.n_wide + pl.narrow;
+  p.full_items = pl.full_items;
+  p.tail_tiles = pl.tail_tiles;
+  p.tail_splits = pl.tail_splits;
+  p.tail_kbs = pl.tail_kbs;
+  p.tail_shift = pl.tail_shift;
+  p.pair_partial = pl.ws_bytes ? static_cast<float*>(workspace) : nullptr;
+  const int sf_bufs = env_int("ANIMA_MX_GEMM_SFBUFS", 4);
+  p.sf_bufs = (sf_bufs == 1 || sf_bufs == 2) ? sf_bufs : 4;
+  CUtensorMap ma, mb, msa, msb, mc, mp;
   ANIMA_REQUIRE(make_map(&ma, a_codes, p.M, p.K, 128) && make_map(&mb, b_codes, p.N, p.K, kBN2 / 2) &&
                     make_sf_map(&msa, p.a_scales, p.sfa_rt, p.k_blocks, 1) &&
-                    make_sf_map(&msb, p.b_scales, p.sfb_rt, p.k_blocks, 2) && make_c_map(&mc, p),
+                    make_sf_map(&msb, p.b_scales, p.sfb_rt, p.k_blocks, 2) && make_c_map(&mc, p) &&
+                    (pl.ws_bytes ? make_part_map(&mp, p.pair_partial, static_cast<int64_t>(pl.tail_tiles) * pl.tail_splits)
+                                 : make_c_map(&mp, p)),
                 ANIMA_E_CUDA, "mx_gemm: cuTensorMapEncodeTiled failed (driver entry point missing or bad operand)");
-  p.m_tiles = static_cast<int>(ceil_div(p.M, 256));
-  p.n_tiles = static_cast<int>(ceil_div(p.N, kBN2));
-  const int tiles = p.m_tiles * p.n_tiles;
-  const int pairs = std::max(1, std::min(tiles, sm_count() / 2));
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * pairs);
+  cfg.gridDim = dim3(2 * pl.pairs);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = Cfg2::kSmemBytes;
   cfg.stream = s;
@@ -848,8 +1094,14 @@ int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmParams p, cu
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const cudaError_t rc = cudaLaunchKernelEx(&cfg, mx_gemm2_kernel, ma, mb, msa, msb, mc, p);
+  const cudaError_t rc = cudaLaunchKernelEx(&cfg, mx_gemm2_kernel, ma, mb, msa, msb, mc, mp, p);
   ANIMA_REQUIRE(rc == cudaSuccess, ANIMA_E_CUDA, "mx_gemm: cluster launch failed: %s", cudaGetErrorString(rc));
+  if (pl.ws_bytes) {
+    const int64_t threads = static_cast<int64_t>(pl.tail_tiles) * 256 * (kBN2 / 4);
+    pair_tail_finalize_kernel<<<static_cast<unsigned>(std::min<int64_t>(ceil_div(threads, 256), 8LL * sm_count())), 256, 0,
+                                s>>>(p);
+    ANIMA_CHECK_LAUNCH("mx_gemm K-split tail finalize");
+  }
   return ANIMA_OK;
 }
 
@@ -951,9 +1203,9 @@ static int mx_gemm_impl(const uint8_t* a_codes, const uint8_t* a_scales, const u
   p.ldr = ldr;
   p.alpha = alpha;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (use_pair(M, N)) return launch_pair(a_codes, b_codes, p, s);
+  ANIMA_REQUIRE(!workspace || aligned16(workspace), ANIMA_E_ALIGN, "mx_gemm: workspace must be 16-byte aligned");
+  if (use_pair(M, N)) return launch_pair(a_codes, b_codes, p, workspace, workspace_bytes, s);
   if (workspace) {
-    ANIMA_REQUIRE(aligned16(workspace), ANIMA_E_ALIGN, "mx_gemm: workspace must be 16-byte aligned");
     int splits, kb_per;
     plan_splits(M, N, K, &splits, &kb_per);
     if (splits > 1) {
@@ -981,6 +1233,8 @@ extern "C" int anima_mx_gemm(const uint8_t* a_codes, const uint8_t* a_scales, co
 
 extern "C" int64_t anima_mx_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   if (M <= 0 || N <= 0 || K <= 0) return ANIMA_E_ARG;
+  if (M >= (1ll << 31) - 256 || N >= (1ll << 31) - 256 || K >= (1ll << 31) - 256) return ANIMA_E_TOO_LARGE;
+  if (use_pair(M, N)) return plan_pair(M, N, K, true).ws_bytes;
   int splits, kb_per;
   plan_splits(M, N, K, &splits, &kb_per);
   return splits > 1 ? static_cast<int64_t>(splits) * M * N * 4 : 0;
@@ -992,4 +1246,17 @@ extern "C" int anima_mx_gemm_ex(const uint8_t* a_codes, const uint8_t* a_scales,
                                 void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
   return mx_gemm_impl(a_codes, a_scales, b_codes, b_scales, c, M, N, K, ldc, bias, residual, ldr, alpha, out_dtype,
                       workspace, workspace_bytes, status, stream);
+}
+
+extern "C" int anima_mx_gemm_pair_plan(int64_t M, int64_t N, int64_t K, int with_workspace, int32_t* out8) {
+  ANIMA_REQUIRE(out8 != nullptr, ANIMA_E_ARG, "mx_gemm_pair_plan: null pointer");
+  ANIMA_REQUIRE(M > 0 && N > 0 && K > 0, ANIMA_E_ARG, "mx_gemm_pair_plan: bad sizes");
+  ANIMA_REQUIRE(M < (1ll << 31) - 256 && N < (1ll << 31) - 256 && K < (1ll << 31) - 256, ANIMA_E_TOO_LARGE,
+                "mx_gemm_pair_plan: a dimension exceeds 2^31");
+  if (!use_pair(M, N)) return 1;
+  const PairPlan pl = plan_pair(M, N, K, with_workspace != 0);
+  const int32_t v[8] = {pl.pairs, pl.n_wide, pl.narrow, pl.full_items, pl.tail_tiles, pl.tail_splits, pl.tail_kbs,
+                        pl.tail_shift};
+  for (int i = 0; i < 8; ++i) out8[i] = v[i];
+  return ANIMA_OK;
 }

@@ -1,6 +1,6 @@
 """Per-kernel throughput of ``libanima_b200.so`` at the production shapes.
 
-    python -m anima_trainer_sm120_b200.kernel_bench [--iters 20] [--only gemm|hbm] [--small]
+    python -m anima_trainer_sm120_b200.kernel_bench [--iters 20] [--only gemm|hbm|tlokr] [--small]
                                                    [--pick TEXT] [--direct]
 
 Every kernel is timed alone with CUDA events on the launching stream (warm-ups, then the median
@@ -89,8 +89,27 @@ def cublaslt_mxfp8(a, b):
     return lambda: torch._scaled_mm(a8, b8, scale_a=sa, scale_b=sb, out_dtype=BF16)
 
 
+class _Ctx:
+    """Stand-in for an autograd context, so that the forward and the backward of an autograd node can be timed
+    (and captured into a CUDA graph) as plain functions, without the autograd engine around them."""
+
+    needs_input_grad = (True,) * 16
+
+    def save_for_backward(self, *tensors):
+        self.saved_tensors = tensors
+
+    def mark_dirty(self, *tensors):
+        pass
+
+
+# The four module shapes of the 168-module T-LoKr preset (cross-attn q/o, k/v on the text tokens, mlp.layer1,
+# mlp.layer2): (name, in, out, rows at M = 32768 image tokens / 4096 text tokens).
+TLOKR_MODULES = [("cross q/o", 2048, 2048, 32768), ("cross k/v", 1024, 2048, 4096),
+                 ("mlp.layer1", 2048, 8192, 32768), ("mlp.layer2", 8192, 2048, 32768)]
+
+
 def run(iters: int, only: str | None, small: bool, pick: str | None = None, direct: bool = False,
-        yardstick: bool = False) -> list[dict]:
+        yardstick: bool = False, quiet: bool = False) -> list[dict]:
     _lib.load()
     torch.manual_seed(0)
     peaks = _peaks()
@@ -112,7 +131,8 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
                     "unit": "GB/s", "algorithmic_bytes": nbytes, "peak": hbm_peak,
                     "frac_of_measured": round(gbs / hbm_peak, 3) if hbm_peak else None,
                     "frac_of_nominal_8000": round(gbs / 8000.0, 3)})
-        print(json.dumps(out[-1]), flush=True)
+        if not quiet:
+            print(json.dumps(out[-1]), flush=True)
 
     def tensor(name, shape, flops, fn):
         if not wanted(name, shape):
@@ -124,7 +144,8 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
                     "peak_note": "2 x measured burst bf16 cuBLAS (no measured fp8 figure)",
                     "frac_of_measured": round(tf / tf_peak, 3) if tf_peak else None,
                     "frac_of_nominal_4500": round(tf / 4500.0, 3)})
-        print(json.dumps(out[-1]), flush=True)
+        if not quiet:
+            print(json.dumps(out[-1]), flush=True)
 
     if only in (None, "hbm"):
         K = 2048
@@ -184,6 +205,33 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
         hbm("rmsnorm_rope_fwd", [BT, L, 16, 128], M * D * 4 + M * 16 * 4, lambda: ops.rmsnorm_rope_fwd(q, wn, cos, sin, 1e-6))
         hbm("rmsnorm_rope_bwd", [BT, L, 16, 128], M * D * 6 + M * 16 * 4, lambda: ops.rmsnorm_rope_bwd(dq, q, wn, cos, sin, rs))
 
+    if only in (None, "tlokr"):
+        # The T-LoKr delta of one module, x -> x @ kron(W1, (A * mask) @ B)^T, forward and backward (recomputation,
+        # the four factor-gradient GEMMs, dC and the input gradient). Algorithmic bytes: forward reads x and
+        # writes the delta, 2 B * rows * (in + out); backward reads x and the incoming gradient and writes the
+        # input gradient, 2 B * rows * (2 * in + out). Factors, mask and W1 are KB-scale.
+        from . import tlokr
+        rank, batch = 128, 8
+        for name, d_in, d_out, rows in TLOKR_MODULES:
+            rows = rows // 8 if small else rows
+            if not (wanted(f"tlokr_delta fwd {name}", [rows, d_in, d_out]) or wanted(f"tlokr_delta bwd {name}", [rows, d_in, d_out])):
+                continue
+            x = _acts(rows, d_in).view(batch, rows // batch, d_in)
+            g = _acts(rows, d_out, 0.01).view(batch, rows // batch, d_out)
+            w1 = (torch.randn(8, 8, device="cuda") * 0.3)
+            a = torch.randn(d_out // 8, rank, device="cuda") * 0.05
+            b = torch.randn(rank, d_in // 8, device="cuda") * 0.05
+            t_s = torch.rand(batch, device="cuda")
+            mask = tlokr._TimestepState(timesteps=t_s).mask(max_rank=rank, min_rank=rank // 2, dtype=BF16,
+                                                            device=x.device)
+            ctx = _Ctx()
+            tlokr._MXStructuredLoKr.forward(ctx, x, w1, a, b, mask)
+            hbm(f"tlokr_delta fwd {name}", [rows, d_in, d_out], 2 * rows * (d_in + d_out),
+                lambda: tlokr._MXStructuredLoKr.forward(_Ctx(), x, w1, a, b, mask))
+            hbm(f"tlokr_delta bwd {name}", [rows, d_in, d_out], 2 * rows * (2 * d_in + d_out),
+                lambda: tlokr._MXStructuredLoKr.backward(ctx, g))
+            del x, g, ctx
+
     if only in (None, "gemm"):
         for (N, K) in [(2048, 2048), (6144, 2048), (8192, 2048), (2048, 8192)]:
             x, w, gy = _acts(M, K), _acts(N, K, 0.02), _acts(M, N, 0.01)
@@ -211,10 +259,24 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
     return out
 
 
+def summary(iters: int = 8) -> dict:
+    """Every kernel at its production shape as one compact record per kernel (for the benchmark line):
+    ``{name: {shape, ms, achieved, unit, peak, frac}}``; peaks are the measured ones (HBM copy; 2 x burst bf16
+    GEMM, a kernel timed alone being in the burst regime)."""
+    rows = run(iters, None, False, quiet=True)
+    out = {}
+    for r in rows:
+        out[f"{r['kernel']} {r['shape']}"] = {
+            "ms": r["ms"], "achieved": r["achieved"], "unit": r["unit"], "bound": r["bound"], "peak": r["peak"],
+            "frac": r["frac_of_measured"],
+            "algorithmic": r.get("algorithmic_bytes", r.get("algorithmic_flops"))}
+    return out
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--only", choices=["gemm", "hbm"], default=None)
+    ap.add_argument("--only", choices=["gemm", "hbm", "tlokr"], default=None)
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--pick", default=None, help="run only entries whose 'name [shape]' contains this text")
     ap.add_argument("--direct", action="store_true", help="plain launches instead of CUDA-graph replays")

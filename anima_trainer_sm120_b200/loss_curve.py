@@ -26,6 +26,42 @@ from .anima_dit import AnimaConfig
 from .train_step import StepConfig, Trainer
 
 
+def two_arm_curve(dev: torch.device, steps: int = 50, *, depth: int = 28, batch: int = 8, latent: int = 128,
+                  text: int = 512, variant: str = "lokr", lr: float = 1e-4) -> dict:
+    """The two-arm curve on one GPU as a compact record: largest per-step relative loss difference between the
+    bf16 restatement and this library's kernels (criterion: <= 2 % at every step), the first and last losses and
+    each arm's steps/s. Same seeded model, adapters, batches, noise and timesteps in both arms."""
+    losses, rate = {}, {}
+    for arm in ("bf16", "mxfp8"):
+        gc.collect()
+        torch.cuda.empty_cache()
+        tr = Trainer(AnimaConfig(depth=depth), StepConfig(precision=arm, variant=variant, lr=lr), dev)
+        ls, times = [], []
+        for s in range(steps):
+            lat, ctx, seed = tr.synthetic_batch(batch, latent, text, s)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            ls.append(tr.step(lat, ctx, seed))
+            e1.record()
+            e1.synchronize()
+            if s >= 2:
+                times.append(e0.elapsed_time(e1))
+        losses[arm] = ls
+        rate[arm] = 1000.0 * len(times) / sum(times) if times else None
+        del tr
+    gc.collect()
+    torch.cuda.empty_cache()
+    rel = [abs(b - m) / b for b, m in zip(losses["bf16"], losses["mxfp8"])]
+    return {"steps": steps, "max_rel_diff": max(rel), "within_2pct": max(rel) <= 0.02,
+            "step_of_max": rel.index(max(rel)), "first_losses": {a: l[0] for a, l in losses.items()},
+            "last_losses": {a: l[-1] for a, l in losses.items()}, "steps_per_s": rate,
+            "config": {"model": f"Anima-shaped stand-in DiT, {depth} blocks (random init, seed 42)", "batch": batch,
+                       "latent_tokens": (latent // 2) ** 2, "text_tokens": text, "variant": variant,
+                       "optimizer": "AdamW (stand-in for Prodigy + ScheduleFree, both arms)", "lr": lr,
+                       "arms": "bf16 = eager restatement of the reference's bf16 mode; mxfp8 = this library",
+                       "data": "synthetic"}}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--steps", type=int, default=50)

@@ -138,8 +138,17 @@ int anima_mx_gemm(const uint8_t* a_codes, const uint8_t* a_scales,
  * tlokr.py:619-667: [r, vq] and [vp, r] outputs contracted over rows * uq = 262144) has only
  * 1 - 8 output tiles; with a workspace the contraction is split over the SMs into fp32 partial
  * tiles that a second kernel sums in a fixed order (bit-reproducible, no atomics).
+ * Large outputs (M > 128 and N > 128, the CTA-pair kernel) use the workspace for their LAST tiles only: when
+ * the tile count does not fill a whole number of rounds over the CTA pairs (the weight gradient
+ * dW[2048,2048] over K = 32768 is 88 tiles on 74 pairs), the tiles of the last, partial round are split
+ * along K over all pairs, again as fp32 partial tiles summed in a fixed order; without a workspace they run
+ * unsplit.
  * anima_mx_gemm_workspace_bytes returns the scratch such a shape uses, or 0 when the shape is not
- * split (workspace may then be NULL). */
+ * split (workspace may then be NULL).
+ * residual == C (same pitch, bf16 C) on the CTA-pair kernel: whole tiles are rounded to bf16
+ * (alpha * acc + bias) and ADDED to C by the store itself, i.e. two roundings; the one-CTA kernel, the split
+ * paths and a residual that is another buffer add in fp32 and round once. Both stay within bf16 rounding of
+ * the exact sum; bit patterns can differ between the two forms. */
 int64_t anima_mx_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int anima_mx_gemm_ex(const uint8_t* a_codes, const uint8_t* a_scales,
                      const uint8_t* b_codes, const uint8_t* b_scales,
@@ -147,6 +156,14 @@ int anima_mx_gemm_ex(const uint8_t* a_codes, const uint8_t* a_scales,
                      const void* bias_bf16, const void* residual_bf16, int64_t ldr, float alpha,
                      int out_dtype, void* workspace, int64_t workspace_bytes,
                      int32_t* status, void* stream);
+
+/* The work list the CTA-pair kernel uses for a problem on the current device (no reference counterpart; for
+ * tests and tuning, nothing is launched): out8 = { CTA pairs launched, 192-wide tile columns, 1 if a narrow
+ * last column (<= 128 outputs, computed with N = 128 instructions) follows them, whole-tile items dealt
+ * round-robin, tail tiles after those, K-ranges per tail tile, K-blocks (of 128) per range, pair at which the
+ * tail's round robin starts }. with_workspace == 0 gives the plan of a call without scratch (no K-split).
+ * Returns 0, 1 if the shape runs on the one-CTA kernel instead (out8 untouched), or a negative status. */
+int anima_mx_gemm_pair_plan(int64_t M, int64_t N, int64_t K, int with_workspace, int32_t* out8);
 
 /* ---------------------------------------------------------------- LoKr merged weight
  * ref: lokr_patch.py:76-84 (merged = W + alpha * kron(w1, w2)) followed by the two

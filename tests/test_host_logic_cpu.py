@@ -199,3 +199,92 @@ def test_factor_forms_are_kept_per_parameter_version(monkeypatch):
     tlokr._factor_forms(sliced, quantise=True)
     tlokr._factor_forms(sliced, quantise=True)
     assert len(calls) == 4
+
+
+# ----------------------------------------------------------------------------- GEMM work list (CTA-pair kernel)
+def _pair_plan(M, N, K, ws=1):
+    import ctypes
+
+    from anima_trainer_sm120_b200 import _lib
+    out = (ctypes.c_int32 * 8)()
+    rc = _lib.load().anima_mx_gemm_pair_plan(M, N, K, ws, out)
+    return rc, dict(zip(("pairs", "n_wide", "narrow", "full_items", "tail_tiles", "splits", "kbs", "shift"), out))
+
+
+def _walk_plan(M, N, K, pl):
+    """The device-side decode of the work list restated: {(mt, nt): [(kb0, kb1, pair, partial slot)]}."""
+    m_tiles, kb = -(-M // 256), -(-K // 128)
+    wide = m_tiles * pl["n_wide"]
+
+    def coords(tile):
+        if tile >= wide:
+            return tile - wide, pl["n_wide"]
+        if m_tiles < pl["n_wide"]:
+            return tile % m_tiles, tile // m_tiles
+        return tile // pl["n_wide"], tile % pl["n_wide"]
+
+    split_items = pl["tail_tiles"] * pl["splits"]
+    slots = pl["full_items"] + (pl["shift"] + split_items if split_items else 0)
+    cover: dict = {}
+    for slot in range(slots):
+        pair = slot % pl["pairs"]
+        kb0, kb1, part, tile = 0, kb, -1, slot
+        if slot >= pl["full_items"]:
+            r = slot - pl["full_items"] - pl["shift"]
+            if r < 0:
+                continue
+            t, sp = divmod(r, pl["splits"])
+            tile = pl["full_items"] + t
+            if pl["splits"] > 1:
+                kb0, kb1, part = sp * pl["kbs"], min(kb, (sp + 1) * pl["kbs"]), r
+        cover.setdefault(coords(tile), []).append((kb0, kb1, pair, part))
+    return cover
+
+
+@pytest.mark.parametrize("M,N,K", [
+    (32768, 2048, 2048), (32768, 6144, 2048), (32768, 8192, 2048), (32768, 2048, 8192),      # forward / dgrad
+    (2048, 2048, 32768), (6144, 2048, 32768), (8192, 2048, 32768), (2048, 8192, 32768),      # weight gradients
+    (4096, 2048, 1024), (2048, 1024, 4096), (512, 512, 16384), (257, 384, 416), (130, 264, 160), (256, 136, 32),
+])
+@pytest.mark.parametrize("ws", [0, 1])
+def test_pair_kernel_work_list_covers_every_tile_and_k_block_once(M, N, K, ws):
+    rc, pl = _pair_plan(M, N, K, ws)
+    assert rc == 0
+    m_tiles, kb = -(-M // 256), -(-K // 128)
+    n_cols = pl["n_wide"] + pl["narrow"]
+    assert pl["n_wide"] * 192 + 128 * pl["narrow"] >= N > (n_cols - 1) * 192
+    assert pl["full_items"] % pl["pairs"] == 0 and pl["full_items"] + pl["tail_tiles"] == m_tiles * n_cols
+    assert pl["pairs"] <= 74 and (ws or pl["splits"] == 1)
+    cover = _walk_plan(M, N, K, pl)
+    assert set(cover) == {(mt, nt) for mt in range(m_tiles) for nt in range(n_cols)}
+    parts = []
+    for ranges in cover.values():
+        ranges.sort()
+        assert ranges[0][0] == 0 and ranges[-1][1] == kb
+        assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:])) and all(a[0] < a[1] for a in ranges)
+        assert (len(ranges) == 1) == (ranges[0][3] < 0)
+        parts += [r[3] for r in ranges if r[3] >= 0]
+    assert sorted(parts) == list(range(len(parts)))                        # every partial slot written exactly once
+    from anima_trainer_sm120_b200 import _lib
+    need = _lib.load().anima_mx_gemm_workspace_bytes(M, N, K)
+    assert need == (len(parts) * 256 * 192 * 4 if ws else need)
+
+
+def test_pair_kernel_splits_the_partial_round_of_long_contractions_only():
+    assert _pair_plan(2048, 2048, 32768)[1]["splits"] > 1                  # 88 tiles on 74 pairs, 256 K-blocks each
+    assert _pair_plan(2048, 2048, 32768, ws=0)[1]["splits"] == 1
+    assert _pair_plan(32768, 2048, 2048)[1]["splits"] == 1                 # 16 K-blocks per tile: a split costs more
+    assert _pair_plan(32768, 2048, 2048)[1]["narrow"] == 1                 # 2048 = 10 x 192 + 128
+    assert _pair_plan(32768, 6144, 2048)[1]["narrow"] == 0                 # 6144 = 32 x 192
+    assert _pair_plan(128, 2048, 2048)[0] == 1                             # one-CTA kernel's shape
+    # the modelled finish time with the split must not exceed the unsplit one: the busiest pair's K-blocks
+    for shape, gain in [((2048, 2048, 32768), 0.65), ((8192, 2048, 32768), 0.95), ((2048, 8192, 32768), 0.95)]:
+        loads = []
+        for ws in (0, 1):
+            pl = _pair_plan(*shape, ws)[1]
+            per_pair = [0.0] * pl["pairs"]
+            for (mt, nt), ranges in _walk_plan(*shape, pl).items():
+                for kb0, kb1, pair, _ in ranges:
+                    per_pair[pair] += (kb1 - kb0) * (1.0 if nt < pl["n_wide"] else 2.0 / 3.0)
+            loads.append(max(per_pair))
+        assert loads[1] < gain * loads[0], (shape, loads)
