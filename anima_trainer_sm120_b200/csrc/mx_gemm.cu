@@ -134,9 +134,9 @@ struct GemmParams {
   int64_t ldr;
   float alpha;
   // Work list of the CTA-pair kernel (see PairPlan below): tile columns 0 .. n_wide-1 are 192 wide; if
-  // `narrow`, one more column of at most 128 valid outputs follows and is computed with N = 128 instructions.
-  // Items 0 .. full_items-1 are whole tiles (wide ones first, narrow ones after them), dealt round-robin to the
-  // pairs (full_items is a multiple of the pair count). The tail_tiles tiles after them are each split along K
+  // `narrow`, one more column of at most 128 valid outputs follows and is computed with N = 128 instructions
+  // (n_tiles = n_wide + narrow). Items 0 .. full_items-1 are whole tiles in tile order, dealt round-robin to
+  // the pairs (full_items is a multiple of the pair count). The tail_tiles tiles after them are each split along K
   // into tail_splits ranges of tail_kbs K-blocks; those items are dealt round-robin starting at pair tail_shift
   // and leave as fp32 partial tiles in pair_partial [item][256][192], summed by pair_tail_finalize_kernel.
   int n_wide, narrow;
@@ -146,23 +146,23 @@ struct GemmParams {
 };
 
 
-// Tile order of the CTA-pair kernel. Wide tiles come first, the narrow last column after them (cheaper items at
-// the end balance the round robin). Inside the wide region the tiles that run at the same time should cover the
-// SHORTER side of the tile grid completely, so that the operand of the longer side is streamed once instead of
-// once per tile row: with n fastest, the wgrad dW[2048, 8192] (8 x 43 tiles) re-read its 268 MB B operand 8
-// times and ran HBM-bound. The index along the shorter side varies fastest.
-__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& mt, int& nt) {
-  const int wide = p.m_tiles * p.n_wide;
-  if (tile >= wide) {
-    mt = tile - wide;
-    nt = p.n_wide;
-  } else if (p.m_tiles < p.n_wide) {
-    nt = tile / p.m_tiles;
-    mt = tile - nt * p.m_tiles;
+// Tile order of the CTA-pair kernel. The tiles that run at the same time should cover the SHORTER side of
+// the tile grid completely, so that the operand of the longer side is streamed once instead of once per
+// tile row: with n fastest, the wgrad dW[2048, 8192] (8 x 43 tiles) re-read its 268 MB B operand 8 times and
+// ran HBM-bound. The index along the shorter side varies fastest. The narrow last tile column (nt == n_wide)
+// stays inside this sweep: run as a phase of its own after the wide tiles it re-read all of A with 16
+// K-blocks of work per tile and was HBM-bound (2644 -> 2509 TFLOP/s on 32768 x 2048 x 2048).
+__host__ __device__ __forceinline__ void tile_coords_of(int m_tiles, int n_tiles, int tile, int& mt, int& nt) {
+  if (m_tiles < n_tiles) {
+    nt = tile / m_tiles;
+    mt = tile - nt * m_tiles;
   } else {
-    mt = tile / p.n_wide;
-    nt = tile - mt * p.n_wide;
+    mt = tile / n_tiles;
+    nt = tile - mt * n_tiles;
   }
+}
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& mt, int& nt) {
+  tile_coords_of(p.m_tiles, p.n_tiles, tile, mt, nt);
 }
 
 // One unit of work of a CTA pair: a whole tile (part < 0) or the K-range [kb0, kb1) of a tail tile, whose fp32
@@ -965,7 +965,7 @@ int env_int(const char* name, int fallback) {
 }
 
 // Work list of the CTA-pair kernel for one problem. A launch holds `pairs` CTA pairs; whole tiles are dealt
-// round-robin (wide ones first, the narrow last column after them), and what does not fill a last round, or
+// round-robin in tile order, and what does not fill a last round, or
 // the whole problem when it has fewer tiles than pairs, may be split along K so that every pair ends at about
 // the same time instead of a few pairs running one more tile while the rest idle: the weight gradient
 // dW[2048, 2048] over K = 32768 is 88 tiles on 74 pairs, i.e. two rounds for 1.19 rounds of work.
@@ -985,11 +985,15 @@ PairPlan plan_pair_uncached(int64_t M, int64_t N, int64_t K, bool allow_split, i
   const int rem_cols = static_cast<int>(N - static_cast<int64_t>(pl.n_wide) * kBN2);
   pl.narrow = (rem_cols > 0 && rem_cols <= 128 && env_int("ANIMA_MX_GEMM_NARROW", 1)) ? 1 : 0;
   if (rem_cols > 0 && !pl.narrow) pl.n_wide += 1;
-  const int wide_tiles = m_tiles * pl.n_wide, tiles = m_tiles * (pl.n_wide + pl.narrow);
+  const int n_tiles = pl.n_wide + pl.narrow, tiles = m_tiles * n_tiles;
   const int kb = static_cast<int>(ceil_div(K, BK));
   const int max_pairs = std::max(1, sms / 2);
   const double kItem = 1.0, kSplitItem = 6.0, kFinalize = 16.0;
-  auto tile_cost = [&](int tile, double frac) { return (tile < wide_tiles ? 1.0 : 2.0 / 3.0) * kb * frac; };
+  auto tile_cost = [&](int tile, double frac) {
+    int mt, nt;
+    tile_coords_of(m_tiles, n_tiles, tile, mt, nt);
+    return (nt < pl.n_wide ? 1.0 : 2.0 / 3.0) * kb * frac;
+  };
 
   double best = 1e300;
   std::vector<double> load;

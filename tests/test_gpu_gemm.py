@@ -284,7 +284,9 @@ def test_full_size_config2_properties():
     dw = ops.mx_gemm(gc, xc, out_dtype=torch.float32)
     dw_t = ops.mx_gemm(xc, gc, out_dtype=torch.float32)
     lib.check_status_word(c.device)
-    torch.testing.assert_close(dw, dw_t.t(), rtol=1e-5, atol=1e-4)
+    # the same products summed in a different association (a tile of one may be K-split where the other's is
+    # not): equal up to fp32 rounding of sums of 32768 terms
+    torch.testing.assert_close(dw, dw_t.t(), rtol=1e-4, atol=2e-5 * float(dw.abs().max()))
     assert _rel_max(gy.float().t() @ x.float(), dw) < 0.10
 
 
