@@ -47,6 +47,7 @@ PROTOTYPES: dict[str, tuple[object, list[object]]] = {
     "anima_mx_gemm_workspace_bytes": (I64, [I64, I64, I64]),
     "anima_mx_gemm_ex": (c_int, [P, P, P, P, P, I64, I64, I64, I64, P, P, I64, c_float, c_int, P, I64, P, P]),
     "anima_mx_gemm_pair_plan": (c_int, [I64, I64, I64, c_int, P]),
+    "anima_mx_gemm_set_clock_probe": (c_int, [P]),
     "anima_lokr_merge_quantize": (
         c_int, [P, P, P, c_int, c_float, I64, I64, I64, I64, P, P, P, P, P, c_int, P]),
     "anima_lokr_kron_backward_workspace_bytes": (I64, [I64, I64, I64, I64]),
@@ -66,6 +67,7 @@ PROTOTYPES: dict[str, tuple[object, list[object]]] = {
     "anima_gated_add_bwd": (c_int, [P, P, P, I64, I64, I64, P, P, P, I64, P]),
     "anima_tlokr_rank_mix": (c_int, [P, P, P, I64, I64, I64, c_int, P, P]),
     "anima_tlokr_rank_mix_quant": (c_int, [P, P, P, I64, I64, I64, c_int, P, P, P, P, P, P]),
+    "anima_tlokr_rank_mix_quant_planes": (c_int, [P, P, P, I64, I64, I64, c_int, P, P, P, P, P]),
     "anima_tlokr_rank_mix_wgrad_workspace_bytes": (I64, [I64, I64, I64]),
     "anima_tlokr_rank_mix_wgrad": (c_int, [P, P, P, I64, I64, I64, P, P, I64, P]),
     "anima_rmsnorm_rope_fwd": (c_int, [P, P, P, P, c_float, I64, I64, I64, I64, P, P, P]),

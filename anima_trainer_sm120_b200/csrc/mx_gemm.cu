@@ -143,6 +143,10 @@ struct GemmParams {
   int full_items, tail_tiles, tail_splits, tail_kbs, tail_shift;
   float* pair_partial;
   int sf_bufs;  // tensor-memory scale buffers the K-blocks rotate through (1, 2 or 4)
+  // Measurement aid (anima_mx_gemm_set_clock_probe): if not null, CTA 0 of a pair-kernel launch adds the SM
+  // cycles and the nanoseconds it ran, so that the clock the GPU actually held under this kernel's power
+  // draw can be read back (the driver's sampled clocks mostly see the idle gaps between launches).
+  long long* clock_probe;
 };
 
 
@@ -470,8 +474,14 @@ __global__ void __launch_bounds__(256) splitk_finalize_kernel(const GemmParams p
 // are delivered to the mbarriers of both CTAs, and both CTAs' TMA loads complete on the
 // leader's "full" barrier. Each CTA drains its own 128 accumulator rows. The loads carry no
 // multicast: each CTA fetches its own boxes.
-constexpr int kStages2 = 6;
+// Tile width 192: tiles start at multiples of 64 columns, so a tile touches two 128-column scale chunks of B
+// and its scales start 0 or 2 tensor-memory columns into the first. A 224-wide variant (tiles at multiples of
+// 32, odd scale-column offsets) raised a misaligned-address fault on its first tile with an odd offset; widths
+// that are not multiples of 64 are therefore not used.
 constexpr int kBN2 = 192;
+constexpr int kStages2 = 6;
+constexpr int kSfbChunks2 = 2;  // 128-column scale chunks of B a tile can touch
+static_assert(kBN2 % 64 == 0 && 2 * kBN2 + 64 <= 512, "two accumulator buffers and four scale buffers must fit");
 
 struct Cfg2 {
   static constexpr int kABytes = 128 * BK;
@@ -479,7 +489,7 @@ struct Cfg2 {
   static constexpr int kAcc1Col = kBN2;            // second accumulator buffer
   static constexpr int kSfaCol = 2 * kBN2;         // scale buffers: 16 columns each (SFA 4, SFB 2 x 4), up to 4 of them
   static constexpr int kTmemCols = 512;
-  static constexpr int kSfBytes = kSfChunk * 3;  // SFA chunk + both SFB chunks
+  static constexpr int kSfBytes = kSfChunk * (1 + kSfbChunks2);  // SFA chunk + the SFB chunks
   static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
   static constexpr int kStoreBytes = 128 * 128;  // one 128-row x 32-column output chunk (fp32 worst case)
   static constexpr int kSmemBytes = kStages2 * kStageBytes + 2 * kStoreBytes + 1024 + 256;
@@ -609,6 +619,8 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const long long probe_cycles0 = clock64();
+  const uint64_t probe_ns0 = global_timer_ns();
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
@@ -854,6 +866,11 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();  // neither CTA releases shared or tensor memory while its peer may still use it
+  if (p.clock_probe && blockIdx.x == 0 && threadIdx.x == 0) {
+    p.clock_probe[0] += clock64() - probe_cycles0;
+    p.clock_probe[1] += static_cast<long long>(global_timer_ns() - probe_ns0);
+    p.clock_probe[2] += 1;  // launches seen
+  }
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_alloc), "r"(C::kTmemCols) : "memory");
@@ -958,6 +975,9 @@ bool make_part_map(CUtensorMap* map, float* ptr, int64_t items) {
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+
+// Device buffer of the clock probe per device (null = off).
+long long* g_clock_probe[64] = {};
 
 int env_int(const char* name, int fallback) {
   const char* v = getenv(name);
@@ -1077,12 +1097,16 @@ int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmParams p, vo
   p.tail_kbs = pl.tail_kbs;
   p.tail_shift = pl.tail_shift;
   p.pair_partial = pl.ws_bytes ? static_cast<float*>(workspace) : nullptr;
+  {
+    int dev = 0;
+    p.clock_probe = (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) ? g_clock_probe[dev] : nullptr;
+  }
   const int sf_bufs = env_int("ANIMA_MX_GEMM_SFBUFS", 4);
   p.sf_bufs = (sf_bufs == 1 || sf_bufs == 2) ? sf_bufs : 4;
   CUtensorMap ma, mb, msa, msb, mc, mp;
   ANIMA_REQUIRE(make_map(&ma, a_codes, p.M, p.K, 128) && make_map(&mb, b_codes, p.N, p.K, kBN2 / 2) &&
                     make_sf_map(&msa, p.a_scales, p.sfa_rt, p.k_blocks, 1) &&
-                    make_sf_map(&msb, p.b_scales, p.sfb_rt, p.k_blocks, 2) && make_c_map(&mc, p) &&
+                    make_sf_map(&msb, p.b_scales, p.sfb_rt, p.k_blocks, kSfbChunks2) && make_c_map(&mc, p) &&
                     (pl.ws_bytes ? make_part_map(&mp, p.pair_partial, static_cast<int64_t>(pl.tail_tiles) * pl.tail_splits)
                                  : make_c_map(&mp, p)),
                 ANIMA_E_CUDA, "mx_gemm: cuTensorMapEncodeTiled failed (driver entry point missing or bad operand)");
@@ -1262,5 +1286,15 @@ extern "C" int anima_mx_gemm_pair_plan(int64_t M, int64_t N, int64_t K, int with
   const int32_t v[8] = {pl.pairs, pl.n_wide, pl.narrow, pl.full_items, pl.tail_tiles, pl.tail_splits, pl.tail_kbs,
                         pl.tail_shift};
   for (int i = 0; i < 8; ++i) out8[i] = v[i];
+  return ANIMA_OK;
+}
+
+extern "C" int anima_mx_gemm_set_clock_probe(void* device_buffer_3xint64) {
+  int dev = 0;
+  const cudaError_t rc = cudaGetDevice(&dev);
+  ANIMA_REQUIRE(rc == cudaSuccess && dev >= 0 && dev < 64, ANIMA_E_CUDA, "mx_gemm_set_clock_probe: no current device");
+  ANIMA_REQUIRE(!device_buffer_3xint64 || (reinterpret_cast<uintptr_t>(device_buffer_3xint64) & 7) == 0, ANIMA_E_ALIGN,
+                "mx_gemm_set_clock_probe: buffer must be 8-byte aligned");
+  g_clock_probe[dev] = static_cast<long long*>(device_buffer_3xint64);
   return ANIMA_OK;
 }

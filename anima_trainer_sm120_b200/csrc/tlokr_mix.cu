@@ -85,6 +85,10 @@ struct MixCodes {
   uint8_t* scales_row;   // tiled
   uint8_t* codes_colT;   // [rank, R] or null
   uint8_t* scales_col;   // tiled
+  // Row form as eight planes: row i of item t goes to matrix row i * plane_rows + t instead of t * 8 + i
+  // (plane_rows = items, a multiple of 128, so every plane is a whole number of scale row tiles). A GEMM over
+  // the items can then take plane i as a K-major [items, rank] operand. 0 = the plain [R, rank] order.
+  int64_t plane_rows;
 };
 
 template <bool TRANSPOSE, bool HAS_MASK, bool ROW, bool COL>
@@ -157,7 +161,7 @@ rank_mix_quant_kernel(const __nv_bfloat16* __restrict__ hidden, const __nv_bfloa
       uint2 codes;
       codes.x = mxq::e4m3x2(f[0] * inv, f[1] * inv) | (mxq::e4m3x2(f[2] * inv, f[3] * inv) << 16);
       codes.y = mxq::e4m3x2(f[4] * inv, f[5] * inv) | (mxq::e4m3x2(f[6] * inv, f[7] * inv) << 16);
-      const int64_t row = item * 8 + i;
+      const int64_t row = q.plane_rows ? i * q.plane_rows + item : item * 8 + i;
       *reinterpret_cast<uint2*>(q.codes_row + row * rank + rc * 8) = codes;
       if ((rc & 3) == 0) {
         const int kb = rc >> 2;
@@ -335,10 +339,10 @@ extern "C" int anima_tlokr_rank_mix(const void* hidden, const void* c, const voi
   return ANIMA_OK;
 }
 
-extern "C" int anima_tlokr_rank_mix_quant(const void* hidden, const void* c, const void* mask, int64_t batch,
-                                          int64_t n_per_batch, int64_t rank, int transpose, void* out,
-                                          uint8_t* codes_row, uint8_t* scales_row, uint8_t* codes_colT,
-                                          uint8_t* scales_col, void* stream) {
+static int rank_mix_quant_impl(const void* hidden, const void* c, const void* mask, int64_t batch,
+                               int64_t n_per_batch, int64_t rank, int transpose, void* out,
+                               uint8_t* codes_row, uint8_t* scales_row, uint8_t* codes_colT,
+                               uint8_t* scales_col, bool planes, void* stream) {
   ANIMA_REQUIRE(hidden && c, ANIMA_E_ARG, "tlokr_rank_mix_quant: null pointer");
   ANIMA_REQUIRE(codes_row || codes_colT, ANIMA_E_ARG, "tlokr_rank_mix_quant: no operand requested");
   ANIMA_REQUIRE((codes_row == nullptr) == (scales_row == nullptr) && (codes_colT == nullptr) == (scales_col == nullptr),
@@ -360,7 +364,9 @@ extern "C" int anima_tlokr_rank_mix_quant(const void* hidden, const void* c, con
   const auto* cp = static_cast<const __nv_bfloat16*>(c);
   const auto* mp = static_cast<const __nv_bfloat16*>(mask);
   auto* op = static_cast<__nv_bfloat16*>(out);
-  const MixCodes q{codes_row, scales_row, codes_colT, scales_col};
+  ANIMA_REQUIRE(!planes || (codes_row && items % 128 == 0), ANIMA_E_SHAPE,
+                "tlokr_rank_mix_quant_planes: needs the row form and batch * n = %lld a multiple of 128", (long long)items);
+  const MixCodes q{codes_row, scales_row, codes_colT, scales_col, planes ? items : 0};
 #define ANIMA_MIXQ(T, M, R, C) rank_mix_quant_kernel<T, M, R, C><<<grid, 256, 0, s>>>(hp, cp, mp, items, n_per_batch, r8, op, q)
 #define ANIMA_MIXQ_FORMS(T, M)                                     \
   do {                                                             \
@@ -377,6 +383,22 @@ extern "C" int anima_tlokr_rank_mix_quant(const void* hidden, const void* c, con
 #undef ANIMA_MIXQ
   ANIMA_CHECK_LAUNCH("tlokr_rank_mix_quant");
   return ANIMA_OK;
+}
+
+extern "C" int anima_tlokr_rank_mix_quant(const void* hidden, const void* c, const void* mask, int64_t batch,
+                                          int64_t n_per_batch, int64_t rank, int transpose, void* out,
+                                          uint8_t* codes_row, uint8_t* scales_row, uint8_t* codes_colT,
+                                          uint8_t* scales_col, void* stream) {
+  return rank_mix_quant_impl(hidden, c, mask, batch, n_per_batch, rank, transpose, out, codes_row, scales_row, codes_colT,
+                             scales_col, false, stream);
+}
+
+extern "C" int anima_tlokr_rank_mix_quant_planes(const void* hidden, const void* c, const void* mask, int64_t batch,
+                                                 int64_t n_per_batch, int64_t rank, int transpose,
+                                                 uint8_t* codes_planes, uint8_t* scales_planes, uint8_t* codes_colT,
+                                                 uint8_t* scales_col, void* stream) {
+  return rank_mix_quant_impl(hidden, c, mask, batch, n_per_batch, rank, transpose, nullptr, codes_planes, scales_planes,
+                             codes_colT, scales_col, true, stream);
 }
 
 extern "C" int64_t anima_tlokr_rank_mix_wgrad_workspace_bytes(int64_t batch, int64_t n_per_batch,

@@ -134,16 +134,28 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
         if not quiet:
             print(json.dumps(out[-1]), flush=True)
 
+    probe = torch.zeros(3, dtype=torch.int64, device="cuda")
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+
     def tensor(name, shape, flops, fn):
         if not wanted(name, shape):
             return
+        # SM cycles / ns added up by CTA 0 of every CTA-pair GEMM launch while this entry is timed: the clock the
+        # GPU holds under the kernel's own power draw (a library GEMM timed as a yardstick adds nothing)
+        probe.zero_()
+        _lib.check(_lib.load().anima_mx_gemm_set_clock_probe(probe.data_ptr()))
         ms = t(fn)
+        _lib.check(_lib.load().anima_mx_gemm_set_clock_probe(None))
+        cycles, ns, _ = (int(v) for v in probe.cpu().tolist())
         tf = flops / ms / 1e9
+        ghz = cycles / ns if ns else None
         out.append({"kernel": name, "shape": shape, "ms": round(ms, 4), "bound": "tensor", "achieved": round(tf, 1),
                     "unit": "TFLOP/s", "algorithmic_flops": flops, "peak": tf_peak,
                     "peak_note": "2 x measured burst bf16 cuBLAS (no measured fp8 figure)",
                     "frac_of_measured": round(tf / tf_peak, 3) if tf_peak else None,
-                    "frac_of_nominal_4500": round(tf / 4500.0, 3)})
+                    "frac_of_nominal_4500": round(tf / 4500.0, 3),
+                    "sm_mhz_in_kernel": round(ghz * 1000.0) if ghz else None,
+                    "tensor_pipe_util_at_that_clock": round(tf * 1e3 / (sms * 16384 * ghz), 3) if ghz else None})
         if not quiet:
             print(json.dumps(out[-1]), flush=True)
 
@@ -269,7 +281,9 @@ def summary(iters: int = 8) -> dict:
         out[f"{r['kernel']} {r['shape']}"] = {
             "ms": r["ms"], "achieved": r["achieved"], "unit": r["unit"], "bound": r["bound"], "peak": r["peak"],
             "frac": r["frac_of_measured"],
-            "algorithmic": r.get("algorithmic_bytes", r.get("algorithmic_flops"))}
+            "algorithmic": r.get("algorithmic_bytes", r.get("algorithmic_flops")),
+            **({"sm_mhz_in_kernel": r["sm_mhz_in_kernel"], "tensor_pipe_util_at_that_clock":
+                r["tensor_pipe_util_at_that_clock"]} if r.get("sm_mhz_in_kernel") else {})}
     return out
 
 

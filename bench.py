@@ -371,7 +371,13 @@ def run_gpu_arm(args) -> None:
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    # the clock the GPU holds INSIDE the GEMM (cycles / ns added up by CTA 0 of every launch): the driver's
+    # sampled clocks mostly see the gaps between launches of a region this short
+    probe = torch.zeros(3, dtype=torch.int64, device=dev)
+    _lib.check(_lib.load().anima_mx_gemm_set_clock_probe(probe.data_ptr()))
     ms_total = timed(False, args.steps, max(args.warmup, 3))
+    _lib.check(_lib.load().anima_mx_gemm_set_clock_probe(None))
+    probe_cycles, probe_ns, probe_n = (int(v) for v in probe.cpu().tolist())
     clocks = sampler.stop() if rank == 0 else {}
     _lib.check_status_word(dev)
     n_launch = launches[0]
@@ -439,6 +445,7 @@ def run_gpu_arm(args) -> None:
         use_burst = near_max or ms_total < 1000.0
         peak = 2.0 * (burst if use_burst else sustained)
         achieved = gemm_fl / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+        sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
         ms_step = ms_total / args.steps
         fl = gemm_flops_per_step() * world
         d2h = n_grad * 4 + len(shapes) * 4
@@ -463,6 +470,14 @@ def run_gpu_arm(args) -> None:
                          "frac_of_2x_burst_bf16": achieved / (2.0 * burst),
                          "frac_of_2x_sustained_bf16": achieved / (2.0 * sustained),
                          "frac_of_nominal_4500": achieved / 4500.0,
+                         "sm_mhz_in_kernel": round(1000.0 * probe_cycles / probe_ns, 1) if probe_ns else None,
+                         "tensor_pipe_util_at_that_clock": (
+                             achieved * 1e12 / (sm_count * 16384.0 * (probe_cycles / probe_ns) * 1e9)
+                             if probe_ns else None),
+                         "in_kernel_clock_note": ("SM cycles / ns summed by CTA 0 over the timed region's (warm-up "
+                                                  "included) GEMM launches; util = achieved / (SMs x 8192 MAC/clk x "
+                                                  "that clock): the kernel runs under the power cap, below the "
+                                                  "clock nvidia-smi samples between launches"),
                          "launches": n_gemm, "avg_launch_ms": gemm_ms / max(n_gemm, 1),
                          "gemm_share_of_step": gemm_ms / ms_total},
             "clocks": clocks,

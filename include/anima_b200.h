@@ -165,6 +165,13 @@ int anima_mx_gemm_ex(const uint8_t* a_codes, const uint8_t* a_scales,
  * Returns 0, 1 if the shape runs on the one-CTA kernel instead (out8 untouched), or a negative status. */
 int anima_mx_gemm_pair_plan(int64_t M, int64_t N, int64_t K, int with_workspace, int32_t* out8);
 
+/* Measurement aid (no reference counterpart). With a device buffer of three int64 registered for the current
+ * device (zeroed by the caller), CTA 0 of every later CTA-pair GEMM launch on that device ADDS { SM cycles it
+ * ran, nanoseconds it ran, 1 } to it: cycles / ns is the SM clock the GPU held under the kernel's own power
+ * draw, which sampling nvidia-smi between launches does not show. NULL switches it off. The buffer must
+ * outlive every launch made while it is registered; launches that overlap on several streams race on it. */
+int anima_mx_gemm_set_clock_probe(void* device_buffer_3xint64);
+
 /* ---------------------------------------------------------------- LoKr merged weight
  * ref: lokr_patch.py:76-84 (merged = W + alpha * kron(w1, w2)) followed by the two
  *      weight quantisations of fp8_quant.py:234-235 / :501.
@@ -302,6 +309,16 @@ int anima_tlokr_rank_mix_quant(const void* hidden, const void* c, const void* ma
                                int64_t n_per_batch, int64_t rank, int transpose, void* out,
                                uint8_t* codes_row, uint8_t* scales_row, uint8_t* codes_colT,
                                uint8_t* scales_col, void* stream);
+
+/* The same, with the row form written as EIGHT PLANES: row i of item t (t = b * n_per_batch + n) becomes row
+ * i * items + t of a u8 [8 * items, rank] matrix (TILED scales of that matrix), so that plane i is a K-major
+ * [items, rank] GEMM operand over the items: what the delta K-blocks of anima_mx_gemm_delta consume. The
+ * codes of a row equal those of anima_tlokr_rank_mix_quant. items = batch * n_per_batch must be a multiple of
+ * 128 (whole scale row tiles per plane). The column form (may be NULL) is unchanged. No reference counterpart. */
+int anima_tlokr_rank_mix_quant_planes(const void* hidden, const void* c, const void* mask, int64_t batch,
+                                      int64_t n_per_batch, int64_t rank, int transpose,
+                                      uint8_t* codes_planes, uint8_t* scales_planes,
+                                      uint8_t* codes_colT, uint8_t* scales_col, void* stream);
 
 /* ref: tlokr_kernels.py:85-122, :168-204 (rank_mix_wgrad).
  *   dc[i,j] = sum_{b,n,r} grad_mixed[b,n,i,r] * hidden[b,n,j,r] * mask[b,r]   (fp32 [8,8])
