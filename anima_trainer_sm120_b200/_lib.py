@@ -46,6 +46,7 @@ PROTOTYPES: dict[str, tuple[object, list[object]]] = {
     "anima_mx_gemm": (c_int, [P, P, P, P, P, I64, I64, I64, I64, P, c_int, P, P]),
     "anima_mx_gemm_workspace_bytes": (I64, [I64, I64, I64]),
     "anima_mx_gemm_ex": (c_int, [P, P, P, P, P, I64, I64, I64, I64, P, P, I64, c_float, c_int, P, I64, P, P]),
+    "anima_mx_gemm_delta": (c_int, [P, P, P, P, P, I64, I64, I64, I64, P, c_int, P, P, P, P, P, I64, P, P]),
     "anima_mx_gemm_pair_plan": (c_int, [I64, I64, I64, c_int, P]),
     "anima_mx_gemm_set_clock_probe": (c_int, [P]),
     "anima_lokr_merge_quantize": (

@@ -143,6 +143,11 @@ struct GemmParams {
   int full_items, tail_tiles, tail_splits, tail_kbs, tail_shift;
   float* pair_partial;
   int sf_bufs;  // tensor-memory scale buffers the K-blocks rotate through (1, 2 or 4)
+  // Low-rank delta folded in as extra K-blocks (anima_mx_gemm_delta): output columns [i * delta_block,
+  // (i + 1) * delta_block) also receive planes[i][m, 0:128] . d[p, 0:128]^T. For a tile, every run of its
+  // columns inside one block is one more pipeline stage (A slot: 128 rows of plane i; B slot: the factor rows of
+  // the run, half per CTA) and one group of MMAs of that width into the run's accumulator columns.
+  int delta, delta_block;
   // Measurement aid (anima_mx_gemm_set_clock_probe): if not null, CTA 0 of a pair-kernel launch adds the SM
   // cycles and the nanoseconds it ran, so that the clock the GPU actually held under this kernel's power
   // draw can be read back (the driver's sampled clocks mostly see the idle gaps between launches).
@@ -598,6 +603,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
                 const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_part,
+                const __grid_constant__ CUtensorMap map_pl, const __grid_constant__ CUtensorMap map_d,
+                const __grid_constant__ CUtensorMap map_plsf, const __grid_constant__ CUtensorMap map_dsf,
                 const GemmParams p) {
   using C = Cfg2;
   extern __shared__ uint8_t smem_raw[];
@@ -690,6 +697,30 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           __syncwarp();
           if (++s == kStages2) { s = 0; ph ^= 1u; }
         }
+        if (p.delta && it.kb1 == p.k_blocks) {
+          // one stage per run of this tile's columns inside one delta block
+          int c = it.nt * kBN2;
+          const int c_end = min(c + (narrow ? 128 : kBN2), p.N);
+          while (c < c_end) {
+            const int blk = c / p.delta_block, p0 = c - blk * p.delta_block;
+            const int n = min(c_end - c, p.delta_block - p0);
+            if (!mbar_try_wait(empty_bar(s), ph ^ 1u)) ok = mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (elect_one()) {
+              if (rank == 0) mbar_expect_tx(full_bar(s), Cfg2::kTxBytes);
+              const uint32_t leader_full = leader_full0 + 8 * s;
+              const int prow = blk * p.M + row_a;  // row of the plane matrix [8 * M, 128]
+              tma2_load_2d(a_smem(s), &map_pl, leader_full, 0, prow);
+              tma2_load_2d(b_smem(s), &map_d, leader_full, 0, p0 + static_cast<int>(rank) * (n >> 1));
+              tma2_load_3d(sfa_smem(s), &map_plsf, leader_full, 0, 0, prow >> 7);
+              tma2_load_3d(sfb_smem(s), &map_dsf, leader_full, 0, 0, p0 >> 7);
+            }
+            __syncwarp();
+            if (++s == kStages2) { s = 0; ph ^= 1u; }
+            c += n;
+          }
+        }
       }
     }
   } else if (warp == 1) {
@@ -733,6 +764,30 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           acc = 1;
           sf_rot = (sf_rot + 1) & sf_mask;
           if (++s == kStages2) { s = 0; ph ^= 1u; }
+        }
+        if (ok && p.delta && it.kb1 == p.k_blocks) {
+          const int col0 = it.nt * kBN2;
+          int c = col0;
+          const int c_end = min(c + (it.nt >= p.n_wide ? 128 : kBN2), p.N);
+          while (c < c_end) {
+            const int blk = c / p.delta_block, p0 = c - blk * p.delta_block;
+            const int n = min(c_end - c, p.delta_block - p0);
+            if (!mbar_try_wait(full_bar(s), ph)) ok = mbar_wait(full_bar(s), ph, &abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t a_lo = a_lo0 + s * ((Cfg2::kABytes + Cfg2::kBBytes) >> 4);
+            const uint32_t sf_lo = sf_lo0 + s * (Cfg2::kSfBytes >> 4);
+            const uint32_t sfa_t = tmem_base + C::kSfaCol + 16u * sf_rot, sfb_t = sfa_t + 4;
+            if (elect_one())
+              tc2_kblock(d_tmem + static_cast<uint32_t>(c - col0), a_lo, a_lo + (Cfg2::kABytes >> 4), sf_lo, sfa_t, sfb_t,
+                         sfb_t + static_cast<uint32_t>((p0 & 127) >> 5), acc, empty_bar(s), pair_idesc(n));
+            __syncwarp();
+            acc = 1;
+            sf_rot = (sf_rot + 1) & sf_mask;
+            if (++s == kStages2) { s = 0; ph ^= 1u; }
+            c += n;
+          }
         }
         if (ok && elect_one()) tc2_commit_both(acc_full_bar(as));
         __syncwarp();
@@ -1075,8 +1130,18 @@ PairPlan plan_pair(int64_t M, int64_t N, int64_t K, bool allow_split) {
   return pl;
 }
 
+// Operands of the low-rank delta (all null = none): the eight activation planes [8 * M, 128] and the factor
+// [block, 128] whose rows are the output columns inside one block, both K-major e4m3 with TILED scales.
+struct DeltaOperands {
+  const uint8_t* planes_codes;
+  const uint8_t* planes_scales;
+  const uint8_t* d_codes;
+  const uint8_t* d_scales;
+  int64_t block;
+};
+
 int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmParams p, void* workspace, int64_t workspace_bytes,
-                cudaStream_t s) {
+                const DeltaOperands& delta, cudaStream_t s) {
   static PerDeviceOnce once;
   const cudaError_t attr_rc = per_device_once(once, [] {
     return cudaFuncSetAttribute(mx_gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg2::kSmemBytes);
@@ -1110,6 +1175,17 @@ int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmParams p, vo
                     (pl.ws_bytes ? make_part_map(&mp, p.pair_partial, static_cast<int64_t>(pl.tail_tiles) * pl.tail_splits)
                                  : make_c_map(&mp, p)),
                 ANIMA_E_CUDA, "mx_gemm: cuTensorMapEncodeTiled failed (driver entry point missing or bad operand)");
+  CUtensorMap mpl = ma, md = mb, mplsf = msa, mdsf = msb;   // placeholders when there is no delta
+  p.delta = delta.planes_codes ? 1 : 0;
+  p.delta_block = static_cast<int>(delta.block);
+  if (p.delta) {
+    const int64_t plane_rows = 8 * static_cast<int64_t>(p.M);
+    ANIMA_REQUIRE(make_map(&mpl, delta.planes_codes, plane_rows, 128, 128) &&
+                      make_map(&md, delta.d_codes, delta.block, 128, kBN2 / 2) &&
+                      make_sf_map(&mplsf, delta.planes_scales, plane_rows / 128, 1, 1) &&
+                      make_sf_map(&mdsf, delta.d_scales, ceil_div(delta.block, 128), 1, kSfbChunks2),
+                  ANIMA_E_CUDA, "mx_gemm_delta: cuTensorMapEncodeTiled failed (driver entry point missing or bad operand)");
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pl.pairs);
   cfg.blockDim = dim3(kThreads);
@@ -1122,7 +1198,7 @@ int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmParams p, vo
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const cudaError_t rc = cudaLaunchKernelEx(&cfg, mx_gemm2_kernel, ma, mb, msa, msb, mc, mp, p);
+  const cudaError_t rc = cudaLaunchKernelEx(&cfg, mx_gemm2_kernel, ma, mb, msa, msb, mc, mp, mpl, md, mplsf, mdsf, p);
   ANIMA_REQUIRE(rc == cudaSuccess, ANIMA_E_CUDA, "mx_gemm: cluster launch failed: %s", cudaGetErrorString(rc));
   if (pl.ws_bytes) {
     const int64_t threads = static_cast<int64_t>(pl.tail_tiles) * 256 * (kBN2 / 4);
@@ -1194,7 +1270,8 @@ using namespace anima;
 static int mx_gemm_impl(const uint8_t* a_codes, const uint8_t* a_scales, const uint8_t* b_codes,
                         const uint8_t* b_scales, void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
                         const void* bias, const void* residual, int64_t ldr, float alpha, int out_dtype,
-                        void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
+                        void* workspace, int64_t workspace_bytes, int32_t* status, void* stream,
+                        const DeltaOperands& delta = DeltaOperands{}) {
   ANIMA_REQUIRE(!residual || (aligned16(residual) && ldr >= N && ldr % 8 == 0), ANIMA_E_ALIGN,
                 "mx_gemm: residual must be 16-byte aligned with a row pitch that is a multiple of 8 elements");
   ANIMA_REQUIRE(a_codes && a_scales && b_codes && b_scales && c, ANIMA_E_ARG, "mx_gemm: null pointer");
@@ -1232,7 +1309,10 @@ static int mx_gemm_impl(const uint8_t* a_codes, const uint8_t* a_scales, const u
   p.alpha = alpha;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   ANIMA_REQUIRE(!workspace || aligned16(workspace), ANIMA_E_ALIGN, "mx_gemm: workspace must be 16-byte aligned");
-  if (use_pair(M, N)) return launch_pair(a_codes, b_codes, p, workspace, workspace_bytes, s);
+  if (use_pair(M, N)) return launch_pair(a_codes, b_codes, p, workspace, workspace_bytes, delta, s);
+  ANIMA_REQUIRE(!delta.planes_codes, ANIMA_E_UNSUPPORTED,
+                "mx_gemm_delta: M=%lld N=%lld runs on the one-CTA kernel, which has no delta K-blocks", (long long)M,
+                (long long)N);
   if (workspace) {
     int splits, kb_per;
     plan_splits(M, N, K, &splits, &kb_per);
@@ -1297,4 +1377,20 @@ extern "C" int anima_mx_gemm_set_clock_probe(void* device_buffer_3xint64) {
                 "mx_gemm_set_clock_probe: buffer must be 8-byte aligned");
   g_clock_probe[dev] = static_cast<long long*>(device_buffer_3xint64);
   return ANIMA_OK;
+}
+
+extern "C" int anima_mx_gemm_delta(const uint8_t* a_codes, const uint8_t* a_scales, const uint8_t* b_codes,
+                                   const uint8_t* b_scales, void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
+                                   const void* bias, int out_dtype, const uint8_t* planes_codes,
+                                   const uint8_t* planes_scales, const uint8_t* d_codes, const uint8_t* d_scales,
+                                   void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
+  ANIMA_REQUIRE(planes_codes && planes_scales && d_codes && d_scales, ANIMA_E_ARG, "mx_gemm_delta: null delta operand");
+  ANIMA_REQUIRE(aligned16(planes_codes) && aligned16(planes_scales) && aligned16(d_codes) && aligned16(d_scales),
+                ANIMA_E_ALIGN, "mx_gemm_delta: delta operands must be 16-byte aligned");
+  ANIMA_REQUIRE(M > 0 && N > 0 && M % 128 == 0 && N % 8 == 0 && (N / 8) % 64 == 0, ANIMA_E_SHAPE,
+                "mx_gemm_delta: needs M %% 128 == 0 and N / 8 a multiple of 64 (M=%lld N=%lld)", (long long)M,
+                (long long)N);
+  DeltaOperands delta{planes_codes, planes_scales, d_codes, d_scales, N / 8};
+  return mx_gemm_impl(a_codes, a_scales, b_codes, b_scales, c, M, N, K, ldc, bias, nullptr, 0, 1.f, out_dtype, workspace,
+                      workspace_bytes, status, stream, delta);
 }

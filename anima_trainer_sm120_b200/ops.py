@@ -189,6 +189,47 @@ def mx_gemm(a: MXOperand, b: MXOperand, *, bias: torch.Tensor | None = None,
     return out
 
 
+def can_fold_delta(M: int, N: int) -> bool:
+    """Shapes for which a T-LoKr delta can enter the base GEMM as extra K-blocks (:func:`mx_gemm_delta`)."""
+    return M > 128 and N > 128 and M % 128 == 0 and N % 8 == 0 and (N // 8) % 64 == 0
+
+
+def mx_gemm_delta(a: MXOperand, b: MXOperand, planes: MXOperand, d: MXOperand, *, bias: torch.Tensor | None = None,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+    """``C[m, i * N/8 + p] = (A . B^T)[m, i * N/8 + p] + planes[i * M + m, :] . d[p, :] (+ bias)`` as ONE GEMM: the
+    low-rank delta of a T-LoKr linear enters as extra K-blocks of the base product. ``planes`` is the
+    ``[8 * M, 128]`` operand written by :func:`tlokr_rank_mix_quant_planes`, ``d`` the ``[N / 8, 128]`` factor
+    (with any scalar already folded in). bf16 output, rounded once."""
+    dev = _lib.require_cuda(a.codes, a.scales, b.codes, b.scales, planes.codes, planes.scales, d.codes, d.scales, bias)
+    if any(op.layout != SCALES_TILED for op in (a, b, planes, d)):
+        raise ValueError("mx_gemm_delta needs TILED scales")
+    M, N, K = a.rows, b.rows, a.k
+    if a.k != b.k:
+        raise ValueError(f"contraction sizes differ: A has K={a.k}, B has K={b.k}")
+    if not can_fold_delta(M, N):
+        raise ValueError(f"mx_gemm_delta cannot take M={M}, N={N}")
+    if planes.codes.shape != (8 * M, 128) or d.codes.shape != (N // 8, 128):
+        raise ValueError(f"delta operands must be [8 * M, 128] and [N / 8, 128], got {tuple(planes.codes.shape)} "
+                         f"and {tuple(d.codes.shape)}")
+    if not all(t.is_contiguous() for t in (a.codes, b.codes, planes.codes, d.codes)):
+        raise ValueError("mx_gemm_delta operands must be contiguous (K-major)")
+    if bias is not None and (bias.dtype != BF16 or bias.numel() != N or not bias.is_contiguous()):
+        raise ValueError("bias must be contiguous bfloat16 of length N")
+    if out is None:
+        out = torch.empty((M, N), dtype=BF16, device=dev)
+    elif out.shape != (M, N) or out.dtype != BF16 or out.stride(1) != 1:
+        raise ValueError("out has the wrong shape, dtype or layout")
+    lib = _lib.load()
+    ws_bytes = check(lib.anima_mx_gemm_workspace_bytes(M, N, K))
+    ws = _lib.workspace(ws_bytes, dev, "gemm_splitk") if ws_bytes else None
+    with torch.cuda.device(dev):
+        check(lib.anima_mx_gemm_delta(
+            ptr(a.codes), ptr(a.scales), ptr(b.codes), ptr(b.scales), ptr(out), M, N, K, out.stride(0), ptr(bias), 0,
+            ptr(planes.codes), ptr(planes.scales), ptr(d.codes), ptr(d.scales), ptr(ws),
+            ws.numel() if ws is not None else 0, ptr(_lib.status_word(dev)), _lib.stream_ptr(dev)))
+    return out
+
+
 def _factor_flag(w1: torch.Tensor, w2: torch.Tensor) -> int:
     if w1.dtype != w2.dtype or w1.dtype not in (BF16, torch.float32):
         raise TypeError("LoKr factors must both be bfloat16 or both float32")
@@ -398,6 +439,33 @@ def tlokr_rank_mix_quant(hidden: torch.Tensor, c: torch.Tensor, mask: torch.Tens
             ptr(row.codes) if row else None, ptr(row.scales) if row else None,
             ptr(col.codes) if col else None, ptr(col.scales) if col else None, _lib.stream_ptr(dev)))
     return row, col, out
+
+
+def can_mix_to_planes(batch: int, n: int, rank: int) -> bool:
+    """Shapes for which the quantising mix can write its row form as eight planes (``rank`` is one K-block)."""
+    return rank == 128 and batch * n > 0 and (batch * n) % 128 == 0
+
+
+def tlokr_rank_mix_quant_planes(hidden: torch.Tensor, c: torch.Tensor, mask: torch.Tensor | None, transpose: bool, *,
+                                colwise: bool = False) -> tuple[MXOperand, MXOperand | None]:
+    """The 8x8 mix of ``hidden [batch, n, 8, rank]`` leaving as the MXFP8 row form laid out as eight planes
+    (row ``i`` of item ``t`` at row ``i * items + t`` of a ``[8 * items, rank]`` operand, which
+    :func:`mx_gemm_delta` consumes), and optionally the usual transposed column form ``[rank, items * 8]``."""
+    dev = _lib.require_cuda(hidden, c, mask)
+    batch, n, _, rank = hidden.shape
+    R = batch * n * 8
+    planes = MXOperand(torch.empty((R, rank), dtype=torch.uint8, device=dev),
+                       torch.empty(scales_bytes(R, rank, SCALES_TILED), dtype=torch.uint8, device=dev), SCALES_TILED)
+    col = None
+    if colwise:
+        col = MXOperand(torch.empty((rank, R), dtype=torch.uint8, device=dev),
+                        torch.empty(scales_bytes(rank, R, SCALES_TILED), dtype=torch.uint8, device=dev), SCALES_TILED)
+    with torch.cuda.device(dev):
+        check(_lib.load().anima_tlokr_rank_mix_quant_planes(
+            ptr(hidden), ptr(c), ptr(mask), batch, n, rank, 1 if transpose else 0, ptr(planes.codes),
+            ptr(planes.scales), ptr(col.codes) if col else None, ptr(col.scales) if col else None,
+            _lib.stream_ptr(dev)))
+    return planes, col
 
 
 def tlokr_rank_mix_wgrad(grad_mixed: torch.Tensor, hidden: torch.Tensor, mask: torch.Tensor | None

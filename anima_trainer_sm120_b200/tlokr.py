@@ -20,6 +20,7 @@ variant uses ``torch.matmul`` for the factor GEMMs (a library GEMM, as in the re
 from __future__ import annotations
 
 import math
+import os
 from contextvars import ContextVar
 from dataclasses import dataclass, field
 from types import MethodType
@@ -245,6 +246,34 @@ def _factor_forms(p: torch.Tensor, *, quantise: bool):
     return val
 
 
+def _scaled_row_form(p: torch.Tensor, alpha: float) -> ops.MXOperand:
+    """Row-wise MXFP8 operand of ``alpha * p`` rounded to bf16 (the factor a folded delta multiplies by), kept on
+    a leaf parameter like :func:`_factor_forms`."""
+    cacheable = p.is_leaf and isinstance(p, nn.Parameter)
+    key = (p._version, p.data_ptr(), float(alpha))
+    if cacheable:
+        hit = getattr(p, "_anima_mx_scaled_row", None)
+        if hit is not None and hit[0] == key:
+            return hit[1]
+    with torch.no_grad():
+        val = ops.mx_quantize((p.detach().float() * float(alpha)).to(BF16).contiguous(), rowwise=True)[0]
+    if cacheable:
+        p._anima_mx_scaled_row = (key, val)
+    return val
+
+
+# Fold the structured delta into the base GEMMs as extra K-blocks (``ops.mx_gemm_delta``) where the shapes allow:
+# the base projection and ``+ alpha * delta`` (forward), the base input gradient and ``+ grad_hidden @ B``
+# (backward) are then one GEMM each, and the output is neither re-read nor rounded twice. False keeps the
+# separate add-GEMMs (for comparison; ANIMA_TLOKR_FOLD_DELTA=0 sets it at import).
+FOLD_DELTA = os.environ.get("ANIMA_TLOKR_FOLD_DELTA", "1") != "0"
+
+
+def _can_fold(rows: int, n_cols: int, factor_dim: int, batch: int, rank: int) -> bool:
+    return (FOLD_DELTA and factor_dim == 8 and ops.can_fold_delta(rows, n_cols) and rows % batch == 0
+            and ops.can_mix_to_planes(batch, rows // batch, rank))
+
+
 def _q(t2d: torch.Tensor, *, col: bool = False):
     return ops.mx_quantize(t2d.contiguous() if t2d.dtype == BF16 else t2d.to(BF16).contiguous(),
                            rowwise=True, colwise=col)
@@ -380,8 +409,14 @@ def _mx_linear_fwd(x_row, gq, lead_shape, W_mx, bias, w1, w2_a, w2_b, mask, alph
     aq, aq_col = _factor_forms(w2_a, quantise=True)      # A [vp, r]: row form for out, column form for dgrad
     bq, bq_col = _factor_forms(w2_b, quantise=True)      # B [r, vq]
     y = torch.empty(*lead_shape, n_out, dtype=BF16, device=x_row.codes.device)
-    ops.mx_gemm(x_row, W_mx.row, bias=_bias_bf16(bias), out=y.view(-1, n_out))
     hidden = ops.mx_gemm(gq, bq).view(lead_shape[0], -1, uq, rank)
+    if _can_fold(x_row.rows, n_out, c.shape[0], lead_shape[0], rank) and n_out == c.shape[0] * vp:
+        # one GEMM: the mixed hidden tensor (eight planes) times alpha * A enters as extra K-blocks
+        planes, _ = ops.tlokr_rank_mix_quant_planes(hidden, c, None if mask is None else mask.contiguous().to(BF16), False)
+        ops.mx_gemm_delta(x_row, W_mx.row, planes, _scaled_row_form(w2_a, alpha), bias=_bias_bf16(bias),
+                          out=y.view(-1, n_out))
+        return y, (aq_col, bq, bq_col)
+    ops.mx_gemm(x_row, W_mx.row, bias=_bias_bf16(bias), out=y.view(-1, n_out))
     mq, _ = _mix_operands(hidden, c, mask, False, row=True, col=False)
     res = y.view(-1, vp)
     ops.mx_gemm(mq, aq, residual=res, alpha=float(alpha), out=res)       # y += alpha * delta
@@ -417,13 +452,22 @@ def _mx_linear_bwd(quant_grad, quant_grouped, lead_shape, K, W_mx, w1, w2_a, w2_
         rows *= d
     gbq, gbq_col = quant_grad(rows * up, vp)                                        # grad as [rows * up, vp]
     g_x = torch.empty(*lead_shape, K, dtype=BF16, device=gbq.codes.device)
-    ops.mx_gemm(ops.mx_regroup(gbq, rows, up * vp), W_mx.col, out=g_x.view(rows, K))   # base dgrad
+    fold = _can_fold(rows, K, uq, lead_shape[0], rank) and K == uq * vq
+    if not fold:
+        ops.mx_gemm(ops.mx_regroup(gbq, rows, up * vp), W_mx.col, out=g_x.view(rows, K))   # base dgrad
     gq, gq_col = quant_grouped(rows * uq, vq)
     hidden = ops.mx_gemm(gq, bq).view(lead_shape[0], -1, uq, rank)
     _, mq_col = _mix_operands(hidden, c, mask, False, row=False, col=True)
     g_a = ops.mx_gemm(gbq_col, mq_col, out_dtype=torch.float32, alpha=alpha)        # alpha * grad^T @ mixed  [vp, r]
     g_mixed = ops.mx_gemm(gbq, aq_col, alpha=alpha).view(*hidden.shape)             # alpha * grad @ A        [.., r]
     g_c = rank_mix_wgrad(g_mixed, hidden, mask)
+    if fold:
+        # grad_hidden leaves as eight planes + its column form; base dgrad and + grad_hidden @ B are one GEMM
+        gh_planes, ghq_col = ops.tlokr_rank_mix_quant_planes(
+            g_mixed, c, None if mask is None else mask.contiguous().to(BF16), True, colwise=True)
+        g_b = ops.mx_gemm(ghq_col, gq_col, out_dtype=torch.float32)                 # grad_hidden^T @ grouped [r, vq]
+        ops.mx_gemm_delta(ops.mx_regroup(gbq, rows, up * vp), W_mx.col, gh_planes, bq_col, out=g_x.view(rows, K))
+        return g_x, g_c.to(w1.dtype), g_a.to(w2_a.dtype), g_b.to(w2_b.dtype)
     ghq, ghq_col = _mix_operands(g_mixed, c, mask, True, row=True, col=True)        # of grad_hidden
     g_b = ops.mx_gemm(ghq_col, gq_col, out_dtype=torch.float32)                     # grad_hidden^T @ grouped [r, vq]
     res = g_x.view(-1, vq)

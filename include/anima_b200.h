@@ -157,6 +157,25 @@ int anima_mx_gemm_ex(const uint8_t* a_codes, const uint8_t* a_scales,
                      int out_dtype, void* workspace, int64_t workspace_bytes,
                      int32_t* status, void* stream);
 
+/* A T-LoKr linear as ONE GEMM: the low-rank delta enters as extra K-blocks of the base product.
+ * ref: tlokr.py:738-759 (base = fp8_frozen_linear(x); delta = _FP8StructuredLoKr(x); torch.add(base, delta,
+ * alpha=)) and, for the input gradient, :531-532 (grad_hidden @ B) added to the base dgrad.
+ *   C[m, i * (N/8) + p] = sum_k A[m,k] B[i*(N/8)+p, k]  +  sum_r planes[i*M + m, r] * d[p, r]   (+ bias)
+ * planes: e4m3 [8 * M, 128] + TILED scales of that matrix, plane i = rows [i*M, (i+1)*M): the mixed hidden
+ * tensor (forward) or the mixed gradient (backward) as written by anima_tlokr_rank_mix_quant_planes.
+ * d: e4m3 [N/8, 128] + TILED scales: the factor whose rows are the output columns inside a block (alpha * A for
+ * the forward, the column-wise form of B for the input gradient); a scalar alpha is folded into d by the caller.
+ * The accumulator holds base + delta in fp32 and is rounded once. The rank is 128 (one K-block). Needs
+ * M % 128 == 0, N/8 % 64 == 0 and a shape of the CTA-pair kernel (M > 128, N > 128), else ANIMA_E_SHAPE /
+ * ANIMA_E_UNSUPPORTED. workspace as for anima_mx_gemm_ex (anima_mx_gemm_workspace_bytes). */
+int anima_mx_gemm_delta(const uint8_t* a_codes, const uint8_t* a_scales,
+                        const uint8_t* b_codes, const uint8_t* b_scales,
+                        void* c, int64_t M, int64_t N, int64_t K, int64_t ldc,
+                        const void* bias_bf16, int out_dtype,
+                        const uint8_t* planes_codes, const uint8_t* planes_scales,
+                        const uint8_t* d_codes, const uint8_t* d_scales,
+                        void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
+
 /* The work list the CTA-pair kernel uses for a problem on the current device (no reference counterpart; for
  * tests and tuning, nothing is launched): out8 = { CTA pairs launched, 192-wide tile columns, 1 if a narrow
  * last column (<= 128 outputs, computed with N = 128 instructions) follows them, whole-tile items dealt

@@ -310,3 +310,62 @@ def test_agrees_with_the_vendor_library_mxfp8_gemm(M, N, K):
     lib.check_status_word(got.device)
     torch.testing.assert_close(got.float(), want.float(), rtol=RTOL, atol=ATOL)
     assert float((got.float() - want.float()).abs().max()) <= 0.0625 * float(want.float().abs().max()) / 8
+
+
+def _planes_from_rows(t: torch.Tensor) -> torch.Tensor:
+    """[items, 8, r] -> the plane order [8 * items, r] (row i of item t at i * items + t)."""
+    return t.transpose(0, 1).reshape(-1, t.shape[-1]).contiguous()
+
+
+@pytest.mark.parametrize("M,N,K", [
+    (256, 2048, 256),     # blocks of 256 columns against 192-wide tiles: runs of 192, 64|128, 128|64, 192 ... and a narrow tile
+    (384, 1024, 128),     # blocks of 128: a tile touches two or three blocks; the last row tile is half empty
+    (1024, 512, 512),     # blocks of 64
+    (512, 512, 16384),    # fewer tiles than CTA pairs and a long contraction: every tile is K-split, the delta rides the last range
+    (4096, 2048, 1024),   # cross-attention k / v on the text tokens
+])
+def test_low_rank_delta_as_extra_k_blocks(M, N, K):
+    """anima_mx_gemm_delta: C = A.B^T + bias + sum_r planes[i*M + m, r] * d[p, r] for column i * N/8 + p, against
+    the oracle on identical codes; the planes come from the quantising mix, checked against its plain row form."""
+    ops, lib = _ops()
+    from oracle import tlokr as OT
+    g = torch.Generator().manual_seed(M + N + K)
+    x = _acts(M, K, 31).cuda()
+    w = _acts(N, K, 32, std=0.02, outliers=False).cuda()
+    bias = (torch.randn(N, generator=g) * 0.3).to(BF16).cuda()
+    blk = N // 8
+    batch = 2
+    hidden = torch.randn(batch, M // batch, 8, 128, generator=g).to(BF16).cuda()
+    cmat = (torch.randn(8, 8, generator=g) * 0.4).to(BF16).cuda()
+    mask = OT.rank_mask(torch.rand(batch, generator=g), max_rank=128, min_rank=64, dtype=BF16).cuda()
+    d = (torch.randn(blk, 128, generator=g) * 0.05).to(BF16).cuda()
+    xa, _ = ops.mx_quantize(x, rowwise=True, layout=0)
+    wb, _ = ops.mx_quantize(w, rowwise=True, layout=0)
+    dq, _ = ops.mx_quantize(d, rowwise=True, layout=0)
+    planes, col = ops.tlokr_rank_mix_quant_planes(hidden, cmat, mask, False, colwise=True)
+    # the planes hold the codes of the plain row form, reordered; the column form is unchanged
+    row, col2, _ = ops.tlokr_rank_mix_quant(hidden, cmat, mask, False, rowwise=True, colwise=True)
+    assert torch.equal(planes.codes, _planes_from_rows(row.codes.view(M, 8, 128)))
+    assert torch.equal(col.codes, col2.codes) and torch.equal(col.scales, col2.scales)
+    mixed = ops.tlokr_rank_mix(hidden, cmat, mask, False)                     # bf16 [batch, n, 8, 128]
+    pl_plain, _ = ops.mx_quantize(_planes_from_rows(mixed.view(M, 8, 128)), rowwise=True, layout=0)
+    assert torch.equal(pl_plain.codes, planes.codes)
+    assert torch.equal(ops.mx_retile(pl_plain).scales, planes.scales)
+    c = ops.mx_gemm_delta(ops.mx_retile(xa), ops.mx_retile(wb), planes, ops.mx_retile(dq), bias=bias)
+    again = ops.mx_gemm_delta(ops.mx_retile(xa), ops.mx_retile(wb), planes, ops.mx_retile(dq), bias=bias)
+    torch.cuda.synchronize()
+    lib.check_status_word(c.device)
+    assert torch.equal(c, again)
+    base = _oracle_product(xa, wb, bias, out_bf16=False)
+    delta = _oracle_product(pl_plain, dq, out_bf16=False).reshape(8, M, blk).transpose(1, 0, 2).reshape(M, N)
+    want = base + delta
+    got = c.float().cpu().numpy()
+    bound = ATOL + RTOL * (np.abs(base) + np.abs(delta))
+    assert (np.abs(got - want) <= bound).all(), float(np.abs(got - want).max())
+    assert float(np.abs(delta).max()) > 0.05 * float(np.abs(base).max())      # the delta is not a rounding-level term
+
+
+def test_delta_gemm_rejects_shapes_it_cannot_tile():
+    ops, _ = _ops()
+    assert not ops.can_fold_delta(128, 2048) and not ops.can_fold_delta(200, 2048) and not ops.can_fold_delta(256, 1032)
+    assert ops.can_fold_delta(32768, 8192) and ops.can_fold_delta(4096, 1024)
