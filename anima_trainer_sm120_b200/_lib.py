@@ -69,6 +69,7 @@ PROTOTYPES: dict[str, tuple[object, list[object]]] = {
     "anima_tlokr_rank_mix": (c_int, [P, P, P, I64, I64, I64, c_int, P, P]),
     "anima_tlokr_rank_mix_quant": (c_int, [P, P, P, I64, I64, I64, c_int, P, P, P, P, P, P]),
     "anima_tlokr_rank_mix_quant_planes": (c_int, [P, P, P, I64, I64, I64, c_int, P, P, P, P, P]),
+    "anima_tlokr_hidden_mix_planes": (c_int, [P, P, P, P, P, P, I64, I64, I64, c_int, P, P, P, P, P]),
     "anima_tlokr_rank_mix_wgrad_workspace_bytes": (I64, [I64, I64, I64]),
     "anima_tlokr_rank_mix_wgrad": (c_int, [P, P, P, I64, I64, I64, P, P, I64, P]),
     "anima_rmsnorm_rope_fwd": (c_int, [P, P, P, P, c_float, I64, I64, I64, I64, P, P, P]),

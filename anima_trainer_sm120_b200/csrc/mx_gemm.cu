@@ -37,6 +37,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "mx_quantize_tile.cuh"
 #include "tma_util.cuh"
 
 namespace anima {
@@ -143,6 +144,17 @@ struct GemmParams {
   int full_items, tail_tiles, tail_splits, tail_kbs, tail_shift;
   float* pair_partial;
   int sf_bufs;  // tensor-memory scale buffers the K-blocks rotate through (1, 2 or 4)
+  // Mix epilogue of the one-CTA kernel, N = 128 (anima_tlokr_hidden_mix_planes): the accumulator tile is the
+  // T-LoKr hidden tensor of 16 tokens (row = token * 8 + j); instead of being stored it is rounded to bf16,
+  // mixed over j with the 8 x 8 factor inside each group of eight lanes, masked, rounded, quantised (one MX
+  // block per row and 32-column chunk) and written as e4m3 planes (row i of token t at plane row i * items + t).
+  const __nv_bfloat16* mix_c;     // [8, 8]
+  const __nv_bfloat16* mix_mask;  // [batch, 128] or null
+  uint8_t* mix_codes;             // [8 * items, 128]; null = ordinary epilogue
+  uint8_t* mix_scales;            // TILED scales of that matrix
+  __nv_bfloat16* mix_hidden;      // optional bf16 copy of the hidden tile rows [M, 128]
+  int64_t mix_items, mix_n_per_batch;
+  int mix_transpose;
   // Low-rank delta folded in as extra K-blocks (anima_mx_gemm_delta): output columns [i * delta_block,
   // (i + 1) * delta_block) also receive planes[i][m, 0:128] . d[p, 0:128]^T. For a tile, every run of its
   // columns inside one block is one more pipeline stage (A slot: 128 rows of plane i; B slot: the factor rows of
@@ -256,6 +268,67 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int co
       }
     }
   }
+}
+
+// One 32-column chunk of the mix epilogue for the thread that owns accumulator row (token, j = lane % 8) and
+// produces output row (token, i = lane % 8). The arithmetic and its order are those of the GEMM's bf16 store
+// followed by rank_mix_quant_kernel (fp32 fma over j ascending from 0, mask, bf16 rounding, MX quantisation of
+// the rounded values), so codes and scale are bit-identical to running the two kernels.
+__device__ __forceinline__ void mix_chunk(const uint32_t (&v)[32], const float (&cw)[8], int lane,
+                                          const __nv_bfloat16* mask_chunk, __nv_bfloat16* hidden_chunk,
+                                          uint4 (&codes)[2], uint32_t& scale_byte) {
+  uint32_t pk[16];  // the chunk rounded to bf16, two columns per word
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1]));
+    pk[k] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  if (hidden_chunk != nullptr) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      stg_stream16(hidden_chunk + 8 * q, make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]));
+  }
+  float acc[32];
+#pragma unroll
+  for (int k = 0; k < 32; ++k) acc[k] = 0.f;
+  const int base = lane & 24;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float w = cw[j];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const uint32_t other = __shfl_sync(0xffffffffu, pk[k], base + j);
+      acc[2 * k] = fmaf(__uint_as_float(other << 16), w, acc[2 * k]);
+      acc[2 * k + 1] = fmaf(__uint_as_float(other & 0xffff0000u), w, acc[2 * k + 1]);
+    }
+  }
+  if (mask_chunk != nullptr) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float m[8];
+      unpack8(*reinterpret_cast<const uint4*>(mask_chunk + 8 * q), m);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[8 * q + e] *= m[e];
+    }
+  }
+  float f[32];
+  float amax = 0.f;
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    const float2 r = __bfloat1622float2(__floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]));
+    f[2 * k] = r.x;
+    f[2 * k + 1] = r.y;
+    amax = fmaxf(amax, fmaxf(fabsf(r.x), fabsf(r.y)));
+  }
+  const int ex = mxq::mx_exponent(fmaxf(amax, mxq::kAmaxFloor));
+  const float inv = mxq::mx_inv_scale(ex);
+  uint32_t w8[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q)
+    w8[q] = mxq::e4m3x2(f[4 * q] * inv, f[4 * q + 1] * inv) | (mxq::e4m3x2(f[4 * q + 2] * inv, f[4 * q + 3] * inv) << 16);
+  codes[0] = make_uint4(w8[0], w8[1], w8[2], w8[3]);
+  codes[1] = make_uint4(w8[4], w8[5], w8[6], w8[7]);
+  scale_byte = static_cast<uint32_t>(ex + 127);
 }
 
 template <int BN>
@@ -380,6 +453,49 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int quad = warp & 3;  // tensor-memory lane quadrant this warp may access
     bool ok = true;
     int it = 0;
+    if (BN == 128 && p.mix_codes != nullptr) {
+      // mix epilogue: see GemmParams. splits == 1 here, so an item is a tile.
+      float cw[8];
+      {
+        const int i = lane & 7;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) cw[j] = __bfloat162float(p.mix_transpose ? p.mix_c[j * 8 + i] : p.mix_c[i * 8 + j]);
+      }
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++it) {
+        const int mt = item;  // n_tiles == 1
+        const int as = it & 1;
+        if (!mbar_wait(acc_full_bar(as), (it >> 1) & 1u, &abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const int64_t row = static_cast<int64_t>(mt) * BM + quad * 32 + lane;   // accumulator row (token * 8 + j)
+        const int64_t token = row >> 3;
+        const int64_t prow = static_cast<int64_t>(lane & 7) * p.mix_items + token;   // plane row this thread writes
+        const __nv_bfloat16* mask_row = p.mix_mask ? p.mix_mask + (token / p.mix_n_per_batch) * 128 : nullptr;
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + (as ? C::kAcc1Col : 0);
+        uint32_t scale_word = 0;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tc_ld32(t_row + c * 32, v);
+          tc_wait_ld();
+          if (c == 0) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_free_bar);
+          }
+          uint4 codes[2];
+          uint32_t sb;
+          mix_chunk(v, cw, lane, mask_row ? mask_row + c * 32 : nullptr,
+                    p.mix_hidden ? p.mix_hidden + row * 128 + c * 32 : nullptr, codes, sb);
+          uint8_t* dst = p.mix_codes + prow * 128 + c * 32;
+          stg_stream16(dst, codes[0]);
+          stg_stream16(dst + 16, codes[1]);
+          scale_word |= sb << (8 * c);
+        }
+        // the row's four scale bytes are adjacent in the tiled layout (one 128-column chunk per row tile)
+        *reinterpret_cast<uint32_t*>(p.mix_scales + (prow >> 7) * 512 + mxq::tiled_offset(static_cast<int>(prow & 127), 0)) =
+            scale_word;
+      }
+    } else {
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++it) {
       const int tile = item / p.splits, split = item - tile * p.splits;
       const int mt = tile / p.n_tiles, nt = tile - mt * p.n_tiles;
@@ -411,6 +527,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         store_chunk(dst, row, nt * BN + chunk * 32, v);
       }
+    }
     }
   }
 
@@ -1393,4 +1510,51 @@ extern "C" int anima_mx_gemm_delta(const uint8_t* a_codes, const uint8_t* a_scal
   DeltaOperands delta{planes_codes, planes_scales, d_codes, d_scales, N / 8};
   return mx_gemm_impl(a_codes, a_scales, b_codes, b_scales, c, M, N, K, ldc, bias, nullptr, 0, 1.f, out_dtype, workspace,
                       workspace_bytes, status, stream, delta);
+}
+
+extern "C" int anima_tlokr_hidden_mix_planes(const uint8_t* g_codes, const uint8_t* g_scales, const uint8_t* f_codes,
+                                             const uint8_t* f_scales, const void* c, const void* mask, int64_t batch,
+                                             int64_t n_per_batch, int64_t k, int transpose, void* hidden_out,
+                                             uint8_t* planes_codes, uint8_t* planes_scales, int32_t* status,
+                                             void* stream) {
+  ANIMA_REQUIRE(g_codes && g_scales && f_codes && f_scales && c && planes_codes && planes_scales, ANIMA_E_ARG,
+                "tlokr_hidden_mix_planes: null pointer");
+  ANIMA_REQUIRE(batch > 0 && n_per_batch > 0 && k > 0, ANIMA_E_ARG, "tlokr_hidden_mix_planes: bad sizes");
+  const int64_t items = batch * n_per_batch, M = items * 8;
+  ANIMA_REQUIRE(items % 128 == 0 && k % 32 == 0, ANIMA_E_SHAPE,
+                "tlokr_hidden_mix_planes: batch * n = %lld must be a multiple of 128 and k = %lld of 32", (long long)items,
+                (long long)k);
+  ANIMA_REQUIRE(M < (1ll << 31) - 256 && k < (1ll << 31) - 256, ANIMA_E_TOO_LARGE, "tlokr_hidden_mix_planes: too large");
+  ANIMA_REQUIRE(aligned16(g_codes) && aligned16(g_scales) && aligned16(f_codes) && aligned16(f_scales) &&
+                    aligned16(planes_codes) && aligned16(planes_scales) && (!mask || aligned16(mask)) &&
+                    (!hidden_out || aligned16(hidden_out)),
+                ANIMA_E_ALIGN, "tlokr_hidden_mix_planes: buffers must be 16-byte aligned");
+  GemmParams p{};
+  p.a_scales = g_scales;
+  p.b_scales = f_scales;
+  p.c = planes_codes;   // not written through the ordinary epilogue
+  p.status = status;
+  p.M = static_cast<int>(M);
+  p.N = 128;
+  p.K = static_cast<int>(k);
+  p.ldc = 128;
+  p.m_tiles = static_cast<int>(M / BM);
+  p.k_blocks = static_cast<int>(ceil_div(k, BK));
+  p.sfa_rt = p.m_tiles;
+  p.sfb_rt = 1;
+  p.splits = 1;
+  p.kb_per_split = p.k_blocks;
+  p.alpha = 1.f;
+  p.mix_c = static_cast<const __nv_bfloat16*>(c);
+  p.mix_mask = static_cast<const __nv_bfloat16*>(mask);
+  p.mix_codes = planes_codes;
+  p.mix_scales = planes_scales;
+  p.mix_hidden = static_cast<__nv_bfloat16*>(hidden_out);
+  p.mix_items = items;
+  p.mix_n_per_batch = n_per_batch;
+  p.mix_transpose = transpose ? 1 : 0;
+  CUtensorMap ma, mb;
+  ANIMA_REQUIRE(make_map(&ma, g_codes, M, k, BM) && make_map(&mb, f_codes, 128, k, 128), ANIMA_E_CUDA,
+                "tlokr_hidden_mix_planes: cuTensorMapEncodeTiled failed (driver entry point missing or bad operand)");
+  return launch<128>(ma, mb, p, static_cast<cudaStream_t>(stream));
 }

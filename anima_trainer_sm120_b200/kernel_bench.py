@@ -188,6 +188,8 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
             lambda: ops.gated_add_adaln_fwd(xa, ga, y2, sc, sh, 1e-6, HW))
         hbm("gated_add + adaln fwd + row-wise MXFP8 operand of y", [BT, HW, D], int(M * D * 9.03125) + M * 8,
             lambda: ops.gated_add_adaln_fwd(xa, ga, y2, sc, sh, 1e-6, HW, quant=True))
+        hbm("gated_add + adaln bwd (one pass)", [BT, HW, D], M * D * 12 + M * 8,
+            lambda: ops.gated_add_adaln_bwd(dy, y2, xa, sc, mean, rstd, y2, ga, HW))
         hid = (torch.randn(8, M // 8, 8, 128, device="cuda")).to(BF16)
         gm = torch.randn_like(hid)
         c = _acts(8, 8)
@@ -200,6 +202,16 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
         hbm("tlokr_rank_mix + row and column operands (no bf16 output)", list(hid.shape), int(hid.numel() * 4.0625),
             lambda: ops.tlokr_rank_mix_quant(hid, c, mask, True, rowwise=True, colwise=True))
         hbm("tlokr_rank_mix_wgrad", list(hid.shape), hid.numel() * 4, lambda: ops.tlokr_rank_mix_wgrad(gm, hid, mask))
+        hbm("tlokr_rank_mix + row form as planes and column operand", list(hid.shape), int(hid.numel() * 4.0625),
+            lambda: ops.tlokr_rank_mix_quant_planes(hid, c, mask, True, colwise=True))
+        # hidden = grouped . B^T, mix, mask, quantise in one kernel: reads the grouped codes, writes the planes
+        xg = _acts(M * 8, 256)
+        xgq, _ = ops.mx_quantize(xg, rowwise=True)
+        bq, _ = ops.mx_quantize(_acts(128, 256, 0.2), rowwise=True)
+        hbm("tlokr hidden GEMM + mix + quantise to planes (one kernel)", [8, M // 8, 8, 256],
+            int(M * 8 * (256 * 1.03125 + 128 * 1.03125)), lambda: ops.tlokr_hidden_mix_planes(xgq, bq, c, mask, 8, False))
+        hbm("mx_scales_regroup", [M, 2048], M * 2048 // 32 * 2, lambda: ops.mx_regroup(xgq, M, 2048))
+        del xg, xgq
         hh, gg = _acts(M, 8192), _acts(M, 8192)
         nh = M * 8192
         hbm("mx_quantize_gelu rowwise", [M, 8192], int(nh * 3.03125), lambda: ops.mx_quantize_gelu(hh, rowwise=True))
@@ -257,6 +269,13 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
             tensor("mx_gemm fwd", [M, N, K], fl, lambda: ops.mx_gemm(xr, wr, out=y))
             tensor("mx_gemm dgrad", [M, K, N], fl, lambda: ops.mx_gemm(gr, wc, out=dx))
             tensor("mx_gemm wgrad (fp32 out)", [N, K, M], fl, lambda: ops.mx_gemm(gc, xc, out_dtype=torch.float32, out=dw))
+            if ops.can_fold_delta(M, N):
+                # the T-LoKr linear as one GEMM: one more K-block per run of a tile's columns inside a delta block
+                pl, _ = ops.mx_quantize(_acts(8 * M, 128), rowwise=True)
+                dq, _ = ops.mx_quantize(_acts(N // 8, 128, 0.05), rowwise=True)
+                tensor("mx_gemm_delta fwd (base + rank-128 delta)", [M, N, K], 2.0 * M * N * (K + 128),
+                       lambda: ops.mx_gemm_delta(xr, wr, pl, dq, out=y))
+                del pl, dq
             if yardstick:
                 # the vendor library's MXFP8 GEMM on the SAME operands (its swizzled scale layout is the
                 # 128 x 4 tiled layout): a measured ceiling to read the kernel against, not a code path
@@ -267,6 +286,14 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
                 except Exception as e:  # noqa: BLE001 - the yardstick is optional
                     print(json.dumps({"kernel": "yardstick: cuBLASLt MXFP8", "unavailable": str(e)[:200]}), flush=True)
             del x, w, gy, xr, xc, wr, wc, gr, gc, y, dx, dw
+        # the T-LoKr factor gradients: small outputs over a contraction of rows * 8, split over K on the one-CTA kernel
+        R8 = M * 8
+        for (m_, n_) in [(256, 128), (128, 256), (1024, 128)]:
+            aq, _ = ops.mx_quantize(_acts(m_, R8, 0.05), rowwise=True)
+            bq2, _ = ops.mx_quantize(_acts(n_, R8, 0.05), rowwise=True)
+            tensor("mx_gemm split-K factor gradient (fp32 out)", [m_, n_, R8], 2.0 * m_ * n_ * R8,
+                   lambda: ops.mx_gemm(aq, bq2, out_dtype=torch.float32))
+            del aq, bq2
         _lib.check_status_word(torch.device("cuda", torch.cuda.current_device()))
     return out
 

@@ -468,6 +468,37 @@ def tlokr_rank_mix_quant_planes(hidden: torch.Tensor, c: torch.Tensor, mask: tor
     return planes, col
 
 
+def tlokr_hidden_mix_planes(g: MXOperand, f: MXOperand, c: torch.Tensor, mask: torch.Tensor | None, batch: int,
+                            transpose: bool = False, *, want_hidden: bool = False
+                            ) -> tuple[MXOperand, torch.Tensor | None]:
+    """``hidden = g . f^T`` (``g [batch * n * 8, k]``, ``f [128, k]``), the 8x8 mix, the mask and the MXFP8
+    quantisation of the mixed tensor in ONE kernel; returns the eight-plane operand (as
+    :func:`tlokr_rank_mix_quant_planes`) and, with ``want_hidden``, the bf16 hidden tensor ``[batch, n, 8, 128]``,
+    which otherwise never leaves the SM. Bit-identical to ``mx_gemm`` followed by the quantising mix."""
+    dev = _lib.require_cuda(g.codes, g.scales, f.codes, f.scales, c, mask)
+    if g.layout != SCALES_TILED or f.layout != SCALES_TILED:
+        raise ValueError("tlokr_hidden_mix_planes needs TILED scales")
+    R, k = g.rows, g.k
+    if f.codes.shape != (128, k):
+        raise ValueError(f"the factor operand must be [128, {k}], got {tuple(f.codes.shape)}")
+    if R % (8 * batch) or not can_mix_to_planes(batch, R // (8 * batch), 128):
+        raise ValueError(f"cannot mix {R} grouped rows of {batch} samples into planes")
+    if c.dtype != BF16 or c.shape != (8, 8) or not c.is_contiguous():
+        raise ValueError("c must be contiguous bfloat16 [8, 8]")
+    if mask is not None and (mask.dtype != BF16 or mask.shape != (batch, 128) or not mask.is_contiguous()):
+        raise ValueError("mask must be contiguous bfloat16 [batch, 128]")
+    n = R // (8 * batch)
+    planes = MXOperand(torch.empty((R, 128), dtype=torch.uint8, device=dev),
+                       torch.empty(scales_bytes(R, 128, SCALES_TILED), dtype=torch.uint8, device=dev), SCALES_TILED)
+    hidden = torch.empty((batch, n, 8, 128), dtype=BF16, device=dev) if want_hidden else None
+    with torch.cuda.device(dev):
+        check(_lib.load().anima_tlokr_hidden_mix_planes(
+            ptr(g.codes), ptr(g.scales), ptr(f.codes), ptr(f.scales), ptr(c), ptr(mask), batch, n, k,
+            1 if transpose else 0, ptr(hidden), ptr(planes.codes), ptr(planes.scales), ptr(_lib.status_word(dev)),
+            _lib.stream_ptr(dev)))
+    return planes, hidden
+
+
 def tlokr_rank_mix_wgrad(grad_mixed: torch.Tensor, hidden: torch.Tensor, mask: torch.Tensor | None
                          ) -> torch.Tensor:
     dev = _lib.require_cuda(grad_mixed, hidden, mask)

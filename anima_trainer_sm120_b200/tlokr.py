@@ -269,6 +269,11 @@ def _scaled_row_form(p: torch.Tensor, alpha: float) -> ops.MXOperand:
 FOLD_DELTA = os.environ.get("ANIMA_TLOKR_FOLD_DELTA", "1") != "0"
 
 
+# Compute hidden, the mix and the quantisation of the mixed tensor in one kernel in the forward chain
+# (``ops.tlokr_hidden_mix_planes``); False runs the factor GEMM and the quantising mix as two kernels (same bits).
+FUSE_HIDDEN_MIX = os.environ.get("ANIMA_TLOKR_FUSE_HIDDEN_MIX", "1") != "0"
+
+
 def _can_fold(rows: int, n_cols: int, factor_dim: int, batch: int, rank: int) -> bool:
     return (FOLD_DELTA and factor_dim == 8 and ops.can_fold_delta(rows, n_cols) and rows % batch == 0
             and ops.can_mix_to_planes(batch, rows // batch, rank))
@@ -409,13 +414,20 @@ def _mx_linear_fwd(x_row, gq, lead_shape, W_mx, bias, w1, w2_a, w2_b, mask, alph
     aq, aq_col = _factor_forms(w2_a, quantise=True)      # A [vp, r]: row form for out, column form for dgrad
     bq, bq_col = _factor_forms(w2_b, quantise=True)      # B [r, vq]
     y = torch.empty(*lead_shape, n_out, dtype=BF16, device=x_row.codes.device)
-    hidden = ops.mx_gemm(gq, bq).view(lead_shape[0], -1, uq, rank)
-    if _can_fold(x_row.rows, n_out, c.shape[0], lead_shape[0], rank) and n_out == c.shape[0] * vp:
-        # one GEMM: the mixed hidden tensor (eight planes) times alpha * A enters as extra K-blocks
-        planes, _ = ops.tlokr_rank_mix_quant_planes(hidden, c, None if mask is None else mask.contiguous().to(BF16), False)
+    if _can_fold(x_row.rows, n_out, c.shape[0], lead_shape[0], rank) and n_out == c.shape[0] * vp and uq == 8:
+        # Two kernels for the whole linear: (1) hidden = grouped . B^T, the 8x8 mix, the mask and the quantisation
+        # of the mixed tensor, which leaves as eight e4m3 planes (hidden itself stays on the SM); (2) ONE GEMM in
+        # which those planes times alpha * A enter as extra K-blocks of the base projection.
+        m = None if mask is None else mask.contiguous().to(BF16)
+        if FUSE_HIDDEN_MIX:
+            planes, _ = ops.tlokr_hidden_mix_planes(gq, bq, c, m, lead_shape[0], False)
+        else:
+            hidden = ops.mx_gemm(gq, bq).view(lead_shape[0], -1, uq, rank)
+            planes, _ = ops.tlokr_rank_mix_quant_planes(hidden, c, m, False)
         ops.mx_gemm_delta(x_row, W_mx.row, planes, _scaled_row_form(w2_a, alpha), bias=_bias_bf16(bias),
                           out=y.view(-1, n_out))
         return y, (aq_col, bq, bq_col)
+    hidden = ops.mx_gemm(gq, bq).view(lead_shape[0], -1, uq, rank)
     ops.mx_gemm(x_row, W_mx.row, bias=_bias_bf16(bias), out=y.view(-1, n_out))
     mq, _ = _mix_operands(hidden, c, mask, False, row=True, col=False)
     res = y.view(-1, vp)

@@ -339,6 +339,21 @@ int anima_tlokr_rank_mix_quant_planes(const void* hidden, const void* c, const v
                                       uint8_t* codes_planes, uint8_t* scales_planes,
                                       uint8_t* codes_colT, uint8_t* scales_col, void* stream);
 
+/* First half of the T-LoKr delta in one kernel: hidden = g . f^T (block-scaled GEMM over k), then the 8x8 mix,
+ * the mask and the MXFP8 quantisation of the mixed tensor, written as eight planes. The hidden tensor stays in
+ * tensor memory and registers; it is written (bf16 [batch * n * 8, 128]) only if hidden_out is given.
+ * ref: tlokr.py:476-483 (hidden = grouped @ B.T; mixed = rank_mix(hidden, C, mask)) followed by the
+ * quantisation of `mixed` in _FP8StructuredLoKr (:589-590).
+ * g: e4m3 [batch * n * 8, k] + TILED scales (the grouped view of the layer input, row = token * 8 + j);
+ * f: e4m3 [128, k] + TILED scales (B, rank 128). c bf16 [8, 8], mask bf16 [batch, 128] or NULL.
+ * planes_codes / planes_scales as anima_tlokr_rank_mix_quant_planes writes them; values are bit-identical to
+ * anima_mx_gemm (bf16 output) followed by that call. batch * n % 128 == 0, k % 32 == 0. */
+int anima_tlokr_hidden_mix_planes(const uint8_t* g_codes, const uint8_t* g_scales,
+                                  const uint8_t* f_codes, const uint8_t* f_scales,
+                                  const void* c, const void* mask, int64_t batch, int64_t n_per_batch, int64_t k,
+                                  int transpose, void* hidden_out, uint8_t* planes_codes, uint8_t* planes_scales,
+                                  int32_t* status, void* stream);
+
 /* ref: tlokr_kernels.py:85-122, :168-204 (rank_mix_wgrad).
  *   dc[i,j] = sum_{b,n,r} grad_mixed[b,n,i,r] * hidden[b,n,j,r] * mask[b,r]   (fp32 [8,8])
  * Reads both tensors once (the reference reads them once per (i,j) pair). */

@@ -174,3 +174,36 @@ def test_kron_backward_vs_oracle(N, K, dw_dtype):
     (0.5 * torch.kron(w1a, w2a) * dw.float()).sum().backward()
     torch.testing.assert_close(dw1.cpu(), w1a.grad, rtol=1e-3, atol=1e-4 * float(w1a.grad.abs().max()))
     torch.testing.assert_close(dw2.cpu(), w2a.grad, rtol=1e-3, atol=1e-4 * float(w2a.grad.abs().max()))
+
+
+@pytest.mark.parametrize("batch,n,k", [(1, 128, 128), (2, 192, 256), (8, 512, 1024), (3, 128, 96)])
+@pytest.mark.parametrize("transpose", [False, True])
+@pytest.mark.parametrize("masked", [True, False])
+def test_hidden_gemm_mix_and_quantisation_in_one_kernel(batch, n, k, transpose, masked):
+    """anima_tlokr_hidden_mix_planes == the factor GEMM (bf16 output) followed by the quantising mix, bit for bit:
+    plane codes, tiled scales and the optional bf16 hidden tensor; and the hidden GEMM against the oracle."""
+    ops = _ops()
+    from anima_trainer_sm120_b200 import _lib
+    g = torch.Generator().manual_seed(batch * 1000 + n + k)
+    rows8 = batch * n * 8
+    x = (torch.randn(rows8, k, generator=g)).to(BF16).cuda()
+    x[5] = 0                                                   # an all-zero row: amax floor in hidden's consumers
+    f = (torch.randn(128, k, generator=g) * 0.2).to(BF16).cuda()
+    cmat = (torch.randn(8, 8, generator=g) * 0.4).to(BF16).cuda()
+    mask = OT.rank_mask(torch.rand(batch, generator=g), max_rank=128, min_rank=64, dtype=BF16).cuda() if masked else None
+    xq, _ = ops.mx_quantize(x, rowwise=True)
+    fq, _ = ops.mx_quantize(f, rowwise=True)
+    hidden = ops.mx_gemm(xq, fq).view(batch, n, 8, 128)
+    want_planes, _ = ops.tlokr_rank_mix_quant_planes(hidden, cmat, mask, transpose)
+    planes, hid = ops.tlokr_hidden_mix_planes(xq, fq, cmat, mask, batch, transpose, want_hidden=True)
+    planes2, none = ops.tlokr_hidden_mix_planes(xq, fq, cmat, mask, batch, transpose)
+    torch.cuda.synchronize()
+    _lib.check_status_word(x.device)
+    assert none is None
+    assert torch.equal(hid, hidden)
+    assert torch.equal(planes.codes, want_planes.codes) and torch.equal(planes.scales, want_planes.scales)
+    assert torch.equal(planes2.codes, planes.codes) and torch.equal(planes2.scales, planes.scales)
+    xp, _ = ops.mx_quantize(x, rowwise=True, layout=0)
+    fp, _ = ops.mx_quantize(f, rowwise=True, layout=0)
+    want_h = OQ.matmul(xp.codes.cpu().numpy(), xp.scales.cpu().numpy(), fp.codes.cpu().numpy(), fp.scales.cpu().numpy())
+    np.testing.assert_allclose(hid.float().cpu().numpy().reshape(rows8, 128), want_h, rtol=1e-2, atol=2e-2)
