@@ -331,8 +331,11 @@ __device__ __forceinline__ void mix_chunk(const uint32_t (&v)[32], const float (
   scale_byte = static_cast<uint32_t>(ex + 127);
 }
 
-template <int BN>
-__global__ void __launch_bounds__(kThreads, 1)
+// EPI = number of epilogue warps: 4 (one per tensor-memory lane quadrant) for the ordinary epilogue; 8 for the mix
+// epilogue, whose shuffles and conversions are bound by instruction latency with a single warp per scheduler
+// (two warps per quadrant then take two of the four 32-column chunks each).
+template <int BN, int EPI = 4>
+__global__ void __launch_bounds__(64 + 32 * EPI, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const GemmParams p) {
   using C = Cfg<BN>;
@@ -364,7 +367,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     mbar_init(acc_full_bar(0), 1);
     mbar_init(acc_full_bar(1), 1);
-    mbar_init(acc_free_bar, 4);
+    mbar_init(acc_free_bar, EPI);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
@@ -471,13 +474,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int64_t prow = static_cast<int64_t>(lane & 7) * p.mix_items + token;   // plane row this thread writes
         const __nv_bfloat16* mask_row = p.mix_mask ? p.mix_mask + (token / p.mix_n_per_batch) * 128 : nullptr;
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + (as ? C::kAcc1Col : 0);
+        constexpr int kChunks = 16 / EPI;                 // chunks per warp: 4, or 2 with two warps per quadrant
+        const int c0 = ((warp - 2) >> 2) * kChunks;
         uint32_t scale_word = 0;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = c0; c < c0 + kChunks; ++c) {
           uint32_t v[32];
           tc_ld32(t_row + c * 32, v);
           tc_wait_ld();
-          if (c == 0) {
+          if (c == c0) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_free_bar);
@@ -489,11 +494,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           uint8_t* dst = p.mix_codes + prow * 128 + c * 32;
           stg_stream16(dst, codes[0]);
           stg_stream16(dst + 16, codes[1]);
-          scale_word |= sb << (8 * c);
+          scale_word |= sb << (8 * (c - c0));
         }
-        // the row's four scale bytes are adjacent in the tiled layout (one 128-column chunk per row tile)
-        *reinterpret_cast<uint32_t*>(p.mix_scales + (prow >> 7) * 512 + mxq::tiled_offset(static_cast<int>(prow & 127), 0)) =
-            scale_word;
+        // the row's scale bytes are adjacent in the tiled layout (one 128-column chunk per row tile)
+        uint8_t* sdst = p.mix_scales + (prow >> 7) * 512 + mxq::tiled_offset(static_cast<int>(prow & 127), c0);
+        if (kChunks == 4) *reinterpret_cast<uint32_t*>(sdst) = scale_word;
+        else *reinterpret_cast<uint16_t*>(sdst) = static_cast<uint16_t>(scale_word);
       }
     } else {
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++it) {
@@ -554,7 +560,18 @@ __global__ void __launch_bounds__(256) splitk_finalize_kernel(const GemmParams p
     const int64_t row = i / n4, col = (i - row * n4) * 4;
     const float* src = p.partial + row * p.N + col;
     float4 acc = *reinterpret_cast<const float4*>(src);
-    for (int s = 1; s < p.splits; ++s) {
+    // The loads of eight splits are issued together and then added in index order: the sum keeps its fixed
+    // association, and a thread no longer waits one memory latency per split (a [256, 128] factor gradient is
+    // summed over up to 74 splits by 8192 threads).
+    int s = 1;
+    for (; s + 8 <= p.splits; s += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const float4*>(src + (s + u) * plane);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
+    }
+    for (; s < p.splits; ++s) {
       const float4 v = *reinterpret_cast<const float4*>(src + s * plane);
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
@@ -1332,11 +1349,11 @@ int forced_variant() {
   return v ? atoi(v) : 0;
 }
 
-template <int BN>
+template <int BN, int EPI = 4>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, cudaStream_t s) {
   static PerDeviceOnce once;
   const cudaError_t attr_rc = per_device_once(once, [] {
-    return cudaFuncSetAttribute(mx_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    return cudaFuncSetAttribute(mx_gemm_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 Cfg<BN>::kSmemBytes);
   });
   ANIMA_REQUIRE(attr_rc == cudaSuccess, ANIMA_E_CUDA, "mx_gemm: cannot reserve %d bytes of shared memory: %s",
@@ -1344,7 +1361,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams p, cudaStrea
   p.n_tiles = static_cast<int>(ceil_div(p.N, BN));
   const int items = p.m_tiles * p.n_tiles * p.splits;
   const int grid = std::min(items, sm_count());
-  mx_gemm_kernel<BN><<<grid, kThreads, Cfg<BN>::kSmemBytes, s>>>(ma, mb, p);
+  mx_gemm_kernel<BN, EPI><<<grid, 64 + 32 * EPI, Cfg<BN>::kSmemBytes, s>>>(ma, mb, p);
   ANIMA_CHECK_LAUNCH("mx_gemm");
   if (p.splits > 1) {
     const int64_t groups = static_cast<int64_t>(p.M) * (p.N / 4);
@@ -1556,5 +1573,5 @@ extern "C" int anima_tlokr_hidden_mix_planes(const uint8_t* g_codes, const uint8
   CUtensorMap ma, mb;
   ANIMA_REQUIRE(make_map(&ma, g_codes, M, k, BM) && make_map(&mb, f_codes, 128, k, 128), ANIMA_E_CUDA,
                 "tlokr_hidden_mix_planes: cuTensorMapEncodeTiled failed (driver entry point missing or bad operand)");
-  return launch<128>(ma, mb, p, static_cast<cudaStream_t>(stream));
+  return launch<128, 8>(ma, mb, p, static_cast<cudaStream_t>(stream));
 }

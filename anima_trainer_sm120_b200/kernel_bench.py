@@ -230,31 +230,53 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
         hbm("rmsnorm_rope_bwd", [BT, L, 16, 128], M * D * 6 + M * 16 * 4, lambda: ops.rmsnorm_rope_bwd(dq, q, wn, cos, sin, rs))
 
     if only in (None, "tlokr"):
-        # The T-LoKr delta of one module, x -> x @ kron(W1, (A * mask) @ B)^T, forward and backward (recomputation,
-        # the four factor-gradient GEMMs, dC and the input gradient). Algorithmic bytes: forward reads x and
-        # writes the delta, 2 B * rows * (in + out); backward reads x and the incoming gradient and writes the
-        # input gradient, 2 B * rows * (2 * in + out). Factors, mask and W1 are KB-scale.
+        # The T-LoKr delta of one module, x -> x @ kron(W1, (A * mask) @ B)^T, as the training step runs it: inside
+        # the one-node quantised linear, where the mixed hidden tensor is made by one kernel and enters the base
+        # GEMM as extra K-blocks. Its cost is what the linear takes beyond the base projection on the same
+        # operands: forward = linear - base GEMM; backward = (input gradient + factor gradients) - base dgrad.
+        # Algorithmic bytes of the delta alone: forward reads x and writes the delta, 2 B * rows * (in + out);
+        # backward reads x and the incoming gradient and writes the input gradient, 2 B * rows * (2 * in + out).
         from . import tlokr
+        from .fp8_quant import quantize_weight
         rank, batch = 128, 8
         for name, d_in, d_out, rows in TLOKR_MODULES:
             rows = rows // 8 if small else rows
-            if not (wanted(f"tlokr_delta fwd {name}", [rows, d_in, d_out]) or wanted(f"tlokr_delta bwd {name}", [rows, d_in, d_out])):
+            shape = [rows, d_in, d_out]
+            if not any(wanted(f"tlokr_delta {d} {name}", shape) for d in ("fwd", "bwd")):
                 continue
-            x = _acts(rows, d_in).view(batch, rows // batch, d_in)
-            g = _acts(rows, d_out, 0.01).view(batch, rows // batch, d_out)
-            w1 = (torch.randn(8, 8, device="cuda") * 0.3)
-            a = torch.randn(d_out // 8, rank, device="cuda") * 0.05
-            b = torch.randn(rank, d_in // 8, device="cuda") * 0.05
-            t_s = torch.rand(batch, device="cuda")
-            mask = tlokr._TimestepState(timesteps=t_s).mask(max_rank=rank, min_rank=rank // 2, dtype=BF16,
-                                                            device=x.device)
-            ctx = _Ctx()
-            tlokr._MXStructuredLoKr.forward(ctx, x, w1, a, b, mask)
-            hbm(f"tlokr_delta fwd {name}", [rows, d_in, d_out], 2 * rows * (d_in + d_out),
-                lambda: tlokr._MXStructuredLoKr.forward(_Ctx(), x, w1, a, b, mask))
-            hbm(f"tlokr_delta bwd {name}", [rows, d_in, d_out], 2 * rows * (2 * d_in + d_out),
-                lambda: tlokr._MXStructuredLoKr.backward(ctx, g))
-            del x, g, ctx
+            x = _acts(rows, d_in)
+            g = _acts(rows, d_out, 0.01)
+            W_mx = quantize_weight(_acts(d_out, d_in, 0.02))
+            w1 = torch.nn.Parameter(torch.randn(8, 8, device="cuda") * 0.3)
+            a = torch.nn.Parameter(torch.randn(d_out // 8, rank, device="cuda") * 0.05)
+            b = torch.nn.Parameter(torch.randn(rank, d_in // 8, device="cuda") * 0.05)
+            mask = tlokr._TimestepState(timesteps=torch.rand(batch, device="cuda")).mask(
+                max_rank=rank, min_rank=rank // 2, dtype=BF16, device=x.device)
+            lead = (batch, rows // batch)
+            gq, gq_col = ops.mx_quantize(x.view(rows * 8, d_in // 8), rowwise=True, colwise=True)
+            x_row = ops.mx_regroup(gq, rows, d_in)
+            gbq, gbq_col = ops.mx_quantize(g.view(rows * 8, d_out // 8), rowwise=True, colwise=True)
+            g_row = ops.mx_regroup(gbq, rows, d_out)
+            y = torch.empty(rows, d_out, dtype=BF16, device="cuda")
+            gx = torch.empty(rows, d_in, dtype=BF16, device="cuda")
+            _, fops = tlokr._mx_linear_fwd(x_row, gq, lead, W_mx, None, w1, a, b, mask, 0.5)
+            t_lin = t(lambda: tlokr._mx_linear_fwd(x_row, gq, lead, W_mx, None, w1, a, b, mask, 0.5))
+            t_base = t(lambda: ops.mx_gemm(x_row, W_mx.row, out=y))
+            t_bwd = t(lambda: tlokr._mx_linear_bwd(lambda r, k: (gbq, gbq_col), lambda r, k: (gq, gq_col), lead, d_in, W_mx,
+                                                   w1, a, b, mask, 0.5, fops))
+            t_dgrad = t(lambda: ops.mx_gemm(g_row, W_mx.col, out=gx))
+            for direction, ms, ms_base, nbytes in (("fwd", t_lin, t_base, 2 * rows * (d_in + d_out)),
+                                                   ("bwd", t_bwd, t_dgrad, 2 * rows * (2 * d_in + d_out))):
+                d_ms = max(ms - ms_base, 1e-6)
+                gbs = nbytes / d_ms / 1e6
+                out.append({"kernel": f"tlokr_delta {direction} {name}", "shape": shape, "ms": round(d_ms, 4),
+                            "bound": "hbm", "achieved": round(gbs, 1), "unit": "GB/s", "algorithmic_bytes": nbytes,
+                            "peak": hbm_peak, "frac_of_measured": round(gbs / hbm_peak, 3) if hbm_peak else None,
+                            "frac_of_nominal_8000": round(gbs / 8000.0, 3),
+                            "how": f"one-node T-LoKr linear {ms:.4f} ms - base GEMM alone {ms_base:.4f} ms, same operands"})
+                if not quiet:
+                    print(json.dumps(out[-1]), flush=True)
+            del x, g, W_mx, gq, gq_col, gbq, gbq_col, x_row, g_row, y, gx
 
     if only in (None, "gemm"):
         for (N, K) in [(2048, 2048), (6144, 2048), (8192, 2048), (2048, 8192)]:
