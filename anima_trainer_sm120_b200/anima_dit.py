@@ -146,7 +146,7 @@ class Block(nn.Module):
         if self.training and self.gradient_checkpointing:
             from .fp8_quant import first_pass      # this pass's saved tensors are dropped and recomputed
             with first_pass():
-                return torch_checkpoint(self._forward, *args, use_reentrant=False, **kwargs)
+                return torch_checkpoint(self._forward, *args, use_reentrant=False, preserve_rng_state=False, **kwargs)
         return self._forward(*args, **kwargs)
 
     def _mod(self, seq, emb, adaln_lora):

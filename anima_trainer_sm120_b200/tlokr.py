@@ -225,6 +225,13 @@ class _StructuredLoKr(torch.autograd.Function):
         return g_x.to(x.dtype), g_c.to(w1.dtype), g_a.to(w2_a.dtype), g_b.to(w2_b.dtype), None
 
 
+def _capturing(p: torch.Tensor) -> bool:
+    """Inside a CUDA-graph capture the factor conversions must be recorded with the rest of the step: a form kept
+    from an earlier call would be baked into the graph and every replay would multiply by the factors of the step
+    that was captured."""
+    return p.is_cuda and torch.cuda.is_current_stream_capturing()
+
+
 def _factor_forms(p: torch.Tensor, *, quantise: bool):
     """bf16 copy (``quantise=False``) or both MXFP8 operands (``quantise=True``) of a small adapter factor.
 
@@ -232,7 +239,7 @@ def _factor_forms(p: torch.Tensor, *, quantise: bool):
     backward); for a leaf parameter the result is kept on the parameter object, keyed on its in-place version
     counter and storage address (an optimizer step or a reassigned ``.data`` invalidates it), which removes two
     thirds of these tiny launches. Sliced or computed factors are converted on every call."""
-    cacheable = p.is_leaf and isinstance(p, nn.Parameter)
+    cacheable = p.is_leaf and isinstance(p, nn.Parameter) and not _capturing(p)
     slot = "_anima_mx_forms" if quantise else "_anima_bf16_form"
     key = (p._version, p.data_ptr())
     if cacheable:
@@ -249,7 +256,7 @@ def _factor_forms(p: torch.Tensor, *, quantise: bool):
 def _scaled_row_form(p: torch.Tensor, alpha: float) -> ops.MXOperand:
     """Row-wise MXFP8 operand of ``alpha * p`` rounded to bf16 (the factor a folded delta multiplies by), kept on
     a leaf parameter like :func:`_factor_forms`."""
-    cacheable = p.is_leaf and isinstance(p, nn.Parameter)
+    cacheable = p.is_leaf and isinstance(p, nn.Parameter) and not _capturing(p)
     key = (p._version, p.data_ptr(), float(alpha))
     if cacheable:
         hit = getattr(p, "_anima_mx_scaled_row", None)

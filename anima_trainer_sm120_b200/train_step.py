@@ -54,6 +54,8 @@ class StepConfig:
     seed: int = 42
     grad_bucket_blocks: int = 4       # DP: adapter gradients of this many DiT blocks travel in one all-reduce
     status_check_every: int = 1       # steps between reads of the kernels' bounded-wait status words (0 = never)
+    cuda_graph: bool = False          # capture forward + backward per input shape and replay it (cuda_graphs.py)
+    cuda_graph_warmup: int = 3
 
 
 class Trainer:
@@ -123,6 +125,12 @@ class Trainer:
         self.opt = torch.optim.AdamW(self.params, lr=cfg.lr, betas=(0.9, 0.99), weight_decay=0.0)
         self.step_idx = 0
         self.autocast_mode = "bf16" if cfg.precision.startswith("bf16") else "mxfp8"
+        self.runner = None
+        if cfg.cuda_graph:
+            if device.type != "cuda":
+                raise RuntimeError("cuda_graph=True needs a CUDA device")
+            from .cuda_graphs import CUDAGraphRunner
+            self.runner = CUDAGraphRunner(self._loss_of_batch, warmup_steps=cfg.cuda_graph_warmup)
         self.last_allreduce_exposed_ms: float | None = None
         self._build_buckets()
 
@@ -196,29 +204,50 @@ class Trainer:
         return lat.to(self.device, torch.bfloat16), ctx.to(self.device, torch.bfloat16), noise_seed
 
     # ---------------------------------------------------------------- one step
-    def forward_and_loss(self, latents, ctx, noise_seed: int):
+    def make_batch(self, latents, ctx, noise_seed: int) -> dict:
+        """Noise, timesteps and targets of one step (drawn outside any captured region)."""
         g = torch.Generator(device=self.device).manual_seed(noise_seed)
         noisy, target, t = noisy_input_and_target(latents, g)
+        return {"noisy": noisy, "target": target, "timesteps": t, "context": ctx}
+
+    def _loss_of_batch(self, batch: dict) -> torch.Tensor:
         if self.tlokr:
-            self._tlokr.set_timestep(t)
+            self._tlokr.set_timestep(batch["timesteps"])
         with precision.autocast_for(self.autocast_mode, self.device.type), precision.fp8_autocast_for(self.autocast_mode):
-            pred = self.dit(noisy, t, ctx)
-        return F.mse_loss(pred.float(), target.float())
+            pred = self.dit(batch["noisy"], batch["timesteps"], batch["context"])
+        return F.mse_loss(pred.float(), batch["target"].float())
+
+    def forward_and_loss(self, latents, ctx, noise_seed: int):
+        return self._loss_of_batch(self.make_batch(latents, ctx, noise_seed))
 
     def step(self, latents, ctx, noise_seed: int) -> float:
         self.flat_grad.zero_()
-        if self.world > 1:
-            self._pending = list(self._bucket_size)
-        try:
-            loss = self.forward_and_loss(latents, ctx, noise_seed)
-            loss.backward()
-        finally:
-            if self.tlokr:
-                self._tlokr.clear_timestep()
-            if self.world > 1 and not self._works and self._pending == self._bucket_size:
-                self._pending = []              # forward or backward raised before any bucket left
-        if self.world > 1:                      # the only exchange of the data-parallel step
-            self._finish_exchange()
+        if self.runner is not None:
+            # forward + backward as a replayed CUDA graph; no Python runs inside it, so the gradient buckets cannot be
+            # launched as backward retires them: the whole buffer is exchanged after the replay
+            from .cuda_graphs import make_bucket_key
+            batch = self.make_batch(latents, ctx, noise_seed)
+            try:
+                loss = self.runner.step(make_bucket_key(batch["noisy"], batch["context"]), batch, self.params)
+            finally:
+                if self.tlokr:
+                    self._tlokr.clear_timestep()
+            if self.world > 1:
+                dist.all_reduce(self.flat_grad)
+                self.flat_grad.mul_(1.0 / self.world)
+        else:
+            if self.world > 1:
+                self._pending = list(self._bucket_size)
+            try:
+                loss = self.forward_and_loss(latents, ctx, noise_seed)
+                loss.backward()
+            finally:
+                if self.tlokr:
+                    self._tlokr.clear_timestep()
+                if self.world > 1 and not self._works and self._pending == self._bucket_size:
+                    self._pending = []              # forward or backward raised before any bucket left
+            if self.world > 1:                      # the only exchange of the data-parallel step
+                self._finish_exchange()
         torch.nn.utils.clip_grad_norm_(self.params, self.cfg.max_grad_norm)
         self.opt.step()
         self.step_idx += 1

@@ -202,7 +202,8 @@ class Shape:
         self.w2 = (torch.randn(n // FACTOR, k // FACTOR, generator=g) * 0.02).to(dev).requires_grad_(True)
 
 
-def train_steps_per_s(dev, world: int, steps: int = 6, warmup: int = 2, checkpointing: bool = True) -> dict:
+def train_steps_per_s(dev, world: int, steps: int = 6, warmup: int = 2, checkpointing: bool = True,
+                      cuda_graph: bool = False) -> dict:
     """Optimizer steps per second of the config-5 training step (CUDA events, max over ranks)."""
     import torch.distributed as dist
 
@@ -210,7 +211,8 @@ def train_steps_per_s(dev, world: int, steps: int = 6, warmup: int = 2, checkpoi
     from anima_trainer_sm120_b200.train_step import StepConfig, Trainer
 
     torch.cuda.reset_peak_memory_stats(dev)
-    tr = Trainer(AnimaConfig(), StepConfig(precision="mxfp8", variant="lokr", gradient_checkpointing=checkpointing), dev)
+    tr = Trainer(AnimaConfig(), StepConfig(precision="mxfp8", variant="lokr", gradient_checkpointing=checkpointing,
+                                           cuda_graph=cuda_graph), dev)
     times, exposed = [], []
     for i in range(warmup + steps):
         lat, ctx, seed = tr.synthetic_batch(8, 128, 512, i)
@@ -405,6 +407,11 @@ def run_gpu_arm(args) -> None:
             # configuration, which checkpoints every block; reported beside it, never instead of it)
             train["without_checkpointing"] = {k: v for k, v in train_steps_per_s(dev, world, steps=4, checkpointing=False).items()
                                               if k in ("value", "unit", "samples_per_s", "peak_mem_gb", "steps", "warmup")}
+            torch.cuda.empty_cache()
+            # the reference's configuration again, forward + backward replayed as one CUDA graph per rank
+            # (3 eager warm-up steps, the capture, then replays are timed)
+            train["with_cuda_graph"] = {k: v for k, v in train_steps_per_s(dev, world, steps=6, warmup=4, cuda_graph=True).items()
+                                        if k in ("value", "unit", "samples_per_s", "peak_mem_gb", "steps", "warmup")}
         except Exception as e:  # noqa: BLE001 - the extra object must never cost the contract line
             train = {**(train or {}), "metric": "anima_lokr_train_steps_per_s",
                      "error": f"{type(e).__name__}: {str(e)[:300]}"}

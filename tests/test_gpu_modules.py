@@ -279,3 +279,27 @@ def test_tlokr_mlp_node_matches_two_linears_with_eager_gelu():
         res.append([y.detach(), xi.grad] + [p.grad.clone() for p in params])
     rels = [_rel(ref, got) for ref, got in zip(*res)]
     assert all(v < (2e-2 if i < 2 else 0.10) for i, v in enumerate(rels)), rels
+
+
+@pytest.mark.parametrize("variant", ["lokr", "tlokr"])
+def test_cuda_graph_replay_reproduces_the_eager_step(variant):
+    """Forward + backward captured per input shape and replayed (cuda_graphs.CUDAGraphRunner, the reference's
+    cuda_graphs.py:68-234): same seeded steps as the eager trainer, losses and adapters equal; the runner warms up
+    eagerly, captures once, then replays."""
+    from anima_trainer_sm120_b200.anima_dit import tiny_config
+    from anima_trainer_sm120_b200.train_step import StepConfig, Trainer
+    mcfg = tiny_config(depth=2, dim=512, heads=4, mlp_dim=1024, context_dim=256, adaln_lora_dim=64)
+    runs = {}
+    for graph in (False, True):
+        tr = Trainer(mcfg, StepConfig(precision="mxfp8", variant=variant, lokr_dim=32, lr=2e-3, cuda_graph=graph),
+                     torch.device(DEV))
+        losses = tr.run(steps=7, batch=4, latent_hw=32, text_tokens=32)
+        runs[graph] = (losses, [p.detach().clone() for p in tr.params])
+        if graph:
+            assert tr.runner is not None and len(tr.runner._state) == 1
+            assert all(tr.runner.captured(k) for k in tr.runner._state)       # steps 4..7 were replays
+    (l_e, p_e), (l_g, p_g) = runs[False], runs[True]
+    for a, b in zip(l_e, l_g):
+        assert abs(a - b) <= 1e-5 * abs(a), (l_e, l_g)
+    for a, b in zip(p_e, p_g):
+        torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-6)
