@@ -38,6 +38,7 @@ PROTOTYPES: dict[str, tuple[object, list[object]]] = {
     "anima_last_error": (c_char_p, []),
     "anima_mx_quantize": (c_int, [P, I64, I64, I64, P, P, P, P, c_int, P]),
     "anima_mx_quantize_status": (c_int, []),
+    "anima_mx_exponent_probe": (c_int, [P, I64, P, P, P]),
     "anima_mx_quantize_gelu": (c_int, [P, P, I64, I64, I64, P, P, P, P, P, c_int, P]),
     "anima_mx_scales_bytes": (I64, [I64, I64, c_int]),
     "anima_mx_dequantize": (c_int, [P, P, I64, I64, c_int, P, P]),

@@ -302,6 +302,22 @@ __global__ void mx_scales_regroup_words_kernel(const uint32_t* __restrict__ in, 
   }
 }
 
+// Test aid: the block exponent of `amax` by the integer rule the quantiser uses and by the reference's literal
+// fp32 expression ceil(log2(amax) - log2(448)) (mxfp8_gemm.py:118-120) evaluated with the instruction its Triton
+// kernel compiles to on a GPU (lg2.approx.f32), both clamped to [-127, 127].
+__global__ void mx_exponent_probe_kernel(const float* __restrict__ amax, int64_t n, int32_t* __restrict__ by_rule,
+                                         int32_t* __restrict__ by_lg2_approx) {
+  const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (i >= n) return;
+  const float a = fmaxf(amax[i], mxq::kAmaxFloor);
+  by_rule[i] = mxq::mx_exponent(a);
+  float la, l448;
+  asm("lg2.approx.f32 %0, %1;" : "=f"(la) : "f"(a));
+  asm("lg2.approx.f32 %0, %1;" : "=f"(l448) : "f"(448.0f));
+  const float e = ceilf(la - l448);
+  by_lg2_approx[i] = static_cast<int32_t>(fminf(fmaxf(e, -127.f), 127.f));
+}
+
 }  // namespace
 }  // namespace anima
 
@@ -573,5 +589,15 @@ extern "C" int anima_mx_scales_regroup(const uint8_t* tiled_in, int64_t rows_in,
   else
     mx_scales_regroup_kernel<int64_t><<<blocks, 256, 0, s>>>(tiled_in, k_in / 32, rows_out, k_out / 32, total, tiled_out);
   ANIMA_CHECK_LAUNCH("mx_scales_regroup");
+  return ANIMA_OK;
+}
+
+extern "C" int anima_mx_exponent_probe(const float* amax, int64_t n, int32_t* by_rule, int32_t* by_lg2_approx,
+                                       void* stream) {
+  ANIMA_REQUIRE(amax && by_rule && by_lg2_approx && n >= 0, ANIMA_E_ARG, "mx_exponent_probe: bad argument");
+  if (n == 0) return ANIMA_OK;
+  mx_exponent_probe_kernel<<<static_cast<unsigned>(ceil_div(n, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      amax, n, by_rule, by_lg2_approx);
+  ANIMA_CHECK_LAUNCH("mx_exponent_probe");
   return ANIMA_OK;
 }

@@ -76,6 +76,13 @@ int anima_mx_quantize(const void* x_bf16, int64_t rows, int64_t cols, int64_t ld
  * negative on a CUDA error. Synchronises: call it where the host waits anyway (after a step's loss is read). */
 int anima_mx_quantize_status(void);
 
+/* Test aid (ref: mxfp8_gemm.py:118-120): for n fp32 block maxima, the scale exponent by the integer rule this
+ * library uses (E - 8 + (mantissa > 1.75) for amax = m * 2^E) and by the reference's literal expression
+ * ceil(log2(amax) - log2(448)) evaluated with lg2.approx.f32, the instruction its kernel runs on a GPU; both
+ * after the 1e-30 floor and the clamp to [-127, 127]. int32 outputs. Used to show on hardware where, if anywhere,
+ * the two differ (a block maximum with mantissa exactly 1.75 sits on the ceiling's edge). */
+int anima_mx_exponent_probe(const float* amax, int64_t n, int32_t* by_rule, int32_t* by_lg2_approx, void* stream);
+
 /* Quantise an MLP activation without materialising it (no reference counterpart: the reference
  * runs GELU as a separate eager kernel between mlp.layer1 and mlp.layer2 and quantises its output).
  * h bf16 [rows, cols] is the pre-activation.

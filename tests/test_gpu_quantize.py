@@ -147,3 +147,29 @@ def test_full_size_properties():
     step = torch.ldexp(torch.ones((), device="cuda"), row.scales.int() - 127 + 8 - 4)   # 2^(e+8) * 2^-4
     err = (deq.float() - x.float()).abs().view(32768, 64, 32).amax(dim=2)
     assert bool((err <= step).all())
+
+
+def test_exponent_rule_against_the_references_expression_on_this_gpu(capsys):
+    """The reference computes the block exponent as ceil(log2(amax) - log2(448)) in fp32 with the GPU's approximate
+    log2 (mxfp8_gemm.py:118-120); the library uses the exact integer rule. Evaluate both on the device for EVERY
+    positive finite bf16 value (a block maximum of bf16 data is one of them): any difference must be confined to
+    block maxima whose mantissa is exactly 1.75 (the ceiling's edge), and is reported."""
+    from anima_trainer_sm120_b200 import _lib
+    bits = torch.arange(1, 0x7F80, dtype=torch.int32)                       # positive, finite, non-zero bf16 patterns
+    amax = (bits << 16).view(torch.float32).cuda()
+    n = amax.numel()
+    by_rule = torch.empty(n, dtype=torch.int32, device="cuda")
+    by_lg2 = torch.empty(n, dtype=torch.int32, device="cuda")
+    _lib.check(_lib.load().anima_mx_exponent_probe(amax.data_ptr(), n, by_rule.data_ptr(), by_lg2.data_ptr(),
+                                                   _lib.stream_ptr(torch.device("cuda"))))
+    torch.cuda.synchronize()
+    want = torch.from_numpy(OQ.exponent_exact(np.maximum(amax.cpu().numpy(), OQ.AMAX_FLOOR)))
+    assert torch.equal(by_rule.cpu(), want)                                 # the kernel's rule is the oracle's
+    diff = (by_rule != by_lg2).cpu()
+    mant = bits & 0x7F
+    edge = mant == 0x60                                                     # mantissa 1.75 exactly
+    with capsys.disabled():
+        print(f"\nexponent by rule vs ceil(lg2.approx(amax) - lg2.approx(448)) on this GPU: {int(diff.sum())} of {n} "
+              f"bf16 block maxima differ; {int((diff & edge).sum())} of them have mantissa 1.75 "
+              f"({int(edge.sum())} such values exist)")
+    assert not bool((diff & ~edge).any()), bits[diff & ~edge][:10].tolist()
