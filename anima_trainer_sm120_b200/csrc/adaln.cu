@@ -214,7 +214,26 @@ RowSplit make_split(int64_t bt, int64_t hw) {
 // the same thread forms dout = d_res + bf16(dx_ln), writes it (it is also the gradient of x_prev), and
 // continues with dsub = gate * dout and the dgate partial sums. Every rounding point is that of the three
 // separate kernels, so all outputs are bit-identical to them.
-template <int NCH, bool GATED>
+// PF (NCH == 1 only): the next group of rows is copied global -> shared with cp.async while the current one is
+// worked on, each thread fetching exactly the 16-byte chunks it will read itself, so no barrier is involved
+// and no register is spent on the prefetch. Without it the kernel alternates between waiting for its loads and
+// computing at 16 resident warps: DRAM half busy, 2.6 long-scoreboard stalls per issue.
+// Shared layout: [stage 2][tensor (dy, x[, d_res])][row R][thread] x 16 bytes.
+__device__ __forceinline__ uint32_t smem_u32_of(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gptr) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(gptr) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint4 lds16(uint32_t smem_addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_addr));
+  return v;
+}
+constexpr int adaln_bwd_prefetch_bytes(bool gated) { return 2 * (gated ? 3 : 2) * kRowsPerIter * kThreads * 16; }
+
+template <int NCH, bool GATED, bool PF = false>
 __global__ void __launch_bounds__(kThreads, NCH == 1 ? 2 : 1)
 adaln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                  const __nv_bfloat16* __restrict__ scale, const float* __restrict__ mean,
@@ -260,11 +279,42 @@ adaln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __re
     }
   }
 
+  static_assert(!PF || NCH == 1, "the prefetch form covers one 16-byte chunk per thread and row");
+  extern __shared__ uint4 pf_smem[];
+  constexpr int kPfTensors = GATED ? 3 : 2;
+  const uint32_t pf_base = PF ? smem_u32_of(pf_smem) + t * 16 : 0;
+  auto pf_addr = [&](int stage, int tensor, int k) {
+    return pf_base + static_cast<uint32_t>(((stage * kPfTensors + tensor) * R + k) * kThreads * 16);
+  };
+  auto prefetch = [&](int64_t r0n, int stage) {   // this thread's chunks of rows r0n .. r0n + R - 1
+    const int col = t * 8;
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      const int64_t row = r0n + k;
+      if (row < row_end && col < d) {
+        cp_async16(pf_addr(stage, 0, k), dy + row * d + col);
+        cp_async16(pf_addr(stage, 1, k), x + row * d + col);
+        if (GATED) cp_async16(pf_addr(stage, 2, k), d_res + row * d + col);
+      }
+    }
+    cp_async_commit();
+  };
+  if (PF && row_begin < row_end) prefetch(row_begin, 0);
+
   int buf = 0;
   for (int64_t r0 = row_begin; r0 < row_end; r0 += R) {
     float g[R][NCH][8], xh[R][NCH][8];  // dy then dxhat; x then xhat
     uint4 res_raw[GATED ? R : 1][NCH];
     float mu[R], rs[R];
+    if (PF) {
+      // start the next group, then wait for this one (a stage is rewritten only after its values were used)
+      if (r0 + R < row_end) {
+        prefetch(r0 + R, buf ^ 1);
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+    }
 #pragma unroll
     for (int k = 0; k < R; ++k) {
       const int64_t row = r0 + k;
@@ -276,12 +326,12 @@ adaln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __re
         const int col = (j * kThreads + t) * 8;
         uint4 a = make_uint4(0u, 0u, 0u, 0u), b = a;
         if (row_ok && col < d) {
-          a = ldg_stream16(dy + row * d + col);
-          b = ldg_stream16(x + row * d + col);
+          a = PF ? lds16(pf_addr(buf, 0, k)) : ldg_stream16(dy + row * d + col);
+          b = PF ? lds16(pf_addr(buf, 1, k)) : ldg_stream16(x + row * d + col);
         }
         if (GATED) {
           res_raw[k][j] = make_uint4(0u, 0u, 0u, 0u);
-          if (row_ok && col < d) res_raw[k][j] = ldg_stream16(d_res + row * d + col);
+          if (row_ok && col < d) res_raw[k][j] = PF ? lds16(pf_addr(buf, 2, k)) : ldg_stream16(d_res + row * d + col);
         }
         unpack8(a, g[k][j]);
         unpack8(b, xh[k][j]);
@@ -643,6 +693,40 @@ extern "C" int anima_gated_add_adaln_fwd_quant(const void* x, const void* gate, 
   return ANIMA_OK;
 }
 
+namespace anima {
+namespace {
+// Launch of the AdaLN backward main kernel: the prefetching form for d <= 2048 (ANIMA_ADALN_BWD_PREFETCH=0 keeps
+// the plain loads, for comparison; same bits), the two-chunk form above that.
+template <bool GATED>
+int launch_adaln_bwd_main(dim3 grid, cudaStream_t s, const __nv_bfloat16* dy, const __nv_bfloat16* x,
+                          const __nv_bfloat16* scale, const float* mean, const float* rstd, const __nv_bfloat16* d_res,
+                          const __nv_bfloat16* sub, const __nv_bfloat16* gate, int64_t hw, int64_t d, int rows_per_chunk,
+                          __nv_bfloat16* dx, __nv_bfloat16* dsub, float* ws) {
+  if (d > 2048) {
+    adaln_bwd_kernel<2, GATED><<<grid, kThreads, 0, s>>>(dy, x, scale, mean, rstd, d_res, sub, gate, hw, (int)d,
+                                                         rows_per_chunk, dx, dsub, ws);
+    return ANIMA_OK;
+  }
+  const char* env = getenv("ANIMA_ADALN_BWD_PREFETCH");
+  if (env && env[0] == '0') {
+    adaln_bwd_kernel<1, GATED><<<grid, kThreads, 0, s>>>(dy, x, scale, mean, rstd, d_res, sub, gate, hw, (int)d,
+                                                         rows_per_chunk, dx, dsub, ws);
+    return ANIMA_OK;
+  }
+  constexpr int kBytes = adaln_bwd_prefetch_bytes(GATED);
+  static PerDeviceOnce once;
+  const cudaError_t rc = per_device_once(once, [] {
+    return cudaFuncSetAttribute(adaln_bwd_kernel<1, GATED, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
+  });
+  ANIMA_REQUIRE(rc == cudaSuccess, ANIMA_E_CUDA, "adaln_bwd: cannot reserve %d bytes of shared memory: %s", kBytes,
+                cudaGetErrorString(rc));
+  adaln_bwd_kernel<1, GATED, true><<<grid, kThreads, kBytes, s>>>(dy, x, scale, mean, rstd, d_res, sub, gate, hw, (int)d,
+                                                                  rows_per_chunk, dx, dsub, ws);
+  return ANIMA_OK;
+}
+}  // namespace
+}  // namespace anima
+
 extern "C" int64_t anima_adaln_bwd_workspace_bytes(int64_t rows, int64_t hw, int64_t d) {
   if (rows < 0 || hw <= 0 || d <= 0 || rows % hw) return ANIMA_E_SHAPE;
   const RowSplit sp = make_split(rows / hw, hw);
@@ -673,12 +757,9 @@ extern "C" int anima_adaln_bwd(const void* dy, const void* x, const void* scale,
   const auto* xp = static_cast<const __nv_bfloat16*>(x);
   const auto* scp = static_cast<const __nv_bfloat16*>(scale);
   auto* dxp = static_cast<__nv_bfloat16*>(dx);
-  if (d <= 2048)
-    adaln_bwd_kernel<1, false><<<grid, kThreads, 0, s>>>(dyp, xp, scp, mean, rstd, nullptr, nullptr, nullptr, hw,
-                                                         (int)d, sp.rows_per_chunk, dxp, nullptr, ws);
-  else
-    adaln_bwd_kernel<2, false><<<grid, kThreads, 0, s>>>(dyp, xp, scp, mean, rstd, nullptr, nullptr, nullptr, hw,
-                                                         (int)d, sp.rows_per_chunk, dxp, nullptr, ws);
+  if (int rc = launch_adaln_bwd_main<false>(grid, s, dyp, xp, scp, mean, rstd, nullptr, nullptr, nullptr, hw, d,
+                                            sp.rows_per_chunk, dxp, nullptr, ws))
+    return rc;
   ANIMA_CHECK_LAUNCH("adaln_bwd");
   const int64_t total = bt * 2 * d;
   finalize_partials_kernel<<<static_cast<unsigned>(std::min<int64_t>(ceil_div(total, 256), 1024)), 256, 0, s>>>(
@@ -725,12 +806,9 @@ extern "C" int anima_gated_add_adaln_bwd(const void* d_y, const void* d_xnew, co
   const auto* gp = static_cast<const __nv_bfloat16*>(gate);
   auto* dxp = static_cast<__nv_bfloat16*>(dx);
   auto* dsp = static_cast<__nv_bfloat16*>(dsub);
-  if (d <= 2048)
-    adaln_bwd_kernel<1, true><<<grid, kThreads, 0, s>>>(dyp, xp, scp, mean, rstd, drp, sbp, gp, hw, (int)d,
-                                                        sp.rows_per_chunk, dxp, dsp, ws);
-  else
-    adaln_bwd_kernel<2, true><<<grid, kThreads, 0, s>>>(dyp, xp, scp, mean, rstd, drp, sbp, gp, hw, (int)d,
-                                                        sp.rows_per_chunk, dxp, dsp, ws);
+  if (int rc = launch_adaln_bwd_main<true>(grid, s, dyp, xp, scp, mean, rstd, drp, sbp, gp, hw, d,
+                                           sp.rows_per_chunk, dxp, dsp, ws))
+    return rc;
   ANIMA_CHECK_LAUNCH("gated_add_adaln_bwd");
   const int64_t total = bt * 3 * d;
   finalize_partials_kernel<<<static_cast<unsigned>(std::min<int64_t>(ceil_div(total, 256), 1024)), 256, 0, s>>>(

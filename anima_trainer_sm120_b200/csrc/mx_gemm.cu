@@ -274,7 +274,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int co
 // produces output row (token, i = lane % 8). The arithmetic and its order are those of the GEMM's bf16 store
 // followed by rank_mix_quant_kernel (fp32 fma over j ascending from 0, mask, bf16 rounding, MX quantisation of
 // the rounded values), so codes and scale are bit-identical to running the two kernels.
-__device__ __forceinline__ void mix_chunk(const uint32_t (&v)[32], const float (&cw)[8], int lane,
+__device__ __forceinline__ void mix_chunk(const uint32_t (&v)[32], const uint32_t (&cw)[8], int lane,
                                           const __nv_bfloat16* mask_chunk, __nv_bfloat16* hidden_chunk,
                                           uint4 (&codes)[2], uint32_t& scale_byte) {
   uint32_t pk[16];  // the chunk rounded to bf16, two columns per word
@@ -294,12 +294,19 @@ __device__ __forceinline__ void mix_chunk(const uint32_t (&v)[32], const float (
   const int base = lane & 24;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const float w = cw[j];
+    // fma.rn.f32.bf16: bf16 x bf16 + fp32 with one rounding, i.e. fmaf(float(h), float(w), acc) without the two
+    // instructions that widen the halves of the shuffled word (a third of this loop's instruction count)
+    const uint32_t w = cw[j];
 #pragma unroll
     for (int k = 0; k < 16; ++k) {
       const uint32_t other = __shfl_sync(0xffffffffu, pk[k], base + j);
-      acc[2 * k] = fmaf(__uint_as_float(other << 16), w, acc[2 * k]);
-      acc[2 * k + 1] = fmaf(__uint_as_float(other & 0xffff0000u), w, acc[2 * k + 1]);
+      asm("{\n\t.reg .b16 lo, hi, wl, wh;\n\t"
+          "mov.b32 {lo, hi}, %2;\n\t"
+          "mov.b32 {wl, wh}, %3;\n\t"
+          "fma.rn.f32.bf16 %0, lo, wl, %0;\n\t"
+          "fma.rn.f32.bf16 %1, hi, wl, %1;\n\t}"
+          : "+f"(acc[2 * k]), "+f"(acc[2 * k + 1])
+          : "r"(other), "r"(w));
     }
   }
   if (mask_chunk != nullptr) {
@@ -458,11 +465,11 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int it = 0;
     if (BN == 128 && p.mix_codes != nullptr) {
       // mix epilogue: see GemmParams. splits == 1 here, so an item is a tile.
-      float cw[8];
+      uint32_t cw[8];   // this row's mix weights as raw bf16 bits (low half)
       {
         const int i = lane & 7;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) cw[j] = __bfloat162float(p.mix_transpose ? p.mix_c[j * 8 + i] : p.mix_c[i * 8 + j]);
+        for (int j = 0; j < 8; ++j) cw[j] = __bfloat16_as_ushort(p.mix_transpose ? p.mix_c[j * 8 + i] : p.mix_c[i * 8 + j]);
       }
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++it) {
         const int mt = item;  // n_tiles == 1
@@ -1197,7 +1204,7 @@ PairPlan plan_pair_uncached(int64_t M, int64_t N, int64_t K, bool allow_split, i
   const int n_tiles = pl.n_wide + pl.narrow, tiles = m_tiles * n_tiles;
   const int kb = static_cast<int>(ceil_div(K, BK));
   const int max_pairs = std::max(1, sms / 2);
-  const double kItem = 1.0, kSplitItem = 6.0, kFinalize = 16.0;
+  const double kItem = 1.0, kSplitItem = 8.0, kFinalize = 36.0;   // the finalize launch measures 5 - 10 us, a K-block 0.27 us
   auto tile_cost = [&](int tile, double frac) {
     int mt, nt;
     tile_coords_of(m_tiles, n_tiles, tile, mt, nt);

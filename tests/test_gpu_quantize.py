@@ -171,5 +171,6 @@ def test_exponent_rule_against_the_references_expression_on_this_gpu(capsys):
     with capsys.disabled():
         print(f"\nexponent by rule vs ceil(lg2.approx(amax) - lg2.approx(448)) on this GPU: {int(diff.sum())} of {n} "
               f"bf16 block maxima differ; {int((diff & edge).sum())} of them have mantissa 1.75 "
-              f"({int(edge.sum())} such values exist)")
+              f"({int(edge.sum())} such values exist); binary exponents of those that differ: "
+              f"{sorted(int(b >> 7) - 127 for b in bits[diff].tolist())}")
     assert not bool((diff & ~edge).any()), bits[diff & ~edge][:10].tolist()

@@ -272,11 +272,12 @@ def test_pair_kernel_splits_the_partial_round_of_long_contractions_only():
     assert _pair_plan(2048, 2048, 32768)[1]["splits"] > 1                  # 88 tiles on 74 pairs, 256 K-blocks each
     assert _pair_plan(2048, 2048, 32768, ws=0)[1]["splits"] == 1
     assert _pair_plan(32768, 2048, 2048)[1]["splits"] == 1                 # 16 K-blocks per tile: a split costs more
+    assert _pair_plan(32768, 2048, 8192)[1]["splits"] == 1                 # two tail tiles of 64 K-blocks: the finalize launch costs more
     assert _pair_plan(32768, 2048, 2048)[1]["narrow"] == 1                 # 2048 = 10 x 192 + 128
     assert _pair_plan(32768, 6144, 2048)[1]["narrow"] == 0                 # 6144 = 32 x 192
     assert _pair_plan(128, 2048, 2048)[0] == 1                             # one-CTA kernel's shape
     # the modelled finish time with the split must not exceed the unsplit one: the busiest pair's K-blocks
-    for shape, gain in [((2048, 2048, 32768), 0.65), ((8192, 2048, 32768), 0.99), ((2048, 8192, 32768), 0.99)]:
+    for shape, gain in [((2048, 2048, 32768), 0.65), ((6144, 2048, 32768), 0.99), ((2048, 8192, 32768), 0.99)]:
         loads = []
         for ws in (0, 1):
             pl = _pair_plan(*shape, ws)[1]
