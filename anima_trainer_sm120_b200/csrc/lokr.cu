@@ -27,6 +27,13 @@ __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
+static inline int log2_if_pow2(int64_t v) {
+  if (v <= 0 || (v & (v - 1)) != 0) return -1;
+  int s = 0;
+  while ((int64_t{1} << s) < v) ++s;
+  return s;
+}
+
 template <class F>
 struct MergeLoader {
   const __nv_bfloat16* w;
@@ -35,6 +42,7 @@ struct MergeLoader {
   __nv_bfloat16* merged;  // optional [N, K]
   float alpha;
   int64_t K, vp, vq, uq;
+  int vp_shift, vq_shift;   // log2 when the block size is a power of two (then the divisions are shifts), else -1
   using Raw = uint4;
   static constexpr bool kZeroSafe = false;   // finish reads the factors at (row, col)
   static constexpr int kSmemBytes = 0;
@@ -44,8 +52,9 @@ struct MergeLoader {
   // W comes from HBM (fetch); the factors are small and cache-resident and are read here.
   __device__ __forceinline__ uint4 finish(const Raw& raw, int64_t r, int64_t c) const {
     const int ri = static_cast<int>(r), ci = static_cast<int>(c);   // N, K < 2^31 is checked on the host
-    const int i = ri / static_cast<int>(vp), p = ri - i * static_cast<int>(vp);
-    const int j = ci / static_cast<int>(vq), q = ci - j * static_cast<int>(vq);  // vq % 8 == 0: the 8 columns share j
+    const int i = vp_shift >= 0 ? ri >> vp_shift : ri / static_cast<int>(vp), p = ri - i * static_cast<int>(vp);
+    const int j = vq_shift >= 0 ? ci >> vq_shift : ci / static_cast<int>(vq);    // vq % 8 == 0: the 8 columns share j
+    const int q = ci - j * static_cast<int>(vq);
     const float a = to_f32(w1[i * uq + j]);
     float wv[8], o[8], f2[8];
     unpack8(raw, wv);
@@ -181,7 +190,7 @@ int launch_merge(const void* w, const void* w1, const void* w2, float alpha, int
                  uint8_t* codes_colT, uint8_t* scales_col, int scale_layout, cudaStream_t s) {
   const MergeLoader<F> load{static_cast<const __nv_bfloat16*>(w), static_cast<const F*>(w1),
                             static_cast<const F*>(w2), static_cast<__nv_bfloat16*>(merged), alpha,
-                            K, N / up, K / uq, uq};
+                            K, N / up, K / uq, uq, log2_if_pow2(N / up), log2_if_pow2(K / uq)};
   const bool row = codes_row != nullptr, col = codes_colT != nullptr;
   if (!row && !col) {
     const int64_t total = N * (K / 8);

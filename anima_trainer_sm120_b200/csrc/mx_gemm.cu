@@ -6,11 +6,11 @@
 // e8m0 scale per 32 K-elements in the 128x4 tiled layout (see anima_b200.h), so the
 // forward, dgrad and wgrad GEMMs are all this one "TN" form.
 //
-// Two kernel families, both persistent and warp-specialised (192 threads: warp 0 TMA producer,
-// warp 1 MMA issuer, warps 2-5 epilogue), accumulating in tensor memory (fp32):
+// Two kernel families, both persistent and warp-specialised (warp 0 TMA producer, warp 1 MMA issuer, the
+// other warps epilogue), accumulating in tensor memory (fp32):
 //
-//  * mx_gemm2_kernel — the main one (M > 128 and N > 128): a cluster of two CTAs owns a 256 x 192
-//    tile and issues tcgen05.mma.cta_group::2 (M256 x N192 x K32); see the comment above it.
+//  * mx_gemm2_kernel<BN> — the main one (M > 128 and N > 128): a cluster of two CTAs owns a 256 x 192 (K < 4096)
+//    or 256 x 256 tile and issues tcgen05.mma.cta_group::2 (M256 x N192|256 x K32); see the comment above it.
 //  * mx_gemm_kernel<BN> — one CTA per 128 x BN tile (BN = 128 or 256) for small or narrow problems:
 //      warp 0  per K-block of 128 one 128x128 A box and one BNx128 B box (128-byte swizzle) plus the
 //              512-byte scale chunks (bulk copies), all completing on the stage's "full" mbarrier;
@@ -134,13 +134,14 @@ struct GemmParams {
   const __nv_bfloat16* residual;
   int64_t ldr;
   float alpha;
-  // Work list of the CTA-pair kernel (see PairPlan below): tile columns 0 .. n_wide-1 are 192 wide; if
+  // Work list of the CTA-pair kernel (see PairPlan below): tile columns 0 .. n_wide-1 are pair_bn wide; if
   // `narrow`, one more column of at most 128 valid outputs follows and is computed with N = 128 instructions
   // (n_tiles = n_wide + narrow). Items 0 .. full_items-1 are whole tiles in tile order, dealt round-robin to
   // the pairs (full_items is a multiple of the pair count). The tail_tiles tiles after them are each split along K
   // into tail_splits ranges of tail_kbs K-blocks; those items are dealt round-robin starting at pair tail_shift
-  // and leave as fp32 partial tiles in pair_partial [item][256][192], summed by pair_tail_finalize_kernel.
+  // and leave as fp32 partial tiles in pair_partial [item][256][pair_bn], summed by pair_tail_finalize_kernel.
   int n_wide, narrow;
+  int pair_bn;  // width of the wide tile columns, 192 or 256 (the finalize pass reads it; the kernel is compiled per width)
   int full_items, tail_tiles, tail_splits, tail_kbs, tail_shift;
   float* pair_partial;
   int sf_bufs;  // tensor-memory scale buffers the K-blocks rotate through (1, 2 or 4)
@@ -162,7 +163,8 @@ struct GemmParams {
   int delta, delta_block;
   // Measurement aid (anima_mx_gemm_set_clock_probe): if not null, CTA 0 of a pair-kernel launch adds the SM
   // cycles and the nanoseconds it ran, so that the clock the GPU actually held under this kernel's power
-  // draw can be read back (the driver's sampled clocks mostly see the idle gaps between launches).
+  // draw can be read back (the driver's sampled clocks mostly see the idle gaps between launches), and the
+  // cycles its producer, MMA-issuing and first epilogue warp spent waiting on their barriers.
   long long* clock_probe;
 };
 
@@ -220,6 +222,17 @@ __device__ __forceinline__ PairItem pair_item(const GemmParams& p, int slot) {
   }
   tile_coords(p, tile, it.mt, it.nt);
   return it;
+}
+
+// First slot >= `slot` of this pair's round robin (stride `stride`) that holds work; `it` receives its item.
+// Returns total_slots or more when there is none.
+__device__ __forceinline__ int pair_next_item(const GemmParams& p, int slot, int stride, int total_slots, PairItem& it) {
+  while (slot < total_slots) {
+    it = pair_item(p, slot);
+    if (it.valid) break;
+    slot += stride;
+  }
+  return slot;
 }
 
 // Epilogue store of one 32-column accumulator chunk of one row: bias, rounding, predicated 16-byte stores.
@@ -608,37 +621,63 @@ __global__ void __launch_bounds__(256) splitk_finalize_kernel(const GemmParams p
 }
 
 // ================================================================== 2-CTA variant
-// A cluster of two CTAs (two SMs) owns one 256 x 192 output tile. CTA r stages rows
-// [128 r, 128 r + 128) of the A tile and rows [96 r, 96 r + 96) of the B tile, so every
-// tcgen05.mma (cta_group::2, M256 x N192 x K32) is fed by 7 KB of shared-memory fill per
-// SM (the one-CTA kernel needs 12 KB per M128 x N256 x K32), and 6 stages are in flight.
-// N = 192 leaves room in tensor memory for two DISJOINT accumulator buffers (2 x 192
-// columns) next to the 12 scale columns, so the next tile's MMAs start the moment the
-// previous tile's are issued; with N = 256 the buffers must share columns and the tensor
-// pipe idles at every tile boundary until the epilogue has drained them.
+// A cluster of two CTAs (two SMs) owns one 256 x BN output tile, BN = 192 or 256. CTA r stages rows
+// [128 r, 128 r + 128) of the A tile and its half of the B tile's rows, so every tcgen05.mma (cta_group::2,
+// M256 x N192 x K32) is fed by 7 KB of shared-memory fill per SM (the one-CTA kernel needs 12 KB per
+// M128 x N256 x K32), and 5 or 6 stages are in flight.
 // Only the leader CTA (cluster rank 0) issues scale copies, MMAs and commits; the commits
 // are delivered to the mbarriers of both CTAs, and both CTAs' TMA loads complete on the
 // leader's "full" barrier. Each CTA drains its own 128 accumulator rows. The loads carry no
 // multicast: each CTA fetches its own boxes.
-// Tile width 192: tiles start at multiples of 64 columns, so a tile touches two 128-column scale chunks of B
-// and its scales start 0 or 2 tensor-memory columns into the first. A 224-wide variant (tiles at multiples of
-// 32, odd scale-column offsets) raised a misaligned-address fault on its first tile with an odd offset; widths
-// that are not multiples of 64 are therefore not used.
-constexpr int kBN2 = 192;
-constexpr int kStages2 = 6;
+// Tile widths are multiples of 64: tiles start at multiples of 64 columns, so a tile touches two 128-column scale
+// chunks of B and its scales start 0 or 2 tensor-memory columns into the first. A 224-wide variant (tiles at
+// multiples of 32, odd scale-column offsets) raised a misaligned-address fault on its first tile with an odd
+// offset; such widths are therefore not used.
+// What limits it (cycle counters of anima_mx_gemm_set_clock_probe, and builds with parts of the epilogue left
+// out): one more K-block costs the tensor pipe's 384 (512) cycles, i.e. the main loop is MMA-bound; each tile
+// adds about 1200 cycles at BN = 192, of which ~350 are the epilogue's st.shared into the staging buffers and
+// ~200 its TMA stores (the tensor pipe loses about one cycle per 128-byte shared-memory write of the epilogue),
+// and about 2800 at BN = 256 where a tile also waits for the previous one to be read. The SM clock sits at the
+// board's power limit throughout, so energy per flop (operand traffic per flop: 7/8 at BN = 256) decides as much
+// as idle cycles do.
+// Epilogue warps per CTA: 4 * kEpiHalves. With two halves, two warps share each 32-lane quadrant of tensor memory
+// and drain different column ranges of the accumulator at the same time.
+#ifndef ANIMA_PAIR_EPI_HALVES
+#define ANIMA_PAIR_EPI_HALVES 2
+#endif
+constexpr int kEpiHalves = ANIMA_PAIR_EPI_HALVES;
+constexpr int kThreads2 = 64 + 128 * kEpiHalves;
 constexpr int kSfbChunks2 = 2;  // 128-column scale chunks of B a tile can touch
-static_assert(kBN2 % 64 == 0 && 2 * kBN2 + 64 <= 512, "two accumulator buffers and four scale buffers must fit");
+static_assert(kEpiHalves == 1 || kEpiHalves == 2, "one or two epilogue warps per tensor-memory quadrant");
 
+// Two tile widths. 256 x 192: two disjoint accumulator buffers, so a tile's MMAs follow the previous tile's
+// without a gap; per K-block the tensor pipe works 384 cycles on 28 KB of operands. 256 x 256: 512 cycles on
+// 32 KB, i.e. less shared-memory and L2 traffic (and energy) per flop, but the two buffers must share 32 columns
+// of tensor memory and every tile starts only after the epilogue has read those columns of the tile before it
+// (about 2000 idle cycles per tile, measured). The wide form wins once a tile holds enough K-blocks to pay for
+// that gap (K >= 4096 on a power-capped B200), the narrow form below.
+template <int BN>
 struct Cfg2 {
+  static_assert(BN == 192 || BN == 256, "tile widths whose scale columns start at even tensor-memory offsets");
+  static constexpr int kStages = BN == 256 ? 5 : 6;
   static constexpr int kABytes = 128 * BK;
-  static constexpr int kBBytes = (kBN2 / 2) * BK;  // this CTA's half of the B rows
-  static constexpr int kAcc1Col = kBN2;            // second accumulator buffer
-  static constexpr int kSfaCol = 2 * kBN2;         // scale buffers: 16 columns each (SFA 4, SFB 2 x 4), up to 4 of them
+  static constexpr int kBBytes = (BN / 2) * BK;  // this CTA's half of the B rows
+  // At N = 192 the accumulator buffers are disjoint. At N = 256 buffer 0 = columns 0..255 and buffer 1 =
+  // 224..479: the epilogue reads the shared columns first (buffer 0: its last chunk, buffer 1: its first).
+  static constexpr int kOverlap = (BN == 256) ? 32 : 0;
+  static constexpr int kAcc1Col = BN - kOverlap;  // second accumulator buffer
+  static constexpr int kSfaCol = 2 * BN - kOverlap;  // scale buffers: 16 columns each (SFA 4, SFB 2 x 4)
   static constexpr int kTmemCols = 512;
+  static constexpr int kMaxSfBufs = (kTmemCols - kSfaCol) / 16 >= 4 ? 4 : 2;
+  static_assert(kSfaCol + 16 * kMaxSfBufs <= kTmemCols, "accumulators and scale buffers must fit tensor memory");
   static constexpr int kSfBytes = kSfChunk * (1 + kSfbChunks2);  // SFA chunk + the SFB chunks
   static constexpr int kStageBytes = kABytes + kBBytes + kSfBytes;
-  static constexpr int kStoreBytes = 128 * 128;  // one 128-row x 32-column output chunk (fp32 worst case)
-  static constexpr int kSmemBytes = kStages2 * kStageBytes + 2 * kStoreBytes + 1024 + 256;
+  // Output staging, per epilogue half: two buffers of one 128-row x 32-column bf16 chunk each, alternating; an
+  // fp32 chunk takes both (single-buffered: fp32 outputs are the long-K products, whose epilogue is idle most of
+  // the time).
+  static constexpr int kStoreBytes = 128 * 64;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiHalves * 2 * kStoreBytes + 1024 + 256;
+  static_assert(kSmemBytes <= 227 * 1024, "pair kernel exceeds the shared memory of one CTA");
   static constexpr uint32_t kTxBytes = 2u * kStageBytes;  // both CTAs land on the leader's barrier
 };
 
@@ -740,33 +779,37 @@ __device__ __forceinline__ void tc2_kblock(uint32_t d_tmem, uint32_t a_lo, uint3
       : "memory");
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+template <int BN>
+__global__ void __launch_bounds__(kThreads2, 1)
 mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const __grid_constant__ CUtensorMap map_sfa, const __grid_constant__ CUtensorMap map_sfb,
                 const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_part,
                 const __grid_constant__ CUtensorMap map_pl, const __grid_constant__ CUtensorMap map_d,
                 const __grid_constant__ CUtensorMap map_plsf, const __grid_constant__ CUtensorMap map_dsf,
                 const GemmParams p) {
-  using C = Cfg2;
+  using C = Cfg2<BN>;
+  constexpr int kStages2 = C::kStages;
   extern __shared__ uint8_t smem_raw[];
   __shared__ volatile int abort_flag;
   __shared__ uint32_t tmem_base_slot;
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t store_base = base + kStages2 * (Cfg2::kABytes + Cfg2::kBBytes);  // 1024-aligned staging for C
-  const uint32_t sf_base = store_base + 2 * Cfg2::kStoreBytes;
-  const uint32_t bar_base = sf_base + kStages2 * Cfg2::kSfBytes;
-  auto a_smem = [&](int s) { return base + s * (Cfg2::kABytes + Cfg2::kBBytes); };
-  auto b_smem = [&](int s) { return a_smem(s) + Cfg2::kABytes; };
-  auto sfa_smem = [&](int s) { return sf_base + s * Cfg2::kSfBytes; };
+  const uint32_t store_base = base + kStages2 * (C::kABytes + C::kBBytes);  // 1024-aligned staging for C
+  const uint32_t sf_base = store_base + kEpiHalves * 2 * C::kStoreBytes;
+  const uint32_t bar_base = sf_base + kStages2 * C::kSfBytes;
+  auto a_smem = [&](int s) { return base + s * (C::kABytes + C::kBBytes); };
+  auto b_smem = [&](int s) { return a_smem(s) + C::kABytes; };
+  auto sfa_smem = [&](int s) { return sf_base + s * C::kSfBytes; };
   auto sfb_smem = [&](int s) { return sfa_smem(s) + kSfChunk; };
   auto full_bar = [&](int s) { return bar_base + 8 * s; };
   auto empty_bar = [&](int s) { return bar_base + 8 * (kStages2 + s); };
   auto acc_full_bar = [&](int s) { return bar_base + 8 * (2 * kStages2 + s); };
   auto acc_empty_bar = [&](int s) { return bar_base + 8 * (2 * kStages2 + 2 + s); };
+  auto ovl_free_bar = [&](int s) { return bar_base + 8 * (2 * kStages2 + 4 + s); };  // N = 256 only
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const bool probe = p.clock_probe != nullptr;
   const long long probe_cycles0 = clock64();
   const uint64_t probe_ns0 = global_timer_ns();
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
@@ -779,8 +822,10 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
     mbar_init(acc_full_bar(0), 1);
     mbar_init(acc_full_bar(1), 1);
-    mbar_init(acc_empty_bar(0), 8);  // 4 epilogue warps of each CTA arrive on the leader's barriers
-    mbar_init(acc_empty_bar(1), 8);
+    mbar_init(acc_empty_bar(0), 8 * kEpiHalves);  // every epilogue warp of both CTAs arrives on the leader's barriers
+    mbar_init(acc_empty_bar(1), 8 * kEpiHalves);
+    mbar_init(ovl_free_bar(0), 8);  // the four warps of the half that owns the shared columns, in both CTAs
+    mbar_init(ovl_free_bar(1), 8);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
@@ -816,19 +861,27 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       uint32_t ph = 0;
       bool ok = true;
       const uint32_t leader_full0 = map_to_cta(full_bar(0), 0);
-      for (int slot = pair; slot < total_slots && ok; slot += num_pairs) {
-        const PairItem it = pair_item(p, slot);
-        if (!it.valid) continue;
+      long long w_empty = 0;
+      PairItem it = {}, next_it = {};
+      for (int slot = pair_next_item(p, pair, num_pairs, total_slots, it), next_slot; slot < total_slots && ok;
+           slot = next_slot, it = next_it) {
+        // the next item is worked out before this item's K loop: the divisions of its tile index stay off the
+        // path between the last instruction of one tile and the first of the next
+        next_slot = pair_next_item(p, slot + num_pairs, num_pairs, total_slots, next_it);
         const bool narrow = it.nt >= p.n_wide;  // N = 128 instruction: each CTA supplies 64 rows of B
         const int row_a = it.mt * 256 + static_cast<int>(rank) * 128;
-        const int row_b = it.nt * kBN2 + static_cast<int>(rank) * (narrow ? 64 : kBN2 / 2);
-        const int sfa_rt = it.mt * 2 + static_cast<int>(rank), sfb_rt = (it.nt * kBN2) >> 7;
+        const int row_b = it.nt * BN + static_cast<int>(rank) * (narrow ? 64 : BN / 2);
+        const int sfa_rt = it.mt * 2 + static_cast<int>(rank), sfb_rt = (it.nt * BN) >> 7;
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
-          if (!mbar_try_wait(empty_bar(s), ph ^ 1u)) ok = mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag);
+          if (!mbar_try_wait(empty_bar(s), ph ^ 1u)) {
+            const long long t0 = probe ? clock64() : 0;
+            ok = mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag);
+            if (probe) w_empty += clock64() - t0;
+          }
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           if (elect_one()) {
-            if (rank == 0) mbar_expect_tx(full_bar(s), Cfg2::kTxBytes);
+            if (rank == 0) mbar_expect_tx(full_bar(s), C::kTxBytes);
             const uint32_t leader_full = leader_full0 + 8 * s;
             tma2_load_2d(a_smem(s), &map_a, leader_full, kb * BK, row_a);
             tma2_load_2d(b_smem(s), &map_b, leader_full, kb * BK, row_b);  // 96-row box; rows past N read as 0
@@ -840,8 +893,8 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         if (p.delta && it.kb1 == p.k_blocks) {
           // one stage per run of this tile's columns inside one delta block
-          int c = it.nt * kBN2;
-          const int c_end = min(c + (narrow ? 128 : kBN2), p.N);
+          int c = it.nt * BN;
+          const int c_end = min(c + (narrow ? 128 : BN), p.N);
           while (c < c_end) {
             const int blk = c / p.delta_block, p0 = c - blk * p.delta_block;
             const int n = min(c_end - c, p.delta_block - p0);
@@ -849,7 +902,7 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             if (elect_one()) {
-              if (rank == 0) mbar_expect_tx(full_bar(s), Cfg2::kTxBytes);
+              if (rank == 0) mbar_expect_tx(full_bar(s), C::kTxBytes);
               const uint32_t leader_full = leader_full0 + 8 * s;
               const int prow = blk * p.M + row_a;  // row of the plane matrix [8 * M, 128]
               tma2_load_2d(a_smem(s), &map_pl, leader_full, 0, prow);
@@ -863,6 +916,7 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           }
         }
       }
+      if (probe && blockIdx.x == 0 && lane == 0) p.clock_probe[3] += w_empty;
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
@@ -875,31 +929,43 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       int it_n = 0;
       uint32_t sf_rot = 0;  // scale buffer of the next K-block
       const uint32_t sf_mask = static_cast<uint32_t>(p.sf_bufs - 1);
-      for (int slot = pair; slot < total_slots && ok; slot += num_pairs) {
-        const PairItem it = pair_item(p, slot);
-        if (!it.valid) continue;
+      long long w_full = 0, w_acc = 0;
+      PairItem it = {}, next_it = {};
+      for (int slot = pair_next_item(p, pair, num_pairs, total_slots, it), next_slot; slot < total_slots && ok;
+           slot = next_slot, it = next_it) {
+        // the next item is worked out before this item's K loop: the divisions of its tile index stay off the
+        // path between the last instruction of one tile and the first of the next
+        next_slot = pair_next_item(p, slot + num_pairs, num_pairs, total_slots, next_it);
         const int as = it_n & 1;
         // the epilogues of both CTAs must have drained this buffer (used by item it_n - 2)
+        const long long ta = probe ? clock64() : 0;
         ok = __all_sync(0xffffffffu, mbar_wait(acc_empty_bar(as), ((it_n >> 1) & 1u) ^ 1u, &abort_flag));
+        if (C::kOverlap && ok && it_n > 0)  // the tile before this one has read the columns its buffer shares with ours
+          ok = __all_sync(0xffffffffu, mbar_wait(ovl_free_bar(as ^ 1), ((it_n - 1) >> 1) & 1u, &abort_flag));
+        if (probe) w_acc += clock64() - ta;
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (as ? C::kAcc1Col : 0);
-        const uint32_t idesc = pair_idesc(it.nt >= p.n_wide ? 128 : kBN2);
+        const uint32_t idesc = pair_idesc(it.nt >= p.n_wide ? 128 : BN);
         // a tile starts 0 or 64 columns into its first 128-column scale chunk: 32 columns per TMEM column
-        const uint32_t sfb_off = ((it.nt * kBN2) & 127) >> 5;
+        const uint32_t sfb_off = ((it.nt * BN) & 127) >> 5;
         uint32_t acc = 0;
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
-          if (!mbar_try_wait(full_bar(s), ph)) ok = mbar_wait(full_bar(s), ph, &abort_flag);
+          if (!mbar_try_wait(full_bar(s), ph)) {
+            const long long t0 = probe ? clock64() : 0;
+            ok = mbar_wait(full_bar(s), ph, &abort_flag);
+            if (probe) w_full += clock64() - t0;
+          }
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t a_lo = a_lo0 + s * ((Cfg2::kABytes + Cfg2::kBBytes) >> 4);
-          const uint32_t sf_lo = sf_lo0 + s * (Cfg2::kSfBytes >> 4);
+          const uint32_t a_lo = a_lo0 + s * ((C::kABytes + C::kBBytes) >> 4);
+          const uint32_t sf_lo = sf_lo0 + s * (C::kSfBytes >> 4);
           // The scale columns rotate so that the copy for this K-block need not wait for the MMAs of the
           // previous one to have read theirs.
           const uint32_t sfa_t = tmem_base + C::kSfaCol + 16u * sf_rot, sfb_t = sfa_t + 4;
           if (elect_one())
-            tc2_kblock(d_tmem, a_lo, a_lo + (Cfg2::kABytes >> 4), sf_lo, sfa_t, sfb_t, sfb_t + sfb_off, acc, empty_bar(s),
+            tc2_kblock(d_tmem, a_lo, a_lo + (C::kABytes >> 4), sf_lo, sfa_t, sfb_t, sfb_t + sfb_off, acc, empty_bar(s),
                        idesc);
           __syncwarp();
           acc = 1;
@@ -907,9 +973,9 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           if (++s == kStages2) { s = 0; ph ^= 1u; }
         }
         if (ok && p.delta && it.kb1 == p.k_blocks) {
-          const int col0 = it.nt * kBN2;
+          const int col0 = it.nt * BN;
           int c = col0;
-          const int c_end = min(c + (it.nt >= p.n_wide ? 128 : kBN2), p.N);
+          const int c_end = min(c + (it.nt >= p.n_wide ? 128 : BN), p.N);
           while (c < c_end) {
             const int blk = c / p.delta_block, p0 = c - blk * p.delta_block;
             const int n = min(c_end - c, p.delta_block - p0);
@@ -917,11 +983,11 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t a_lo = a_lo0 + s * ((Cfg2::kABytes + Cfg2::kBBytes) >> 4);
-            const uint32_t sf_lo = sf_lo0 + s * (Cfg2::kSfBytes >> 4);
+            const uint32_t a_lo = a_lo0 + s * ((C::kABytes + C::kBBytes) >> 4);
+            const uint32_t sf_lo = sf_lo0 + s * (C::kSfBytes >> 4);
             const uint32_t sfa_t = tmem_base + C::kSfaCol + 16u * sf_rot, sfb_t = sfa_t + 4;
             if (elect_one())
-              tc2_kblock(d_tmem + static_cast<uint32_t>(c - col0), a_lo, a_lo + (Cfg2::kABytes >> 4), sf_lo, sfa_t, sfb_t,
+              tc2_kblock(d_tmem + static_cast<uint32_t>(c - col0), a_lo, a_lo + (C::kABytes >> 4), sf_lo, sfa_t, sfb_t,
                          sfb_t + static_cast<uint32_t>((p0 & 127) >> 5), acc, empty_bar(s), pair_idesc(n));
             __syncwarp();
             acc = 1;
@@ -934,41 +1000,66 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         __syncwarp();
         ++it_n;
       }
+      if (probe && blockIdx.x == 0 && lane == 0) {
+        p.clock_probe[4] += w_full;
+        p.clock_probe[5] += w_acc;
+      }
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
     // Each 128-row x 32-column chunk goes tensor memory -> registers -> (bias, rounding) -> a swizzled
     // shared-memory staging buffer -> one TMA store, which writes full lines and clips rows / columns that
     // lie outside C. Two staging buffers alternate; named barrier 1 joins the 128 epilogue threads.
-    const int quad = warp & 3;
+    const int quad = warp & 3;          // the 32-lane quadrant of tensor memory this warp may read
+    const int half = (warp - 2) >> 2;   // which share of the tile's column chunks this warp drains
     const int r_in = quad * 32 + lane;  // row inside this CTA's 128 accumulator rows
     // residual == C (bf16, same pitch): the tile is ADDED to C by the TMA store (bf16 add at the memory side)
     // instead of being loaded by the epilogue threads, whose per-chunk loads would serialise on latency.
     const bool reduce_add = p.residual && static_cast<const void*>(p.residual) == p.c && !p.out_fp32 && p.ldr == p.ldc;
-    const bool issuer = threadIdx.x == 64;
+    const bool issuer = threadIdx.x == 64 + 128 * half;  // one thread per half issues and tracks its TMA stores
+    const uint32_t my_store = store_base + half * (2 * C::kStoreBytes);
+    const int bar_id = 1 + half;  // named barrier of this half's 128 threads
     const uint32_t leader_empty[2] = {map_to_cta(acc_empty_bar(0), 0), map_to_cta(acc_empty_bar(1), 0)};
+    const uint32_t leader_ovl[2] = {map_to_cta(ovl_free_bar(0), 0), map_to_cta(ovl_free_bar(1), 0)};
     bool ok = true;
     int it_n = 0;
     uint32_t buf = 0;
-    for (int slot = pair; slot < total_slots && ok; slot += num_pairs) {
-      const PairItem it = pair_item(p, slot);
-      if (!it.valid) continue;
+    bool last_fp32 = false;
+    long long w_idle = 0;
+    PairItem it = {}, next_it = {};
+    for (int slot = pair_next_item(p, pair, num_pairs, total_slots, it), next_slot; slot < total_slots && ok;
+         slot = next_slot, it = next_it) {
+      next_slot = pair_next_item(p, slot + num_pairs, num_pairs, total_slots, next_it);
       const int as = it_n & 1;
-      if (!mbar_wait(acc_full_bar(as), (it_n >> 1) & 1u, &abort_flag, 200)) { ok = false; break; }
+      const long long te = probe ? clock64() : 0;
+      // the half that owns the columns shared with the other buffer is on the path to the next tile's first MMA:
+      // it polls without backing off
+      const bool ovl_owner = C::kOverlap && half == (as == 0 ? kEpiHalves - 1 : 0);
+      if (!mbar_wait(acc_full_bar(as), (it_n >> 1) & 1u, &abort_flag, ovl_owner ? 0 : 200)) { ok = false; break; }
+      if (probe) w_idle += clock64() - te;
       ++it_n;
       tc_fence_after();
       const bool partial = it.part >= 0;  // a K-range of a tail tile: raw fp32 accumulators to the scratch tile
       const int row0 = partial ? it.part * 256 + static_cast<int>(rank) * 128 : it.mt * 256 + static_cast<int>(rank) * 128;
-      const int col_base = partial ? 0 : it.nt * kBN2;
-      const int chunks = it.nt >= p.n_wide ? 4 : kBN2 / 32;  // the narrow column accumulates 128 columns only
+      const int col_base = partial ? 0 : it.nt * BN;
+      // 32-column chunks per half: the narrow column accumulates 128 columns only
+      const int chunks = (it.nt >= p.n_wide ? 4 : BN / 32) / kEpiHalves;
       const bool fp32_stage = partial || p.out_fp32;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + (as ? C::kAcc1Col : 0);
 #pragma unroll 1
-      for (int chunk = 0; chunk < chunks; ++chunk, buf ^= 1u) {
+      // Shared columns first: buffer 0 is drained from its last chunk down, buffer 1 from its first chunk up.
+      const bool reverse = C::kOverlap && as == 0;
+      for (int ci = 0; ci < chunks; ++ci, buf ^= 1u) {
+        const int chunk = half * chunks + (reverse ? chunks - 1 - ci : ci);
         uint32_t v[32];
         tc_ld32(t_row + chunk * 32, v);
         tc_wait_ld();
-        if (chunk == chunks - 1) {  // buffer fully read: hand it back to the MMA warp
+        if (ovl_owner && ci == 0) {  // the next tile's MMAs may overwrite the shared columns
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(leader_ovl[as]);
+        }
+        if (ci == chunks - 1) {  // this warp's share is read: hand it back to the MMA warp
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(leader_empty[as]);
@@ -1005,9 +1096,17 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
           }
         }
-        const uint32_t stage = store_base + buf * Cfg2::kStoreBytes;
-        // the store that last read this staging buffer (two chunks ago) was waited for by the issuer
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const uint32_t stage = my_store + (fp32_stage ? 0u : buf * C::kStoreBytes);
+        // The stores that last read the staging bytes about to be written must have finished reading them: all
+        // earlier ones when this chunk or the previous one is fp32 (both buffers), else all but the latest.
+        if (issuer) {
+          if (fp32_stage || last_fp32)
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          else
+            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        }
+        last_fp32 = fp32_stage;
+        asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
         if (fp32_stage) {  // 128-byte rows, 128-byte swizzle: 16-byte piece j of row r sits at piece j ^ (r & 7)
           const uint32_t rb = stage + r_in * 128;
 #pragma unroll
@@ -1030,7 +1129,7 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the TMA engine
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
         if (issuer) {
           if (partial)
             asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&map_part),
@@ -1046,11 +1145,11 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                          "r"(stage), "r"(col0), "r"(row0)
                          : "memory");
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // the other buffer may be rewritten
         }
       }
     }
     if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if (probe && blockIdx.x == 0 && threadIdx.x == 64) p.clock_probe[6] += w_idle;
   }
 
   // ---------------------------------------------------------------- teardown
@@ -1062,7 +1161,7 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();  // neither CTA releases shared or tensor memory while its peer may still use it
-  if (p.clock_probe && blockIdx.x == 0 && threadIdx.x == 0) {
+  if (probe && blockIdx.x == 0 && threadIdx.x == 0) {
     p.clock_probe[0] += clock64() - probe_cycles0;
     p.clock_probe[1] += static_cast<long long>(global_timer_ns() - probe_ns0);
     p.clock_probe[2] += 1;  // launches seen
@@ -1074,9 +1173,10 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 }
 
 // C tile = sum over the K-range partials of a tail tile, in index order (reproducible), then the epilogue
-// (alpha, bias, residual, rounding). One thread per 4 columns of a 256 x 192 tile.
+// (alpha, bias, residual, rounding). One thread per 4 columns of a 256 x pair_bn tile.
 __global__ void __launch_bounds__(256) pair_tail_finalize_kernel(const GemmParams p) {
-  constexpr int kPerRow = kBN2 / 4, kPerTile = 256 * kPerRow, kTileElems = 256 * kBN2;
+  const int kBN2 = p.pair_bn;
+  const int kPerRow = kBN2 / 4, kPerTile = 256 * kPerRow, kTileElems = 256 * kBN2;
   const int64_t total = static_cast<int64_t>(p.tail_tiles) * kPerTile;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -1160,8 +1260,8 @@ bool make_c_map(CUtensorMap* map, const GemmParams& p) {
             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// The scratch of the K-split tail tiles viewed as fp32 [items * 256, 192] for the epilogue's TMA stores.
-bool make_part_map(CUtensorMap* map, float* ptr, int64_t items) {
+// The scratch of the K-split tail tiles viewed as fp32 [items * 256, tile width] for the epilogue's TMA stores.
+bool make_part_map(CUtensorMap* map, float* ptr, int64_t items, int kBN2) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(kBN2), static_cast<cuuint64_t>(std::max<int64_t>(items, 1) * 256)};
@@ -1185,17 +1285,18 @@ int env_int(const char* name, int fallback) {
 // the whole problem when it has fewer tiles than pairs, may be split along K so that every pair ends at about
 // the same time instead of a few pairs running one more tile while the rest idle: the weight gradient
 // dW[2048, 2048] over K = 32768 is 88 tiles on 74 pairs, i.e. two rounds for 1.19 rounds of work.
-// The choice minimises the modelled finish time (unit: one K-block of a wide tile; a narrow tile costs 2/3,
+// The choice minimises the modelled finish time (unit: one K-block of a wide tile; a narrow tile costs 128 / width,
 // every item a constant, a split item a larger constant for its fp32 partial store, the finalize pass a
 // constant) over the number of splits; it depends on the shape and the SM count only, so results are
 // reproducible from call to call.
 struct PairPlan {
-  int pairs, n_wide, narrow, full_items, tail_tiles, tail_splits, tail_kbs, tail_shift;
+  int pairs, n_wide, narrow, full_items, tail_tiles, tail_splits, tail_kbs, tail_shift, bn;
   int64_t ws_bytes;
 };
 
-PairPlan plan_pair_uncached(int64_t M, int64_t N, int64_t K, bool allow_split, int sms) {
+PairPlan plan_pair_uncached(int64_t M, int64_t N, int64_t K, bool allow_split, int sms, int kBN2) {
   PairPlan pl{};
+  pl.bn = kBN2;
   const int m_tiles = static_cast<int>(ceil_div(M, 256));
   pl.n_wide = static_cast<int>(N / kBN2);
   const int rem_cols = static_cast<int>(N - static_cast<int64_t>(pl.n_wide) * kBN2);
@@ -1208,7 +1309,7 @@ PairPlan plan_pair_uncached(int64_t M, int64_t N, int64_t K, bool allow_split, i
   auto tile_cost = [&](int tile, double frac) {
     int mt, nt;
     tile_coords_of(m_tiles, n_tiles, tile, mt, nt);
-    return (nt < pl.n_wide ? 1.0 : 2.0 / 3.0) * kb * frac;
+    return (nt < pl.n_wide ? 1.0 : 128.0 / kBN2) * kb * frac;
   };
 
   double best = 1e300;
@@ -1255,18 +1356,27 @@ PairPlan plan_pair_uncached(int64_t M, int64_t N, int64_t K, bool allow_split, i
   return pl;
 }
 
+// Tile width for a problem: 256 when a tile holds at least 32 K-blocks (its start-up gap is then under a
+// tenth of the tile), else 192. ANIMA_MX_GEMM_BN = 192 / 256 forces one (read per call; for tests and tuning).
+int pair_tile_width(int64_t K) {
+  const int forced = env_int("ANIMA_MX_GEMM_BN", 0);
+  if (forced == 192 || forced == 256) return forced;
+  return K >= 4096 ? 256 : 192;
+}
+
 PairPlan plan_pair(int64_t M, int64_t N, int64_t K, bool allow_split) {
   const int sms = sm_count();
+  const int bn = pair_tile_width(K);
   const int narrow = env_int("ANIMA_MX_GEMM_NARROW", 1), tail = env_int("ANIMA_MX_GEMM_TAIL", 1);
   using Key = std::tuple<int64_t, int64_t, int64_t, int, int>;
   static std::mutex mu;
   static std::map<Key, PairPlan> cache;
-  const Key key{M, N, K, sms, (allow_split ? 1 : 0) | (narrow ? 2 : 0) | (tail ? 4 : 0)};
+  const Key key{M, N, K, sms, (allow_split ? 1 : 0) | (narrow ? 2 : 0) | (tail ? 4 : 0) | (bn == 256 ? 8 : 0)};
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) return it->second;
   if (cache.size() > 4096) cache.clear();
-  const PairPlan pl = plan_pair_uncached(M, N, K, allow_split, sms);
+  const PairPlan pl = plan_pair_uncached(M, N, K, allow_split, sms, bn);
   cache.emplace(key, pl);
   return pl;
 }
@@ -1281,22 +1391,35 @@ struct DeltaOperands {
   int64_t block;
 };
 
+template <int BN>
+int launch_pair_width(const uint8_t* a_codes, const uint8_t* b_codes, GemmParams p, const PairPlan& pl, void* workspace,
+                      const DeltaOperands& delta, cudaStream_t s);
+
 int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmParams p, void* workspace, int64_t workspace_bytes,
                 const DeltaOperands& delta, cudaStream_t s) {
-  static PerDeviceOnce once;
-  const cudaError_t attr_rc = per_device_once(once, [] {
-    return cudaFuncSetAttribute(mx_gemm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg2::kSmemBytes);
-  });
-  ANIMA_REQUIRE(attr_rc == cudaSuccess, ANIMA_E_CUDA, "mx_gemm: cannot reserve %d bytes of shared memory: %s",
-                Cfg2::kSmemBytes, cudaGetErrorString(attr_rc));
   const PairPlan pl = plan_pair(p.M, p.N, p.K, workspace != nullptr);
   ANIMA_REQUIRE(workspace_bytes >= pl.ws_bytes, ANIMA_E_WORKSPACE,
                 "mx_gemm: workspace of %lld bytes is too small (need %lld)", (long long)workspace_bytes,
                 (long long)pl.ws_bytes);
+  return pl.bn == 256 ? launch_pair_width<256>(a_codes, b_codes, p, pl, workspace, delta, s)
+                      : launch_pair_width<192>(a_codes, b_codes, p, pl, workspace, delta, s);
+}
+
+template <int kBN2>
+int launch_pair_width(const uint8_t* a_codes, const uint8_t* b_codes, GemmParams p, const PairPlan& pl, void* workspace,
+                      const DeltaOperands& delta, cudaStream_t s) {
+  using C2 = Cfg2<kBN2>;
+  static PerDeviceOnce once;
+  const cudaError_t attr_rc = per_device_once(once, [] {
+    return cudaFuncSetAttribute(mx_gemm2_kernel<kBN2>, cudaFuncAttributeMaxDynamicSharedMemorySize, C2::kSmemBytes);
+  });
+  ANIMA_REQUIRE(attr_rc == cudaSuccess, ANIMA_E_CUDA, "mx_gemm: cannot reserve %d bytes of shared memory: %s",
+                C2::kSmemBytes, cudaGetErrorString(attr_rc));
   p.m_tiles = static_cast<int>(ceil_div(p.M, 256));
   p.n_wide = pl.n_wide;
   p.narrow = pl.narrow;
   p.n_tiles = pl.n_wide + pl.narrow;
+  p.pair_bn = kBN2;
   p.full_items = pl.full_items;
   p.tail_tiles = pl.tail_tiles;
   p.tail_splits = pl.tail_splits;
@@ -1307,13 +1430,13 @@ int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmParams p, vo
     int dev = 0;
     p.clock_probe = (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) ? g_clock_probe[dev] : nullptr;
   }
-  const int sf_bufs = env_int("ANIMA_MX_GEMM_SFBUFS", 4);
-  p.sf_bufs = (sf_bufs == 1 || sf_bufs == 2) ? sf_bufs : 4;
+  const int sf_bufs = env_int("ANIMA_MX_GEMM_SFBUFS", C2::kMaxSfBufs);
+  p.sf_bufs = (sf_bufs == 1 || sf_bufs == 2) ? sf_bufs : C2::kMaxSfBufs;
   CUtensorMap ma, mb, msa, msb, mc, mp;
   ANIMA_REQUIRE(make_map(&ma, a_codes, p.M, p.K, 128) && make_map(&mb, b_codes, p.N, p.K, kBN2 / 2) &&
                     make_sf_map(&msa, p.a_scales, p.sfa_rt, p.k_blocks, 1) &&
                     make_sf_map(&msb, p.b_scales, p.sfb_rt, p.k_blocks, kSfbChunks2) && make_c_map(&mc, p) &&
-                    (pl.ws_bytes ? make_part_map(&mp, p.pair_partial, static_cast<int64_t>(pl.tail_tiles) * pl.tail_splits)
+                    (pl.ws_bytes ? make_part_map(&mp, p.pair_partial, static_cast<int64_t>(pl.tail_tiles) * pl.tail_splits, kBN2)
                                  : make_c_map(&mp, p)),
                 ANIMA_E_CUDA, "mx_gemm: cuTensorMapEncodeTiled failed (driver entry point missing or bad operand)");
   CUtensorMap mpl = ma, md = mb, mplsf = msa, mdsf = msb;   // placeholders when there is no delta
@@ -1329,8 +1452,8 @@ int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmParams p, vo
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pl.pairs);
-  cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = Cfg2::kSmemBytes;
+  cfg.blockDim = dim3(kThreads2);
+  cfg.dynamicSmemBytes = C2::kSmemBytes;
   cfg.stream = s;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1339,7 +1462,7 @@ int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmParams p, vo
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const cudaError_t rc = cudaLaunchKernelEx(&cfg, mx_gemm2_kernel, ma, mb, msa, msb, mc, mp, mpl, md, mplsf, mdsf, p);
+  const cudaError_t rc = cudaLaunchKernelEx(&cfg, mx_gemm2_kernel<kBN2>, ma, mb, msa, msb, mc, mp, mpl, md, mplsf, mdsf, p);
   ANIMA_REQUIRE(rc == cudaSuccess, ANIMA_E_CUDA, "mx_gemm: cluster launch failed: %s", cudaGetErrorString(rc));
   if (pl.ws_bytes) {
     const int64_t threads = static_cast<int64_t>(pl.tail_tiles) * 256 * (kBN2 / 4);
@@ -1497,26 +1620,26 @@ extern "C" int anima_mx_gemm_ex(const uint8_t* a_codes, const uint8_t* a_scales,
                       workspace, workspace_bytes, status, stream);
 }
 
-extern "C" int anima_mx_gemm_pair_plan(int64_t M, int64_t N, int64_t K, int with_workspace, int32_t* out8) {
-  ANIMA_REQUIRE(out8 != nullptr, ANIMA_E_ARG, "mx_gemm_pair_plan: null pointer");
+extern "C" int anima_mx_gemm_pair_plan(int64_t M, int64_t N, int64_t K, int with_workspace, int32_t* out9) {
+  ANIMA_REQUIRE(out9 != nullptr, ANIMA_E_ARG, "mx_gemm_pair_plan: null pointer");
   ANIMA_REQUIRE(M > 0 && N > 0 && K > 0, ANIMA_E_ARG, "mx_gemm_pair_plan: bad sizes");
   ANIMA_REQUIRE(M < (1ll << 31) - 256 && N < (1ll << 31) - 256 && K < (1ll << 31) - 256, ANIMA_E_TOO_LARGE,
                 "mx_gemm_pair_plan: a dimension exceeds 2^31");
   if (!use_pair(M, N)) return 1;
   const PairPlan pl = plan_pair(M, N, K, with_workspace != 0);
-  const int32_t v[8] = {pl.pairs, pl.n_wide, pl.narrow, pl.full_items, pl.tail_tiles, pl.tail_splits, pl.tail_kbs,
-                        pl.tail_shift};
-  for (int i = 0; i < 8; ++i) out8[i] = v[i];
+  const int32_t v[9] = {pl.pairs, pl.n_wide, pl.narrow, pl.full_items, pl.tail_tiles, pl.tail_splits, pl.tail_kbs,
+                        pl.tail_shift, pl.bn};
+  for (int i = 0; i < 9; ++i) out9[i] = v[i];
   return ANIMA_OK;
 }
 
-extern "C" int anima_mx_gemm_set_clock_probe(void* device_buffer_3xint64) {
+extern "C" int anima_mx_gemm_set_clock_probe(void* device_buffer_8xint64) {
   int dev = 0;
   const cudaError_t rc = cudaGetDevice(&dev);
   ANIMA_REQUIRE(rc == cudaSuccess && dev >= 0 && dev < 64, ANIMA_E_CUDA, "mx_gemm_set_clock_probe: no current device");
-  ANIMA_REQUIRE(!device_buffer_3xint64 || (reinterpret_cast<uintptr_t>(device_buffer_3xint64) & 7) == 0, ANIMA_E_ALIGN,
+  ANIMA_REQUIRE(!device_buffer_8xint64 || (reinterpret_cast<uintptr_t>(device_buffer_8xint64) & 7) == 0, ANIMA_E_ALIGN,
                 "mx_gemm_set_clock_probe: buffer must be 8-byte aligned");
-  g_clock_probe[dev] = static_cast<long long*>(device_buffer_3xint64);
+  g_clock_probe[dev] = static_cast<long long*>(device_buffer_8xint64);
   return ANIMA_OK;
 }
 

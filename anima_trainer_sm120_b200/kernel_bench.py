@@ -134,7 +134,7 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
         if not quiet:
             print(json.dumps(out[-1]), flush=True)
 
-    probe = torch.zeros(3, dtype=torch.int64, device="cuda")
+    probe = torch.zeros(8, dtype=torch.int64, device="cuda")
     sms = torch.cuda.get_device_properties(0).multi_processor_count
 
     def tensor(name, shape, flops, fn):
@@ -146,7 +146,7 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
         _lib.check(_lib.load().anima_mx_gemm_set_clock_probe(probe.data_ptr()))
         ms = t(fn)
         _lib.check(_lib.load().anima_mx_gemm_set_clock_probe(None))
-        cycles, ns, _ = (int(v) for v in probe.cpu().tolist())
+        cycles, ns, _, w_stage, w_operands, w_acc, w_epi, _ = (int(v) for v in probe.cpu().tolist())
         tf = flops / ms / 1e9
         ghz = cycles / ns if ns else None
         out.append({"kernel": name, "shape": shape, "ms": round(ms, 4), "bound": "tensor", "achieved": round(tf, 1),
@@ -156,6 +156,12 @@ def run(iters: int, only: str | None, small: bool, pick: str | None = None, dire
                     "frac_of_nominal_4500": round(tf / 4500.0, 3),
                     "sm_mhz_in_kernel": round(ghz * 1000.0) if ghz else None,
                     "tensor_pipe_util_at_that_clock": round(tf * 1e3 / (sms * 16384 * ghz), 3) if ghz else None})
+        if cycles:   # share of CTA 0's cycles its warps spent waiting (producer: free stage; issuer: operands,
+            # accumulator buffer; first epilogue warp: a finished accumulator)
+            out[-1]["wait_share"] = {"producer_free_stage": round(w_stage / cycles, 3),
+                                     "issuer_operands": round(w_operands / cycles, 3),
+                                     "issuer_accumulator": round(w_acc / cycles, 3),
+                                     "epilogue_idle": round(w_epi / cycles, 3)}
         if not quiet:
             print(json.dumps(out[-1]), flush=True)
 

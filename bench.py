@@ -378,11 +378,11 @@ def run_gpu_arm(args) -> None:
         sampler.start()
     # the clock the GPU holds INSIDE the GEMM (cycles / ns added up by CTA 0 of every launch): the driver's
     # sampled clocks mostly see the gaps between launches of a region this short
-    probe = torch.zeros(3, dtype=torch.int64, device=dev)
+    probe = torch.zeros(8, dtype=torch.int64, device=dev)
     _lib.check(_lib.load().anima_mx_gemm_set_clock_probe(probe.data_ptr()))
     ms_total = timed(False, args.steps, max(args.warmup, 3))
     _lib.check(_lib.load().anima_mx_gemm_set_clock_probe(None))
-    probe_cycles, probe_ns, probe_n = (int(v) for v in probe.cpu().tolist())
+    probe_cycles, probe_ns, probe_n = (int(v) for v in probe.cpu().tolist()[:3])
     clocks = sampler.stop() if rank == 0 else {}
     _lib.check_status_word(dev)
     n_launch = launches[0]

@@ -184,19 +184,25 @@ int anima_mx_gemm_delta(const uint8_t* a_codes, const uint8_t* a_scales,
                         void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
 
 /* The work list the CTA-pair kernel uses for a problem on the current device (no reference counterpart; for
- * tests and tuning, nothing is launched): out8 = { CTA pairs launched, 192-wide tile columns, 1 if a narrow
+ * tests and tuning, nothing is launched): out9 = { CTA pairs launched, wide tile columns, 1 if a narrow
  * last column (<= 128 outputs, computed with N = 128 instructions) follows them, whole-tile items dealt
  * round-robin, tail tiles after those, K-ranges per tail tile, K-blocks (of 128) per range, pair at which the
- * tail's round robin starts }. with_workspace == 0 gives the plan of a call without scratch (no K-split).
- * Returns 0, 1 if the shape runs on the one-CTA kernel instead (out8 untouched), or a negative status. */
-int anima_mx_gemm_pair_plan(int64_t M, int64_t N, int64_t K, int with_workspace, int32_t* out8);
+ * tail's round robin starts, width of the wide tile columns (256 for K >= 4096, else 192; the environment
+ * variable ANIMA_MX_GEMM_BN = 192 / 256 forces one) }. with_workspace == 0 gives the plan of a call without
+ * scratch (no K-split). Returns 0, 1 if the shape runs on the one-CTA kernel instead (out9 untouched), or a
+ * negative status. */
+int anima_mx_gemm_pair_plan(int64_t M, int64_t N, int64_t K, int with_workspace, int32_t* out9);
 
-/* Measurement aid (no reference counterpart). With a device buffer of three int64 registered for the current
- * device (zeroed by the caller), CTA 0 of every later CTA-pair GEMM launch on that device ADDS { SM cycles it
- * ran, nanoseconds it ran, 1 } to it: cycles / ns is the SM clock the GPU held under the kernel's own power
- * draw, which sampling nvidia-smi between launches does not show. NULL switches it off. The buffer must
- * outlive every launch made while it is registered; launches that overlap on several streams race on it. */
-int anima_mx_gemm_set_clock_probe(void* device_buffer_3xint64);
+/* Measurement aid (no reference counterpart). With a device buffer of eight int64 registered for the current
+ * device (zeroed by the caller), CTA 0 of every later CTA-pair GEMM launch on that device ADDS to it
+ *   [0] SM cycles it ran, [1] nanoseconds it ran, [2] 1,
+ *   [3] cycles its TMA producer waited for a free pipeline stage,
+ *   [4] cycles its MMA-issuing warp waited for operands to land, [5] ... for an accumulator buffer to be drained,
+ *   [6] cycles its first epilogue warp waited for a finished accumulator ([7] unused).
+ * [0] / [1] is the SM clock the GPU held under the kernel's own power draw, which sampling nvidia-smi between
+ * launches does not show. NULL switches it off. The buffer must outlive every launch made while it is
+ * registered; launches that overlap on several streams race on it. */
+int anima_mx_gemm_set_clock_probe(void* device_buffer_8xint64);
 
 /* ---------------------------------------------------------------- LoKr merged weight
  * ref: lokr_patch.py:76-84 (merged = W + alpha * kron(w1, w2)) followed by the two

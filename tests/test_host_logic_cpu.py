@@ -206,9 +206,9 @@ def _pair_plan(M, N, K, ws=1):
     import ctypes
 
     from anima_trainer_sm120_b200 import _lib
-    out = (ctypes.c_int32 * 8)()
+    out = (ctypes.c_int32 * 9)()
     rc = _lib.load().anima_mx_gemm_pair_plan(M, N, K, ws, out)
-    return rc, dict(zip(("pairs", "n_wide", "narrow", "full_items", "tail_tiles", "splits", "kbs", "shift"), out))
+    return rc, dict(zip(("pairs", "n_wide", "narrow", "full_items", "tail_tiles", "splits", "kbs", "shift", "bn"), out))
 
 
 def _walk_plan(M, N, K, pl):
@@ -245,12 +245,17 @@ def _walk_plan(M, N, K, pl):
     (4096, 2048, 1024), (2048, 1024, 4096), (512, 512, 16384), (257, 384, 416), (130, 264, 160), (256, 136, 32),
 ])
 @pytest.mark.parametrize("ws", [0, 1])
-def test_pair_kernel_work_list_covers_every_tile_and_k_block_once(M, N, K, ws):
+@pytest.mark.parametrize("width", [0, 192, 256])
+def test_pair_kernel_work_list_covers_every_tile_and_k_block_once(M, N, K, ws, width, monkeypatch):
+    if width:
+        monkeypatch.setenv("ANIMA_MX_GEMM_BN", str(width))
     rc, pl = _pair_plan(M, N, K, ws)
     assert rc == 0
+    bn = pl["bn"]
+    assert bn == (width or (256 if K >= 4096 else 192))
     m_tiles, kb = -(-M // 256), -(-K // 128)
     n_cols = pl["n_wide"] + pl["narrow"]
-    assert pl["n_wide"] * 192 + 128 * pl["narrow"] >= N > (n_cols - 1) * 192
+    assert pl["n_wide"] * bn + 128 * pl["narrow"] >= N > (n_cols - 1) * bn
     assert pl["full_items"] % pl["pairs"] == 0 and pl["full_items"] + pl["tail_tiles"] == m_tiles * n_cols
     assert pl["pairs"] <= 74 and (ws or pl["splits"] == 1)
     cover = _walk_plan(M, N, K, pl)
@@ -265,10 +270,17 @@ def test_pair_kernel_work_list_covers_every_tile_and_k_block_once(M, N, K, ws):
     assert sorted(parts) == list(range(len(parts)))                        # every partial slot written exactly once
     from anima_trainer_sm120_b200 import _lib
     need = _lib.load().anima_mx_gemm_workspace_bytes(M, N, K)
-    assert need == (len(parts) * 256 * 192 * 4 if ws else need)
+    assert need == (len(parts) * 256 * bn * 4 if ws else need)
 
 
-def test_pair_kernel_splits_the_partial_round_of_long_contractions_only():
+def test_pair_kernel_splits_the_partial_round_of_long_contractions_only(monkeypatch):
+    # default tile width: 256 from K = 4096 up
+    assert _pair_plan(2048, 2048, 32768)[1] | {"kbs": 0} == {
+        "pairs": 64, "n_wide": 8, "narrow": 0, "full_items": 64, "tail_tiles": 0, "splits": 1, "kbs": 0, "shift": 0,
+        "bn": 256}                                                         # 64 tiles of 256 x 256: one round, no tail
+    assert _pair_plan(6144, 2048, 32768)[1]["splits"] > 1                  # 192 tiles on 74 pairs: 44 tail tiles
+    assert _pair_plan(32768, 2048, 8192)[1]["bn"] == 256 and _pair_plan(32768, 8192, 2048)[1]["bn"] == 192
+    monkeypatch.setenv("ANIMA_MX_GEMM_BN", "192")
     assert _pair_plan(2048, 2048, 32768)[1]["splits"] > 1                  # 88 tiles on 74 pairs, 256 K-blocks each
     assert _pair_plan(2048, 2048, 32768, ws=0)[1]["splits"] == 1
     assert _pair_plan(32768, 2048, 2048)[1]["splits"] == 1                 # 16 K-blocks per tile: a split costs more
@@ -284,6 +296,6 @@ def test_pair_kernel_splits_the_partial_round_of_long_contractions_only():
             per_pair = [0.0] * pl["pairs"]
             for (mt, nt), ranges in _walk_plan(*shape, pl).items():
                 for kb0, kb1, pair, _ in ranges:
-                    per_pair[pair] += (kb1 - kb0) * (1.0 if nt < pl["n_wide"] else 2.0 / 3.0)
+                    per_pair[pair] += (kb1 - kb0) * (1.0 if nt < pl["n_wide"] else 128.0 / pl["bn"])
             loads.append(max(per_pair))
         assert loads[1] < gain * loads[0], (shape, loads)
