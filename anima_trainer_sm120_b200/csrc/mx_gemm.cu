@@ -873,11 +873,10 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int row_b = it.nt * BN + static_cast<int>(rank) * (narrow ? 64 : BN / 2);
         const int sfa_rt = it.mt * 2 + static_cast<int>(rank), sfb_rt = (it.nt * BN) >> 7;
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
-          if (!mbar_try_wait(empty_bar(s), ph ^ 1u)) {
-            const long long t0 = probe ? clock64() : 0;
-            ok = mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag);
-            if (probe) w_empty += clock64() - t0;
-          }
+          // (try_wait itself blocks for a while before it gives up, so the wait is timed around both)
+          const long long t0 = probe ? clock64() : 0;
+          if (!mbar_try_wait(empty_bar(s), ph ^ 1u)) ok = mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag);
+          if (probe) w_empty += clock64() - t0;
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           if (elect_one()) {
@@ -951,11 +950,9 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const uint32_t sfb_off = ((it.nt * BN) & 127) >> 5;
         uint32_t acc = 0;
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
-          if (!mbar_try_wait(full_bar(s), ph)) {
-            const long long t0 = probe ? clock64() : 0;
-            ok = mbar_wait(full_bar(s), ph, &abort_flag);
-            if (probe) w_full += clock64() - t0;
-          }
+          const long long t0 = probe ? clock64() : 0;
+          if (!mbar_try_wait(full_bar(s), ph)) ok = mbar_wait(full_bar(s), ph, &abort_flag);
+          if (probe) w_full += clock64() - t0;
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();

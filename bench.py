@@ -178,8 +178,8 @@ def workload_config(n_gpus: int) -> dict:
 # ----------------------------------------------------------------------------- GPU arm
 # dram__bytes_read.sum + dram__bytes_write.sum of one forward launch (M=32768, N=8192, K=2048) of the GEMM kernel,
 # taken from one ncu capture of that launch: a number from a profiler run, not re-measured here.
-NCU_TRAFFIC_BYTES = 584.0e6
-NCU_TRAFFIC_NOTE = ("ncu, forward launch 32768x8192x2048: 584 MB moved vs 623 MB algorithmic "
+NCU_TRAFFIC_BYTES = 577.0e6
+NCU_TRAFFIC_NOTE = ("ncu, forward launch 32768x8192x2048: 577 MB moved vs 623 MB algorithmic "
                     "(codes of A and B, scales, bf16 C); the step's launches average 2 M N K = 825 GF")
 
 
