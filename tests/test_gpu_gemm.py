@@ -135,6 +135,23 @@ def test_split_k_matches_oracle_and_single_pass(M, N, K, out_dtype):
     torch.testing.assert_close(c.float(), single.float(), rtol=1e-2 if out_dtype == BF16 else 1e-4, atol=1e-3)
 
 
+@pytest.mark.parametrize("width", ["192", "256"])
+@pytest.mark.parametrize("M,N,K,bias,out_dtype", [
+    (512, 384, 256, True, BF16),            # one tile column at 256 (128 of it outside N), two at 192
+    (1024, 1152, 512, False, BF16),         # 4 x 256 + a narrow column / 6 x 192
+    (264, 2112, 1024, True, BF16),          # 8 x 256 + 64 valid columns in the narrow one; ragged M
+    (19200, 512, 640, False, BF16),         # 150 tiles at 256, 225 at 192: three rounds on 74 pairs, both buffers reused
+    (2048, 2048, 16384, False, torch.float32),   # long contraction, fp32 chunks through the single staging buffer
+    (1536, 768, 8192, True, torch.float32),      # fewer tiles than pairs: every tile split along K, partial tiles
+])
+def test_pair_kernel_at_both_tile_widths(M, N, K, bias, out_dtype, width, monkeypatch):
+    """The CTA-pair kernel picks 256-wide tiles (overlapped accumulator buffers) from K = 4096 up and 192-wide
+    ones below; both forms must serve every shape."""
+    monkeypatch.setenv("ANIMA_MX_GEMM_VARIANT", "2")
+    monkeypatch.setenv("ANIMA_MX_GEMM_BN", width)
+    _gemm_case(M, N, K, seed=41, bias=bias, out_dtype=out_dtype)
+
+
 @pytest.mark.parametrize("M,N,K", [(256, 512, 256), (200, 136, 96), (2048, 256, 128), (128, 256, 8192)])
 def test_alpha_and_residual_epilogue(M, N, K, variant):
     """C = alpha * A.B^T + bias + residual, also written over the residual buffer itself."""
