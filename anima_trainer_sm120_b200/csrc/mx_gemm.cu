@@ -1016,8 +1016,8 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const bool issuer = threadIdx.x == 64 + 128 * half;  // one thread per half issues and tracks its TMA stores
     const uint32_t my_store = store_base + half * (2 * C::kStoreBytes);
     const int bar_id = 1 + half;  // named barrier of this half's 128 threads
-    const uint32_t leader_empty[2] = {map_to_cta(acc_empty_bar(0), 0), map_to_cta(acc_empty_bar(1), 0)};
-    const uint32_t leader_ovl[2] = {map_to_cta(ovl_free_bar(0), 0), map_to_cta(ovl_free_bar(1), 0)};
+    const uint32_t leader_empty0 = map_to_cta(acc_empty_bar(0), 0), leader_empty1 = map_to_cta(acc_empty_bar(1), 0);
+    const uint32_t leader_ovl0 = map_to_cta(ovl_free_bar(0), 0), leader_ovl1 = map_to_cta(ovl_free_bar(1), 0);
     bool ok = true;
     int it_n = 0;
     uint32_t buf = 0;
@@ -1043,9 +1043,9 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const int chunks = (it.nt >= p.n_wide ? 4 : BN / 32) / kEpiHalves;
       const bool fp32_stage = partial || p.out_fp32;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + (as ? C::kAcc1Col : 0);
-#pragma unroll 1
       // Shared columns first: buffer 0 is drained from its last chunk down, buffer 1 from its first chunk up.
       const bool reverse = C::kOverlap && as == 0;
+#pragma unroll 1
       for (int ci = 0; ci < chunks; ++ci, buf ^= 1u) {
         const int chunk = half * chunks + (reverse ? chunks - 1 - ci : ci);
         uint32_t v[32];
@@ -1054,12 +1054,12 @@ mx_gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (ovl_owner && ci == 0) {  // the next tile's MMAs may overwrite the shared columns
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(leader_ovl[as]);
+          if (lane == 0) mbar_arrive_cluster(as ? leader_ovl1 : leader_ovl0);
         }
         if (ci == chunks - 1) {  // this warp's share is read: hand it back to the MMA warp
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(leader_empty[as]);
+          if (lane == 0) mbar_arrive_cluster(as ? leader_empty1 : leader_empty0);
         }
         const int col0 = col_base + chunk * 32;
         float f[32];
