@@ -634,10 +634,11 @@ __global__ void __launch_bounds__(256) splitk_finalize_kernel(const GemmParams p
 // multiples of 32, odd scale-column offsets) raised a misaligned-address fault on its first tile with an odd
 // offset; such widths are therefore not used.
 // What limits it (cycle counters of anima_mx_gemm_set_clock_probe, and builds with parts of the epilogue left
-// out): one more K-block costs the tensor pipe's 384 (512) cycles, i.e. the main loop is MMA-bound; each tile
-// adds about 1200 cycles at BN = 192, of which ~350 are the epilogue's st.shared into the staging buffers and
-// ~200 its TMA stores (the tensor pipe loses about one cycle per 128-byte shared-memory write of the epilogue),
-// and about 2800 at BN = 256 where a tile also waits for the previous one to be read. The SM clock sits at the
+// out): at BN = 192 a K-block costs 404 - 516 cycles depending on K and on the box, against the tensor pipe's
+// 384: operand delivery (57 KB written to and read from shared memory per CTA and K-block) is the limit, and each
+// tile adds about 1200 cycles, of which ~350 are the epilogue's st.shared into the staging buffers and ~200 its
+// TMA stores. At BN = 256 a K-block costs the tensor pipe's 512 cycles (64 KB), and each tile adds about 2800
+// because it also waits for the previous tile's shared columns to be read. The SM clock sits at the
 // board's power limit throughout, so energy per flop (operand traffic per flop: 7/8 at BN = 256) decides as much
 // as idle cycles do.
 // Epilogue warps per CTA: 4 * kEpiHalves. With two halves, two warps share each 32-lane quadrant of tensor memory
