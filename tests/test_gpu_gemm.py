@@ -341,9 +341,12 @@ def _planes_from_rows(t: torch.Tensor) -> torch.Tensor:
     (512, 512, 16384),    # fewer tiles than CTA pairs and a long contraction: every tile is K-split, the delta rides the last range
     (4096, 2048, 1024),   # cross-attention k / v on the text tokens
 ])
-def test_low_rank_delta_as_extra_k_blocks(M, N, K):
+@pytest.mark.parametrize("width", ["192", "256"])
+def test_low_rank_delta_as_extra_k_blocks(M, N, K, width, monkeypatch):
     """anima_mx_gemm_delta: C = A.B^T + bias + sum_r planes[i*M + m, r] * d[p, r] for column i * N/8 + p, against
-    the oracle on identical codes; the planes come from the quantising mix, checked against its plain row form."""
+    the oracle on identical codes; the planes come from the quantising mix, checked against its plain row form.
+    Run at both tile widths of the CTA-pair kernel (the runs of a tile's columns inside one block differ)."""
+    monkeypatch.setenv("ANIMA_MX_GEMM_BN", width)
     ops, lib = _ops()
     from oracle import tlokr as OT
     g = torch.Generator().manual_seed(M + N + K)
